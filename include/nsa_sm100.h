@@ -1,0 +1,224 @@
+/* C ABI of libnsa_sm100.so: hand-written sm_100a kernels for the Native-Sparse-Attention hot path.
+ *
+ * The reference project has no FFI of its own (its kernels are Triton functions launched from Python), so
+ * each entry point below names the reference Python function whose kernel launch it replaces.  The Python
+ * package `flash_nsa` in this repository binds these symbols with ctypes and keeps the reference's Python
+ * signatures on top of them.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless said otherwise; tensors are bf16 (uint16 bit patterns) with a
+ *    contiguous innermost dimension, strides are in ELEMENTS;
+ *  - `stream` is a cudaStream_t passed as void*; calls only enqueue work, they never synchronise, never
+ *    allocate device memory and never free it: every scratch buffer is a caller-provided field;
+ *  - return value 0 = ok, negative = NsaStatus; nsa_last_error() gives the message for the calling thread;
+ *  - sequences are described by NsaSeqMeta.  A "piece" is a run of local query rows belonging to one
+ *    sequence: without context parallelism pieces are the sequences themselves; with it they are the parts
+ *    of sequences that fall into this rank's chunks, and piece_off is the position of the first local row
+ *    inside its sequence (flash_nsa/utils.py:284-323 builds the same table as cp_cu_seqlens / cp_batch_idx /
+ *    cp_offset).  K/V-side tensors always hold whole sequences (x_cu), compressed tensors whole sequences of
+ *    compressed rows (y_cu).
+ */
+#ifndef NSA_SM100_H_
+#define NSA_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum NsaStatus {
+  NSA_OK = 0,
+  NSA_ERR_BAD_ARG = -1,
+  NSA_ERR_UNSUPPORTED_SHAPE = -2,
+  NSA_ERR_CUDA = -3,
+  NSA_ERR_TIMEOUT = -4
+} NsaStatus;
+
+typedef struct NsaSeqMeta {
+  const int32_t* piece_cu;  /* [n_pieces+1] local row offsets of the pieces                                */
+  const int32_t* piece_seq; /* [n_pieces] sequence id of each piece; NULL = identity                         */
+  const int32_t* piece_off; /* [n_pieces] position of the piece's first row in its sequence; NULL = zeros    */
+  const int32_t* x_cu;      /* [n_seq+1] token offsets of the sequences in K/V-side tensors                  */
+  const int32_t* y_cu;      /* [n_seq+1] offsets of the sequences' compressed rows; may be NULL if unused     */
+  int32_t n_pieces;
+  int32_t n_seq;
+  int32_t max_piece_len; /* longest piece (grid sizing)                                                    */
+  int32_t x_maxlen;      /* longest sequence                                                               */
+  int32_t y_maxlen;      /* most compressed rows in one sequence                                           */
+  int32_t reserved0;
+} NsaSeqMeta;
+
+typedef struct NsaHyper {
+  int32_t kernel_size; /* tokens per compressed row (32)            */
+  int32_t stride;      /* distance between compressed rows (16)     */
+  int32_t block_size;  /* tokens per selection block (64)           */
+  int32_t window;      /* sliding window: keys t-window .. t        */
+  int32_t top_n;       /* selected blocks per (token, kv head)      */
+  int32_t num_init;    /* forced first blocks                       */
+  int32_t num_local;   /* forced blocks ending at the query's block */
+  int32_t reserved0;
+} NsaHyper;
+
+/* ---- KV compression ------------------------------------------------------------------------------- */
+typedef struct NsaPoolParams {
+  NsaSeqMeta meta;
+  NsaHyper hp;
+  const void* x; /* [T,H,D] bf16                                                   */
+  void* y;       /* fwd: [Ytot,H,D] bf16 out.  bwd: dy, same shape, bf16 in         */
+  float* dx;     /* bwd only: [T,H,D] fp32                                          */
+  int64_t x_stride_t, y_stride_t, dx_stride_t; /* token strides (head stride = D)   */
+  int32_t H, D;
+  int32_t accumulate; /* bwd: 1 = add into dx, 0 = overwrite                        */
+  int32_t reserved0;
+} NsaPoolParams;
+/* replaces mean_pooling_fwd, flash_nsa/ops/compress_kv.py:335-366 */
+int nsa_mean_pool_fwd(const NsaPoolParams* p, void* stream);
+/* replaces mean_pooling_bwd, flash_nsa/ops/compress_kv.py:368-399 (dx is fp32, as in the fused backward) */
+int nsa_mean_pool_bwd(const NsaPoolParams* p, void* stream);
+
+typedef struct NsaBlockParams {
+  NsaSeqMeta meta;
+  NsaHyper hp;
+  const void* x; /* fwd: [T,H,D] bf16 in                                            */
+  void* y;       /* fwd: [Ytot,H,kernel_size,D] bf16 out.  bwd: dy (bf16 in)        */
+  float* dx;     /* bwd: [T,H,D] fp32                                               */
+  int64_t x_stride_t, dx_stride_t;
+  int32_t H, D;
+  int32_t accumulate;
+  int32_t reserved0;
+} NsaBlockParams;
+/* replaces construct_block_fwd / construct_block_bwd, flash_nsa/ops/compress_kv.py:127-190 */
+int nsa_construct_block_fwd(const NsaBlockParams* p, void* stream);
+int nsa_construct_block_bwd(const NsaBlockParams* p, void* stream);
+
+typedef struct NsaActParams {
+  const void* x;  /* [M,2K] bf16: gate | up                                          */
+  void* y;        /* fwd: [M,K] bf16 out                                             */
+  const void* dy; /* bwd: [M,K] bf16                                                 */
+  void* dx;       /* bwd: [M,2K] bf16 out (may alias x)                              */
+  int64_t M;
+  int32_t K;
+  int32_t kind; /* 0 = swiglu (silu(gate)*up), 1 = sigmoid-mul (sigmoid(gate)*up)    */
+} NsaActParams;
+/* replaces swiglu_fwd/bwd and sigmoid_mul_fwd/bwd, flash_nsa/ops/act.py:60-94, 174-208 */
+int nsa_act_fwd(const NsaActParams* p, void* stream);
+int nsa_act_bwd(const NsaActParams* p, void* stream);
+
+/* ---- attention branches ----------------------------------------------------------------------------- */
+typedef struct NsaAttnParams {
+  NsaSeqMeta meta;
+  NsaHyper hp;
+  const void* q;     /* [Tq,QH,D] bf16 (local rows)                                                      */
+  const void* k;     /* compressed branch: [Ytot,KH,D]; otherwise [Tk,KH,D]                               */
+  const void* v;     /* same rows as k, [.,KH,D]                                                          */
+  void* o;           /* [Tq,QH,D] bf16; fwd out, bwd in                                                   */
+  float* lse;        /* base-2 log-sum-exp of the scaled scores; element (t,h) at t*lse_stride_t+h*lse_stride_h */
+  const void* dout;  /* bwd: [Tq,QH,D] bf16                                                               */
+  float* delta;      /* bwd scratch, same addressing as lse: rowsum(o*dout), written by the call          */
+  void* dq;          /* bwd: [Tq,QH,D] bf16                                                               */
+  float* dk;         /* bwd: fp32, same rows as k                                                         */
+  float* dv;         /* bwd: fp32, same rows as v                                                         */
+  const int32_t* topk; /* selected branch: [KH,Tq,top_n] int32                                            */
+  const int32_t* k2q_offsets; /* selected bwd: [KH, n_blocks_total+1] CSR offsets from nsa_k2q_index      */
+  const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows, ascending inside a block  */
+  int64_t q_stride_t, k_stride_t, v_stride_t, o_stride_t, do_stride_t, dq_stride_t, dk_stride_t, dv_stride_t;
+  int64_t lse_stride_t, lse_stride_h;
+  int64_t topk_stride_h; /* elements between kv heads in topk (= Tq*top_n when contiguous)                */
+  int64_t k2q_stride_h;  /* elements between kv heads in k2q_tokens                                       */
+  float sm_scale;
+  int32_t QH, KH, D;
+  int32_t accumulate_dq;   /* bwd: 1 = dq += result, 0 = dq = result                                      */
+  int32_t accumulate_dkdv; /* bwd: 1 = dk/dv += result, 0 = overwrite (compressed branch always adds:
+                              the caller zero-fills)                                                       */
+  int32_t n_blocks_total;  /* selected bwd: rows of the k2q table per kv head                             */
+  int32_t reserved0;
+} NsaAttnParams;
+
+/* compressed attention: replaces cmp_attn_fwd / cmp_attn_bwd, flash_nsa/ops/compress_attn.py:532-741.
+ * lse layout of the reference is [QH,T]: pass lse_stride_h = T, lse_stride_t = 1.                        */
+int nsa_cmp_attn_fwd(const NsaAttnParams* p, void* stream);
+int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream);
+/* sliding-window attention: replaces swa_fwd / swa_bwd, flash_nsa/ops/sliding_window_attention.py:42-157,
+ * i.e. the flash-attn call with window_size=(window,-1), causal=True.                                     */
+int nsa_swa_fwd(const NsaAttnParams* p, void* stream);
+int nsa_swa_bwd(const NsaAttnParams* p, void* stream);
+/* selected-block attention: replaces slc_attn_fwd / slc_attn_bwd, flash_nsa/ops/select_attn.py:440-701    */
+int nsa_slc_attn_fwd(const NsaAttnParams* p, void* stream);
+int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream);
+
+/* ---- block importance + top-n ----------------------------------------------------------------------- */
+typedef struct NsaTopkParams {
+  NsaSeqMeta meta;
+  NsaHyper hp;
+  const void* q;    /* [Tq,QH,D] bf16                                                                     */
+  const void* ck;   /* [Ytot,KH,D] bf16 compressed keys                                                   */
+  const float* lse; /* log-sum-exp of the compressed branch (addressing as in NsaAttnParams)              */
+  int32_t* topk;    /* out [KH,Tq,top_n]; unused slots keep ignore_index                                  */
+  void* probs;      /* optional out [KH,Tq,probs_stride_t] block scores (fp16 or fp32 per quant), or NULL  */
+  int64_t q_stride_t, ck_stride_t, lse_stride_t, lse_stride_h, probs_stride_t;
+  float sm_scale;
+  int32_t QH, KH, D;
+  int32_t ignore_index;
+  int32_t quant; /* what the selection compares: 0 = fp32 score, 1 = score rounded to fp16,
+                    2 = score^3 rounded to fp16 (the reference default below 128K tokens)                  */
+  int32_t reserved0;
+  int32_t reserved1;
+} NsaTopkParams;
+/* replaces slc_topk_indices_for_32_16_64 (kernel pair _slc_probs_kernel + _topk_kernel),
+ * flash_nsa/ops/topk.py:499-628; scores and selection are fused, no [KH,T,blocks] scratch is needed.      */
+int nsa_slc_topk(const NsaTopkParams* p, void* stream);
+
+typedef struct NsaK2qParams {
+  NsaSeqMeta meta;
+  NsaHyper hp;
+  const int32_t* topk; /* [KH,Tq,top_n]                                                                   */
+  int32_t* offsets;    /* out [KH, n_blocks_total+1]; also used as the histogram while building           */
+  int32_t* tokens;     /* out [KH, Tq*top_n]                                                              */
+  int32_t* cursor;     /* scratch [KH, n_blocks_total] (any contents)                                     */
+  const int32_t* blk_cu; /* [n_pieces+1] offsets of each piece's block rows (cdiv(len+off, block_size))    */
+  int64_t Tq;
+  int32_t KH;
+  int32_t n_blocks_total;
+} NsaK2qParams;
+/* replaces get_bind_from_find, flash_nsa/ops/topk.py:889-945: for every (kv head, key block) the list of local
+ * query rows that selected it, as CSR (counts -> exclusive scan -> stable fill) instead of a dense table.  */
+int nsa_k2q_index(const NsaK2qParams* p, void* stream);
+
+/* ---- gated combine ---------------------------------------------------------------------------------- */
+typedef struct NsaCombineParams {
+  const void *a, *b, *c; /* [T,H,D] bf16 branch outputs                                                    */
+  const void* w;         /* [T,H,3] bf16 gate logits                                                       */
+  void* y;               /* fwd out [T,H,D] bf16                                                           */
+  const void* dy;        /* bwd in                                                                         */
+  void *da, *db, *dc;    /* bwd out [T,H,D] bf16                                                           */
+  void* dw;              /* bwd out [T,H,3] bf16                                                           */
+  int64_t a_stride_t, b_stride_t, c_stride_t, w_stride_t, y_stride_t, dy_stride_t, dw_stride_t;
+  int64_t T;
+  int32_t H, D;
+} NsaCombineParams;
+/* replaces combine_fwd / combine_bwd, flash_nsa/ops/combine.py:114-177 */
+int nsa_combine_fwd(const NsaCombineParams* p, void* stream);
+int nsa_combine_bwd(const NsaCombineParams* p, void* stream);
+
+/* ---- context-parallel chunk reorder ------------------------------------------------------------------ */
+typedef struct NsaReorderParams {
+  const void* x; /* [2*world_size chunks of chunk_bytes bytes]                                            */
+  void* y;       /* same size, must not alias x                                                           */
+  int64_t chunk_bytes; /* multiple of 16                                                                  */
+  int32_t world_size;
+  int32_t unshuffle; /* 0: sequential -> rank-major zig-zag; 1: the inverse                               */
+} NsaReorderParams;
+/* replaces reorder, flash_nsa/ops/reorder.py:43-93 (out of place) */
+int nsa_reorder(const NsaReorderParams* p, void* stream);
+
+/* ---- misc -------------------------------------------------------------------------------------------- */
+const char* nsa_last_error(void);
+int nsa_version(void);
+/* sizeof() of a parameter struct by name ("NsaAttnParams", ...), 0 if unknown: lets a binding verify its mirror */
+int nsa_struct_size(const char* name);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NSA_SM100_H_ */

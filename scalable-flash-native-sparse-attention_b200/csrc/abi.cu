@@ -1,0 +1,48 @@
+// Error reporting and version of the C ABI.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include "nsa_common.cuh"
+
+namespace nsa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+// cudaPeekAtLastError keeps a sticky fault visible to the caller's own checks as well.
+int check_launch(const char* what) {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
+    return NSA_ERR_CUDA;
+  }
+  return NSA_OK;
+}
+
+}  // namespace nsa
+
+extern "C" const char* nsa_last_error(void) { return nsa::g_err; }
+extern "C" int nsa_version(void) { return 100; }
+
+extern "C" int nsa_struct_size(const char* name) {
+  if (!name) return 0;
+#define NSA_SZ(T) if (!strcmp(name, #T)) return (int)sizeof(T)
+  NSA_SZ(NsaSeqMeta);
+  NSA_SZ(NsaHyper);
+  NSA_SZ(NsaPoolParams);
+  NSA_SZ(NsaBlockParams);
+  NSA_SZ(NsaActParams);
+  NSA_SZ(NsaAttnParams);
+  NSA_SZ(NsaTopkParams);
+  NSA_SZ(NsaK2qParams);
+  NSA_SZ(NsaCombineParams);
+  NSA_SZ(NsaReorderParams);
+#undef NSA_SZ
+  return 0;
+}

@@ -1,0 +1,388 @@
+// Memory-bound pieces of the NSA path: window pooling, window gather (im2col), gate activations, the gated
+// combine and the context-parallel chunk reorder.  All of them move 16 bytes per thread per access and do
+// their arithmetic in fp32.
+#include "nsa_common.cuh"
+
+namespace nsa {
+
+struct F8 {
+  float v[8];
+};
+__device__ __forceinline__ F8 unpack8(uint4 u) {
+  F8 r;
+  r.v[0] = bf16_lo(u.x); r.v[1] = bf16_hi(u.x);
+  r.v[2] = bf16_lo(u.y); r.v[3] = bf16_hi(u.y);
+  r.v[4] = bf16_lo(u.z); r.v[5] = bf16_hi(u.z);
+  r.v[6] = bf16_lo(u.w); r.v[7] = bf16_hi(u.w);
+  return r;
+}
+__device__ __forceinline__ uint4 pack8(const F8& f) {
+  uint4 u;
+  u.x = pack_bf16(f.v[0], f.v[1]);
+  u.y = pack_bf16(f.v[2], f.v[3]);
+  u.z = pack_bf16(f.v[4], f.v[5]);
+  u.w = pack_bf16(f.v[6], f.v[7]);
+  return u;
+}
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// ------------------------------------------------------------------------------------------------ pooling
+// y[j,h,:] = (sum_{i<ks} x[st*j+i,h,:]) / ks          grid: (cdiv(y_maxlen*CH,256), n_seq, H)
+__global__ void mean_pool_fwd_kernel(NsaPoolParams p) {
+  const int CH = p.D / 8;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  int j = idx / CH, c = idx % CH;
+  int b = blockIdx.y, h = blockIdx.z;
+  int x_bos = p.meta.x_cu[b];
+  int y_bos = p.meta.y_cu[b], y_len = p.meta.y_cu[b + 1] - y_bos;
+  if (j >= y_len) return;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x) +
+                           (int64_t)(x_bos + (int64_t)j * p.hp.stride) * p.x_stride_t + h * p.D + c * 8;
+  F8 acc;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
+  for (int i = 0; i < p.hp.kernel_size; ++i) {
+    F8 f = unpack8(ldg16(x + (int64_t)i * p.x_stride_t));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+  }
+  float inv = 1.f / (float)p.hp.kernel_size;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] *= inv;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)(y_bos + j) * p.y_stride_t + h * p.D + c * 8;
+  *reinterpret_cast<uint4*>(y) = pack8(acc);
+}
+
+// dx[t,h,:] (+)= sum over rows j whose window holds t of dy[j,h,:] / ks      grid: (cdiv(x_maxlen*CH,256), n_seq, H)
+__global__ void mean_pool_bwd_kernel(NsaPoolParams p) {
+  const int CH = p.D / 8;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  int t = idx / CH, c = idx % CH;
+  int b = blockIdx.y, h = blockIdx.z;
+  int x_bos = p.meta.x_cu[b], x_len = p.meta.x_cu[b + 1] - x_bos;
+  int y_bos = p.meta.y_cu[b], y_len = p.meta.y_cu[b + 1] - y_bos;
+  if (t >= x_len) return;
+  const int ks = p.hp.kernel_size, st = p.hp.stride;
+  int j_hi = min(t / st, y_len - 1);
+  int j_lo = max((t - ks + st) / st, 0);  // ceil((t-ks+1)/st) for t-ks+1 > 0
+  if (t - ks + 1 <= 0) j_lo = 0;
+  F8 acc;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
+  const __nv_bfloat16* dy = reinterpret_cast<const __nv_bfloat16*>(p.y) + h * p.D + c * 8;
+  for (int j = j_lo; j <= j_hi; ++j) {
+    F8 f = unpack8(ldg16(dy + (int64_t)(y_bos + j) * p.y_stride_t));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+  }
+  float inv = 1.f / (float)ks;
+  float* dx = p.dx + (int64_t)(x_bos + t) * p.dx_stride_t + h * p.D + c * 8;
+  float4 o0, o1;
+  if (p.accumulate) {
+    o0 = *reinterpret_cast<float4*>(dx);
+    o1 = *reinterpret_cast<float4*>(dx + 4);
+  } else {
+    o0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    o1 = o0;
+  }
+  o0.x += acc.v[0] * inv; o0.y += acc.v[1] * inv; o0.z += acc.v[2] * inv; o0.w += acc.v[3] * inv;
+  o1.x += acc.v[4] * inv; o1.y += acc.v[5] * inv; o1.z += acc.v[6] * inv; o1.w += acc.v[7] * inv;
+  *reinterpret_cast<float4*>(dx) = o0;
+  *reinterpret_cast<float4*>(dx + 4) = o1;
+}
+
+// ------------------------------------------------------------------------------------------------ im2col
+// y[j,h,i,:] = x[st*j+i,h,:]                      grid: (cdiv(y_maxlen*ks*CH,256), n_seq, H)
+__global__ void construct_block_fwd_kernel(NsaBlockParams p) {
+  const int CH = p.D / 8;
+  const int ks = p.hp.kernel_size;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int c = idx % CH;
+  int i = (idx / CH) % ks;
+  int j = idx / ((int64_t)CH * ks);
+  int b = blockIdx.y, h = blockIdx.z;
+  int x_bos = p.meta.x_cu[b];
+  int y_bos = p.meta.y_cu[b], y_len = p.meta.y_cu[b + 1] - y_bos;
+  if (j >= y_len) return;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x) +
+                           (int64_t)(x_bos + (int64_t)j * p.hp.stride + i) * p.x_stride_t + h * p.D + c * 8;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y) +
+                     (((int64_t)(y_bos + j) * p.H + h) * ks + i) * p.D + c * 8;
+  *reinterpret_cast<uint4*>(y) = ldg16(x);
+}
+
+// dx[t,h,:] (+)= sum_j dy[j,h,t-st*j,:]           grid: (cdiv(x_maxlen*CH,256), n_seq, H)
+__global__ void construct_block_bwd_kernel(NsaBlockParams p) {
+  const int CH = p.D / 8;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  int t = idx / CH, c = idx % CH;
+  int b = blockIdx.y, h = blockIdx.z;
+  int x_bos = p.meta.x_cu[b], x_len = p.meta.x_cu[b + 1] - x_bos;
+  int y_bos = p.meta.y_cu[b], y_len = p.meta.y_cu[b + 1] - y_bos;
+  if (t >= x_len) return;
+  const int ks = p.hp.kernel_size, st = p.hp.stride;
+  int j_hi = min(t / st, y_len - 1);
+  int j_lo = (t - ks + 1 <= 0) ? 0 : (t - ks + st) / st;
+  F8 acc;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
+  const __nv_bfloat16* dy = reinterpret_cast<const __nv_bfloat16*>(p.y);
+  for (int j = j_lo; j <= j_hi; ++j) {
+    int i = t - st * j;
+    F8 f = unpack8(ldg16(dy + (((int64_t)(y_bos + j) * p.H + h) * ks + i) * p.D + c * 8));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+  }
+  float* dx = p.dx + (int64_t)(x_bos + t) * p.dx_stride_t + h * p.D + c * 8;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) dx[e] = (p.accumulate ? dx[e] : 0.f) + acc.v[e];
+}
+
+// ------------------------------------------------------------------------------------------------ gate activations
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__global__ void act_fwd_kernel(NsaActParams p) {
+  const int CH = p.K / 8;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.M * CH) return;
+  int64_t m = idx / CH;
+  int c = idx % CH;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x) + m * 2 * p.K + c * 8;
+  F8 g = unpack8(ldg16(x)), u = unpack8(ldg16(x + p.K)), y;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float s = sigmoidf_(g.v[e]);
+    y.v[e] = (p.kind == 0 ? g.v[e] * s : s) * u.v[e];
+  }
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + m * p.K + c * 8) = pack8(y);
+}
+
+__global__ void act_bwd_kernel(NsaActParams p) {
+  const int CH = p.K / 8;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.M * CH) return;
+  int64_t m = idx / CH;
+  int c = idx % CH;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x) + m * 2 * p.K + c * 8;
+  F8 g = unpack8(*reinterpret_cast<const uint4*>(x)), u = unpack8(*reinterpret_cast<const uint4*>(x + p.K));
+  F8 dy = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.dy) + m * p.K + c * 8));
+  F8 dg, du;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float s = sigmoidf_(g.v[e]);
+    if (p.kind == 0) {
+      du.v[e] = dy.v[e] * g.v[e] * s;
+      dg.v[e] = dy.v[e] * u.v[e] * s * (1.f + g.v[e] * (1.f - s));
+    } else {
+      du.v[e] = dy.v[e] * s;
+      dg.v[e] = dy.v[e] * u.v[e] * s * (1.f - s);
+    }
+  }
+  __nv_bfloat16* dx = reinterpret_cast<__nv_bfloat16*>(p.dx) + m * 2 * p.K + c * 8;
+  *reinterpret_cast<uint4*>(dx) = pack8(dg);
+  *reinterpret_cast<uint4*>(dx + p.K) = pack8(du);
+}
+
+// ------------------------------------------------------------------------------------------------ gated combine
+// one thread per 8 output elements; the D/8 threads of a (t,h) row are adjacent lanes of one warp
+__global__ void combine_fwd_kernel(NsaCombineParams p) {
+  const int CH = p.D / 8;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t row = idx / CH;
+  int c = idx % CH;
+  if (row >= p.T * p.H) return;
+  int64_t t = row / p.H;
+  int h = row % p.H;
+  const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(p.w) + t * p.w_stride_t + h * 3;
+  float s0 = sigmoidf_(__bfloat162float(w[0])), s1 = sigmoidf_(__bfloat162float(w[1])),
+        s2 = sigmoidf_(__bfloat162float(w[2]));
+  int64_t col = (int64_t)h * p.D + c * 8;
+  F8 a = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.a) + t * p.a_stride_t + col));
+  F8 b = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.b) + t * p.b_stride_t + col));
+  F8 cc = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.c) + t * p.c_stride_t + col));
+  F8 y;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y.v[e] = a.v[e] * s0 + b.v[e] * s1 + cc.v[e] * s2;
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + t * p.y_stride_t + col) = pack8(y);
+}
+
+__global__ void combine_bwd_kernel(NsaCombineParams p) {
+  const int CH = p.D / 8;  // 8 or 16: a row's threads are an aligned lane group
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t row = idx / CH;
+  int c = idx % CH;
+  bool live = row < p.T * p.H;
+  int64_t t = live ? row / p.H : 0;
+  int h = live ? row % p.H : 0;
+  const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(p.w) + t * p.w_stride_t + h * 3;
+  float s0 = sigmoidf_(__bfloat162float(w[0])), s1 = sigmoidf_(__bfloat162float(w[1])),
+        s2 = sigmoidf_(__bfloat162float(w[2]));
+  int64_t col = (int64_t)h * p.D + c * 8;
+  F8 a = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.a) + t * p.a_stride_t + col));
+  F8 b = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.b) + t * p.b_stride_t + col));
+  F8 cc = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.c) + t * p.c_stride_t + col));
+  F8 dy = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.dy) + t * p.dy_stride_t + col));
+  F8 da, db, dc;
+  float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    da.v[e] = dy.v[e] * s0;
+    db.v[e] = dy.v[e] * s1;
+    dc.v[e] = dy.v[e] * s2;
+    r0 += dy.v[e] * a.v[e];
+    r1 += dy.v[e] * b.v[e];
+    r2 += dy.v[e] * cc.v[e];
+  }
+  for (int o = CH / 2; o > 0; o >>= 1) {
+    r0 += __shfl_xor_sync(0xffffffffu, r0, o);
+    r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+    r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+  }
+  if (!live) return;
+  int64_t ocol = (t * p.H + h) * (int64_t)p.D + c * 8;  // da/db/dc are contiguous [T,H,D]
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.da) + ocol) = pack8(da);
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.db) + ocol) = pack8(db);
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dc) + ocol) = pack8(dc);
+  if (c == 0) {
+    __nv_bfloat16* dw = reinterpret_cast<__nv_bfloat16*>(p.dw) + t * p.dw_stride_t + h * 3;
+    dw[0] = __float2bfloat16(s0 * (1.f - s0) * r0);
+    dw[1] = __float2bfloat16(s1 * (1.f - s1) * r1);
+    dw[2] = __float2bfloat16(s2 * (1.f - s2) * r2);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ chunk reorder
+// "shuffle": sequential chunk m < W goes to slot 2m, chunk m+W goes to slot 2(W-m)-1 ... i.e. slot 2i holds
+// chunk i and slot 2i+1 holds chunk 2W-1-i.  "unshuffle" is the inverse.
+__global__ void reorder_kernel(NsaReorderParams p) {
+  int64_t per = p.chunk_bytes / 16;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= per * 2 * p.world_size) return;
+  int slot = idx / per;
+  int64_t within = idx % per;
+  int chunk = (slot & 1) ? (2 * p.world_size - 1 - slot / 2) : slot / 2;  // slot (rank-major) -> sequential chunk
+  int src = p.unshuffle ? slot : chunk;
+  int dst = p.unshuffle ? chunk : slot;
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  uint4* y = reinterpret_cast<uint4*>(p.y);
+  y[dst * per + within] = x[src * per + within];
+}
+
+// ------------------------------------------------------------------------------------------------ delta = rowsum(o*do)
+// one thread per 8 elements of a (t,h) row; used by every attention backward.
+__global__ void delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, int64_t T, int H, int D,
+                             int64_t o_stride_t, int64_t do_stride_t, int64_t lse_stride_t, int64_t lse_stride_h) {
+  const int CH = D / 8;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t row = idx / CH;
+  int c = idx % CH;
+  bool live = row < T * H;
+  int64_t t = live ? row / H : 0;
+  int h = live ? row % H : 0;
+  int64_t col = (int64_t)h * D + c * 8;
+  F8 a = unpack8(ldg16(o + t * o_stride_t + col));
+  F8 b = unpack8(ldg16(dout + t * do_stride_t + col));
+  float r = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) r += a.v[e] * b.v[e];
+  for (int off = CH / 2; off > 0; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+  if (live && c == 0) delta[t * lse_stride_t + h * lse_stride_h] = r;
+}
+
+void launch_delta(const void* o, const void* dout, float* delta, int64_t T, int H, int D, int64_t o_stride_t,
+                  int64_t do_stride_t, int64_t lse_stride_t, int64_t lse_stride_h, cudaStream_t st) {
+  int64_t n = T * H * (D / 8);
+  if (n == 0) return;
+  delta_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(o),
+                                                            reinterpret_cast<const __nv_bfloat16*>(dout), delta, T, H, D,
+                                                            o_stride_t, do_stride_t, lse_stride_t, lse_stride_h);
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" int nsa_mean_pool_fwd(const NsaPoolParams* p, void* stream) {
+  NSA_REQUIRE(p && p->x && p->y && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "mean_pool_fwd: null pointer");
+  NSA_REQUIRE(p->D % 8 == 0 && p->D > 0, NSA_ERR_UNSUPPORTED_SHAPE, "mean_pool_fwd: D=%d must be a multiple of 8", p->D);
+  if (p->meta.y_maxlen <= 0 || p->meta.n_seq <= 0) return NSA_OK;
+  dim3 grid((unsigned)(((int64_t)p->meta.y_maxlen * (p->D / 8) + 255) / 256), p->meta.n_seq, p->H);
+  mean_pool_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("mean_pool_fwd");
+}
+
+extern "C" int nsa_mean_pool_bwd(const NsaPoolParams* p, void* stream) {
+  NSA_REQUIRE(p && p->y && p->dx && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "mean_pool_bwd: null pointer");
+  NSA_REQUIRE(p->D % 8 == 0 && p->D > 0, NSA_ERR_UNSUPPORTED_SHAPE, "mean_pool_bwd: D=%d must be a multiple of 8", p->D);
+  if (p->meta.x_maxlen <= 0 || p->meta.n_seq <= 0) return NSA_OK;
+  dim3 grid((unsigned)(((int64_t)p->meta.x_maxlen * (p->D / 8) + 255) / 256), p->meta.n_seq, p->H);
+  mean_pool_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("mean_pool_bwd");
+}
+
+extern "C" int nsa_construct_block_fwd(const NsaBlockParams* p, void* stream) {
+  NSA_REQUIRE(p && p->x && p->y && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "construct_block_fwd: null pointer");
+  NSA_REQUIRE(p->D % 8 == 0 && p->D > 0, NSA_ERR_UNSUPPORTED_SHAPE, "construct_block_fwd: D=%d", p->D);
+  if (p->meta.y_maxlen <= 0 || p->meta.n_seq <= 0) return NSA_OK;
+  int64_t n = (int64_t)p->meta.y_maxlen * p->hp.kernel_size * (p->D / 8);
+  dim3 grid((unsigned)((n + 255) / 256), p->meta.n_seq, p->H);
+  construct_block_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("construct_block_fwd");
+}
+
+extern "C" int nsa_construct_block_bwd(const NsaBlockParams* p, void* stream) {
+  NSA_REQUIRE(p && p->y && p->dx && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "construct_block_bwd: null pointer");
+  NSA_REQUIRE(p->D % 8 == 0 && p->D > 0, NSA_ERR_UNSUPPORTED_SHAPE, "construct_block_bwd: D=%d", p->D);
+  if (p->meta.x_maxlen <= 0 || p->meta.n_seq <= 0) return NSA_OK;
+  dim3 grid((unsigned)(((int64_t)p->meta.x_maxlen * (p->D / 8) + 255) / 256), p->meta.n_seq, p->H);
+  construct_block_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("construct_block_bwd");
+}
+
+extern "C" int nsa_act_fwd(const NsaActParams* p, void* stream) {
+  NSA_REQUIRE(p && p->x && p->y, NSA_ERR_BAD_ARG, "act_fwd: null pointer");
+  NSA_REQUIRE(p->K % 8 == 0 && p->K > 0, NSA_ERR_UNSUPPORTED_SHAPE, "act_fwd: K=%d must be a multiple of 8", p->K);
+  NSA_REQUIRE(p->kind == 0 || p->kind == 1, NSA_ERR_BAD_ARG, "act_fwd: kind=%d", p->kind);
+  int64_t n = p->M * (p->K / 8);
+  if (n == 0) return NSA_OK;
+  act_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("act_fwd");
+}
+
+extern "C" int nsa_act_bwd(const NsaActParams* p, void* stream) {
+  NSA_REQUIRE(p && p->x && p->dy && p->dx, NSA_ERR_BAD_ARG, "act_bwd: null pointer");
+  NSA_REQUIRE(p->K % 8 == 0 && p->K > 0, NSA_ERR_UNSUPPORTED_SHAPE, "act_bwd: K=%d must be a multiple of 8", p->K);
+  NSA_REQUIRE(p->kind == 0 || p->kind == 1, NSA_ERR_BAD_ARG, "act_bwd: kind=%d", p->kind);
+  int64_t n = p->M * (p->K / 8);
+  if (n == 0) return NSA_OK;
+  act_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("act_bwd");
+}
+
+extern "C" int nsa_combine_fwd(const NsaCombineParams* p, void* stream) {
+  NSA_REQUIRE(p && p->a && p->b && p->c && p->w && p->y, NSA_ERR_BAD_ARG, "combine_fwd: null pointer");
+  NSA_REQUIRE(p->D == 64 || p->D == 128 || p->D == 256, NSA_ERR_UNSUPPORTED_SHAPE, "combine_fwd: D=%d (64/128/256)", p->D);
+  int64_t n = p->T * p->H * (p->D / 8);
+  if (n == 0) return NSA_OK;
+  combine_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("combine_fwd");
+}
+
+extern "C" int nsa_combine_bwd(const NsaCombineParams* p, void* stream) {
+  NSA_REQUIRE(p && p->a && p->b && p->c && p->w && p->dy && p->da && p->db && p->dc && p->dw, NSA_ERR_BAD_ARG,
+              "combine_bwd: null pointer");
+  NSA_REQUIRE(p->D == 64 || p->D == 128 || p->D == 256, NSA_ERR_UNSUPPORTED_SHAPE, "combine_bwd: D=%d (64/128/256)", p->D);
+  int64_t n = p->T * p->H * (p->D / 8);
+  if (n == 0) return NSA_OK;
+  combine_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("combine_bwd");
+}
+
+extern "C" int nsa_reorder(const NsaReorderParams* p, void* stream) {
+  NSA_REQUIRE(p && p->x && p->y && p->x != p->y, NSA_ERR_BAD_ARG, "reorder: null or aliased pointer");
+  NSA_REQUIRE(p->chunk_bytes % 16 == 0 && p->world_size > 0, NSA_ERR_BAD_ARG, "reorder: chunk_bytes %% 16 != 0");
+  int64_t n = p->chunk_bytes / 16 * 2 * p->world_size;
+  if (n == 0) return NSA_OK;
+  reorder_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("reorder");
+}

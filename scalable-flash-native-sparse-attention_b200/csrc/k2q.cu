@@ -1,0 +1,113 @@
+// Key-block -> queries index for the selected-attention backward.
+// For every (kv head, key block row) the list of local query rows that selected the block, in CSR form:
+// count (histogram) -> exclusive scan -> fill.  Memory is O(T*top_n) instead of a dense [KH, blocks, T] table.
+// Block rows are laid out piece by piece: row = blk_cu[piece] + block index inside the sequence.
+// The order of the rows inside one list is not fixed (the fill uses an atomic cursor).
+#include "nsa_common.cuh"
+
+namespace nsa {
+
+__device__ __forceinline__ int find_piece(const int32_t* cu, int n, int row) {
+  int lo = 0, hi = n;  // largest b with cu[b] <= row
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (cu[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// returns the table row of entry (kh, q_row, slot) or -1 when the slot is unused / out of range
+__device__ __forceinline__ int entry_row(const NsaK2qParams& p, int kh, int64_t q_row, int slot) {
+  int b = find_piece(p.meta.piece_cu, p.meta.n_pieces, (int)q_row);
+  int off = p.meta.piece_off ? p.meta.piece_off[b] : 0;
+  int t_abs = off + (int)q_row - p.meta.piece_cu[b];
+  int nk = t_abs / p.hp.block_size;
+  if (slot >= min(p.hp.top_n, nk + 1)) return -1;
+  int blk = p.topk[((int64_t)kh * p.Tq + q_row) * p.hp.top_n + slot];
+  if (blk < 0 || blk > nk) return -1;
+  return p.blk_cu[b] + blk;
+}
+
+__global__ void k2q_zero_kernel(NsaK2qParams p) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n_off = (int64_t)p.KH * (p.n_blocks_total + 1), n_cur = (int64_t)p.KH * p.n_blocks_total;
+  if (i < n_off) p.offsets[i] = 0;
+  if (i < n_cur) p.cursor[i] = 0;
+}
+
+__global__ void k2q_count_kernel(NsaK2qParams p) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int kh = blockIdx.y;
+  if (i >= p.Tq * p.hp.top_n) return;
+  int row = entry_row(p, kh, i / p.hp.top_n, (int)(i % p.hp.top_n));
+  if (row >= 0) atomicAdd(p.offsets + (int64_t)kh * (p.n_blocks_total + 1) + row + 1, 1);
+}
+
+// in-place inclusive scan of offsets[kh][1..n] (offsets[kh][0] stays 0): one CTA of 1024 threads per kv head
+__global__ void k2q_scan_kernel(NsaK2qParams p) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  int* a = p.offsets + (int64_t)blockIdx.x * (p.n_blocks_total + 1) + 1;
+  const int n = p.n_blocks_total, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    int i = base + tid;
+    int v = i < n ? a[i] : 0;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_sums[w] = x;
+    __syncthreads();
+    if (w == 0) {
+      int s = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, s, o);
+        if (lane >= o) s += y;
+      }
+      warp_sums[lane] = s;
+    }
+    __syncthreads();
+    int total = x + (w > 0 ? warp_sums[w - 1] : 0) + carry_s;
+    if (i < n) a[i] = total;
+    __syncthreads();
+    if (tid == 1023) carry_s = total;
+    __syncthreads();
+  }
+}
+
+__global__ void k2q_fill_kernel(NsaK2qParams p) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int kh = blockIdx.y;
+  if (i >= p.Tq * p.hp.top_n) return;
+  int64_t q_row = i / p.hp.top_n;
+  int row = entry_row(p, kh, q_row, (int)(i % p.hp.top_n));
+  if (row < 0) return;
+  int pos = p.offsets[(int64_t)kh * (p.n_blocks_total + 1) + row] + atomicAdd(p.cursor + (int64_t)kh * p.n_blocks_total + row, 1);
+  p.tokens[(int64_t)kh * (p.Tq * p.hp.top_n) + pos] = (int)q_row;
+}
+
+}  // namespace nsa
+
+using namespace nsa;
+
+extern "C" int nsa_k2q_index(const NsaK2qParams* p, void* stream) {
+  NSA_REQUIRE(p && p->topk && p->offsets && p->tokens && p->cursor && p->blk_cu && p->meta.piece_cu, NSA_ERR_BAD_ARG,
+              "k2q_index: null pointer");
+  NSA_REQUIRE(p->KH > 0 && p->n_blocks_total >= 0 && p->hp.top_n > 0 && p->hp.block_size > 0, NSA_ERR_BAD_ARG, "k2q_index: bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t nz = (int64_t)p->KH * (p->n_blocks_total + 1);
+  k2q_zero_kernel<<<(unsigned)((nz + 255) / 256), 256, 0, st>>>(*p);
+  int64_t n = p->Tq * p->hp.top_n;
+  if (n > 0 && p->n_blocks_total > 0) {
+    dim3 grid((unsigned)((n + 255) / 256), p->KH);
+    k2q_count_kernel<<<grid, 256, 0, st>>>(*p);
+    k2q_scan_kernel<<<p->KH, 1024, 0, st>>>(*p);
+    k2q_fill_kernel<<<grid, 256, 0, st>>>(*p);
+  }
+  return check_launch("k2q_index");
+}

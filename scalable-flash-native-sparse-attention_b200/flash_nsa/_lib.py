@@ -1,0 +1,88 @@
+"""ctypes binding of libnsa_sm100.so.
+
+The parameter structs are mirrored from include/nsa_sm100.h by parsing the header (one source of truth);
+`nsa_struct_size` cross-checks every mirror against the compiled library at load time.  There is no
+fallback: if the library is missing the import of any op fails with the build command to run.
+"""
+import ctypes
+import os
+import re
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PKG_ROOT = os.path.dirname(_HERE)
+_HEADER = os.path.join(os.path.dirname(_PKG_ROOT), "include", "nsa_sm100.h")
+_LIB_PATH = os.path.join(_PKG_ROOT, "csrc", "libnsa_sm100.so")
+
+_SCALARS = {"int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "float": ctypes.c_float}
+
+structs = {}
+functions = []
+
+
+def _parse_header(text):
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    for m in re.finditer(r"typedef\s+struct\s+(\w+)\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
+        name, body = m.group(3), m.group(2)
+        fields = []
+        for decl in body.split(";"):
+            decl = " ".join(decl.split())
+            if not decl:
+                continue
+            is_ptr_type = False
+            base = decl
+            mm = re.match(r"^(const\s+)?(\w+)\s*(.*)$", decl)
+            base_t, rest = mm.group(2), mm.group(3)
+            for d in rest.split(","):
+                d = d.strip()
+                ptr = d.startswith("*")
+                fname = d.lstrip("* ").strip()
+                if ptr:
+                    ctype = ctypes.c_void_p
+                elif base_t in structs:
+                    ctype = structs[base_t]
+                else:
+                    ctype = _SCALARS[base_t]
+                fields.append((fname, ctype))
+        structs[name] = type(name, (ctypes.Structure,), {"_fields_": fields})
+    for m in re.finditer(r"^\s*(?:const\s+char\s*\*|int)\s+(nsa_\w+)\s*\(", text, flags=re.M):
+        functions.append(m.group(1))
+
+
+with open(_HEADER) as _f:
+    _parse_header(_f.read())
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python {os.path.join(_PKG_ROOT, 'build.py')}` "
+            "(nvcc, sm_100a).  flash_nsa has no CPU or PyTorch fallback.")
+    L = ctypes.CDLL(_LIB_PATH)
+    L.nsa_last_error.restype = ctypes.c_char_p
+    L.nsa_struct_size.argtypes = [ctypes.c_char_p]
+    for name, st in structs.items():
+        n = L.nsa_struct_size(name.encode())
+        if n != ctypes.sizeof(st):
+            raise ImportError(f"ABI mismatch for {name}: header mirror {ctypes.sizeof(st)} bytes, library {n} bytes")
+    for fn in functions:
+        if not hasattr(L, fn):
+            raise ImportError(f"{_LIB_PATH} does not export {fn}")
+    _lib = L
+    return L
+
+
+class NsaError(RuntimeError):
+    pass
+
+
+def call(fn_name, params, stream):
+    """Invoke an entry point `int fn(const Params*, void* stream)`; raise on a non-zero status."""
+    L = lib()
+    rc = getattr(L, fn_name)(ctypes.byref(params), ctypes.c_void_p(stream))
+    if rc != 0:
+        raise NsaError(f"{fn_name} failed ({rc}): {L.nsa_last_error().decode()}")

@@ -1,0 +1,103 @@
+"""Helpers shared by the op wrappers: parameter-struct filling and argument checks."""
+import torch
+
+from .. import _lib
+from ..utils import NSAHelper
+
+S = _lib.structs
+
+
+def stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def hyper(window=None):
+    h = S["NsaHyper"]()
+    h.kernel_size, h.stride, h.block_size = NSAHelper.kernel_size, NSAHelper.stride, NSAHelper.block_size
+    h.window = NSAHelper.window_size if window is None else window
+    h.top_n, h.num_init, h.num_local = NSAHelper.top_n, NSAHelper.num_init_blocks, NSAHelper.num_local_blocks
+    return h
+
+
+def is_cp(helper) -> bool:
+    return (getattr(helper, "cp_cu_seqlens", None) is not None and NSAHelper.is_context_parallel_enable
+            and getattr(helper, "world_size", 1) > 1)
+
+
+def seq_meta(helper, cp=None):
+    """NsaSeqMeta for the helper's current tables; pieces are the rank's shard pieces under context
+    parallelism and whole sequences otherwise."""
+    assert helper.x_cu_seqlens is not None, "call NSAHelper.init_cu_seqlens(cu_seqlens) first"
+    m = S["NsaSeqMeta"]()
+    cp = is_cp(helper) if cp is None else cp
+    n_seq = helper.x_cu_seqlens.numel() - 1
+    if cp:
+        m.piece_cu, m.piece_seq, m.piece_off = ptr(helper.cp_cu_seqlens), ptr(helper.cp_batch_idx), ptr(helper.cp_offset)
+        m.n_pieces, m.max_piece_len = helper.cp_batch_idx.numel(), helper.cp_maxlen
+    else:
+        m.piece_cu, m.piece_seq, m.piece_off = ptr(helper.x_cu_seqlens), 0, 0
+        m.n_pieces, m.max_piece_len = n_seq, helper.x_maxlen
+    m.x_cu, m.y_cu = ptr(helper.x_cu_seqlens), ptr(helper.y_cu_seqlens)
+    m.n_seq, m.x_maxlen, m.y_maxlen = n_seq, helper.x_maxlen, helper.y_maxlen
+    return m
+
+
+def local_rows(helper, cp=None) -> int:
+    cp = is_cp(helper) if cp is None else cp
+    return helper.cp_len if cp else helper.total_len
+
+
+def check_bf16_3d(name, t, last_contig=True):
+    assert t.is_cuda, f"{name} must be a CUDA tensor"
+    assert t.dtype == torch.bfloat16, f"{name} must be bfloat16 (got {t.dtype}); this build computes in bf16 only"
+    assert t.dim() == 3, f"{name} must be [t, h, d]"
+    assert t.stride(-1) == 1 and t.stride(1) == t.size(-1), f"{name}: heads and head_dim must be contiguous"
+
+
+def call(fn, params, ref_tensor):
+    _lib.call(fn, params, stream_ptr(ref_tensor))
+
+
+def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_major=False, dout=None, delta=None,
+                dq=None, dk=None, dv=None, topk=None, cp=None, need_y=False):
+    """Fill an NsaAttnParams.  `lse` (and `delta`) are [QH,T] when lse_is_head_major else [T,QH]."""
+    check_bf16_3d("q", q)
+    check_bf16_3d("k", k)
+    check_bf16_3d("v", v)
+    T, QH, D = q.shape
+    KH = k.size(1)
+    assert k.size(-1) == D and v.size(-1) == D, "this build needs qk_head_dim == v_head_dim"
+    assert v.size(1) == KH and v.size(0) == k.size(0) and QH % KH == 0
+    p = S["NsaAttnParams"]()
+    p.meta, p.hp = seq_meta(helper, cp), hyper()
+    p.q, p.k, p.v, p.o, p.lse = ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse)
+    p.dout, p.delta, p.dq, p.dk, p.dv, p.topk = ptr(dout), ptr(delta), ptr(dq), ptr(dk), ptr(dv), ptr(topk)
+    p.q_stride_t, p.k_stride_t, p.v_stride_t = q.stride(0), k.stride(0), v.stride(0)
+    for name, t in (("o", o), ("dout", dout), ("dq", dq)):
+        if t is not None:
+            assert t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: bf16, contiguous heads"
+    for name, t in (("dk", dk), ("dv", dv)):
+        if t is not None:
+            assert t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: fp32, contiguous heads"
+    p.o_stride_t = o.stride(0) if o is not None else 0
+    p.do_stride_t = dout.stride(0) if dout is not None else 0
+    p.dq_stride_t = dq.stride(0) if dq is not None else 0
+    p.dk_stride_t = dk.stride(0) if dk is not None else 0
+    p.dv_stride_t = dv.stride(0) if dv is not None else 0
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.is_contiguous()
+        if lse_is_head_major:
+            p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
+        else:
+            p.lse_stride_t, p.lse_stride_h = lse.stride(0), 1
+    if topk is not None:
+        assert topk.dtype == torch.int32 and topk.is_contiguous() and topk.size(0) == KH and topk.size(1) == T
+        p.hp.top_n = topk.size(-1)
+        p.topk_stride_h = topk.stride(0)
+    p.sm_scale = float(sm_scale)
+    p.QH, p.KH, p.D = QH, KH, D
+    return p

@@ -1,0 +1,74 @@
+"""Attention over the selected key blocks.  Python surface of flash_nsa/ops/select_attn.py."""
+import torch
+
+from ..utils import NSAHelper
+from ._common import attn_params, call, is_cp, ptr
+from .topk import get_bind_from_find
+
+
+def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
+    """q [t,qh,d], k/v [tokens,kh,d], topk [kh,t,top_n] -> (o, lse [t,qh] fp32 base 2)."""
+    T, QH, D = q.shape
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if o is None:
+        o = torch.empty(T, QH, v.size(-1), device=q.device, dtype=q.dtype)
+    lse = torch.empty(T, QH, device=q.device, dtype=torch.float32)
+    if T > 0:
+        call("nsa_slc_attn_fwd", attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, topk=topk), q)
+    return o, lse
+
+
+def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=None, fuse_dqdkdv=False,
+                 dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper):
+    """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
+    otherwise dq is new and dk/dv come back in k's dtype.  Deterministic: one CTA owns a key block."""
+    T, QH, D = q.shape
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if not (do.stride(-1) == 1 and do.stride(1) == do.size(-1)):
+        do = do.contiguous()
+    acc_dq = dq is not None
+    if dq is None:
+        dq = torch.empty_like(q)
+    own = dk is None
+    if own:
+        dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
+        dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
+    delta = torch.empty_like(lse)
+    if T > 0:
+        offsets, tokens = get_bind_from_find(topk, helper=helper)
+        p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=do, delta=delta, dq=dq, dk=dk, dv=dv, topk=topk)
+        p.k2q_offsets, p.k2q_tokens = ptr(offsets), ptr(tokens)
+        p.k2q_stride_h = tokens.stride(0)
+        p.n_blocks_total = offsets.size(1) - 1
+        p.accumulate_dq, p.accumulate_dkdv = int(acc_dq), 1
+        call("nsa_slc_attn_bwd", p, q)
+    if own:
+        dk, dv = dk.to(k.dtype), dv.to(v.dtype)
+    if async_dq:
+        return dq, dk, dv, (lambda: None)
+    return dq, dk, dv
+
+
+class _SlcAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, topk, sm_scale):
+        if sm_scale is None:
+            sm_scale = q.size(-1) ** -0.5
+        o, lse = slc_attn_fwd(q, k, v, topk, sm_scale)
+        ctx.save_for_backward(q, k, v, o, lse, topk)
+        ctx.sm_scale = sm_scale
+        ctx.helper = NSAHelper.get_bwd_helper()
+        return o
+
+    @staticmethod
+    def backward(ctx, do, *args):
+        q, k, v, o, lse, topk = ctx.saved_tensors
+        dq, dk, dv = slc_attn_bwd(q, k, v, topk, o, lse, do, sm_scale=ctx.sm_scale, helper=ctx.helper)
+        return dq, dk, dv, None, None
+
+
+def select_attn(q, k, v, topk, sm_scale=None):
+    """q [t,qh,d], k/v [t,kh,d], topk [kh,t,top_n] -> o [t,qh,d]"""
+    return _SlcAttention.apply(q, k, v, topk, sm_scale)

@@ -1,0 +1,78 @@
+"""Block-importance scores and top-n block selection, and the key-block -> queries index used by the
+selected-attention backward.  Python surface of flash_nsa/ops/topk.py."""
+import torch
+
+from ..utils import NSAHelper, cdiv
+from ._common import S, call, check_bf16_3d, hyper, is_cp, local_rows, ptr, seq_meta
+
+
+@torch.no_grad()
+def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True, ignore_index=None, fp32=False,
+                     maybe_efficient_version=False, scale_slc_p=True):
+    """q [t,qh,d], k = compressed keys [rows,kh,d], lse [qh,t] of the compressed branch ->
+    (topk [kh,t,top_n] int32, block scores or None).
+
+    Selection compares, per (kv head, token), the pooled block scores: in fp32 when `fp32`, otherwise
+    rounded to half after cubing (`scale_slc_p`, applied while the padded block count is <= 2048, as the
+    reference does) or without cubing.  Unused slots hold `ignore_index` (default: number of blocks of the
+    longest sequence).  Only kernel 32 / stride 16 / block 64 is implemented; `maybe_efficient_version`
+    is accepted for source compatibility (scores are never materialised unless `return_slc_prob`)."""
+    check_bf16_3d("q", q)
+    check_bf16_3d("k", k)
+    T, QH, D = q.shape
+    KH = k.size(1)
+    assert QH % KH == 0
+    assert NSAHelper.num_init_blocks >= 1 or True
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    helper = NSAHelper
+    num_slc_blocks = cdiv(helper.x_maxlen, NSAHelper.block_size)
+    pad_blocks = max(1 << max(num_slc_blocks - 1, 0).bit_length(), 8) if align else max(num_slc_blocks, 8)
+    assert ignore_index is None or ignore_index >= num_slc_blocks
+    ignore_index = num_slc_blocks if ignore_index is None else ignore_index
+    if fp32:
+        quant = 0
+    elif scale_slc_p and pad_blocks <= 2048:
+        quant = 2
+    else:
+        quant = 1
+    topk = torch.empty(KH, T, NSAHelper.top_n, dtype=torch.int32, device=q.device)
+    probs = None
+    if return_slc_prob:
+        probs = torch.zeros(KH, T, pad_blocks, device=q.device, dtype=torch.float32 if fp32 else torch.float16)
+    if T == 0:
+        return topk, probs
+    p = S["NsaTopkParams"]()
+    p.meta, p.hp = seq_meta(helper), hyper()
+    p.q, p.ck, p.lse, p.topk, p.probs = ptr(q), ptr(k), ptr(lse), ptr(topk), ptr(probs)
+    p.q_stride_t, p.ck_stride_t = q.stride(0), k.stride(0)
+    assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (QH, T)
+    p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
+    p.probs_stride_t = pad_blocks if probs is not None else 0
+    p.sm_scale = float(sm_scale)
+    p.QH, p.KH, p.D = QH, KH, D
+    p.ignore_index, p.quant = ignore_index, quant
+    call("nsa_slc_topk", p, q)
+    return topk, probs
+
+
+@torch.no_grad()
+def get_bind_from_find(topk, helper=NSAHelper):
+    """topk [kh,t,top_n] -> (offsets [kh, blocks+1], tokens [kh, t*top_n]): for every (kv head, key block) the
+    ascending list of local query rows that selected it, `tokens[h, offsets[h,b]:offsets[h,b+1]]`.
+    Block rows are laid out per piece (sequence, or shard piece under context parallelism) with
+    k_cu_seqlens / cp_k_cu_seqlens."""
+    KH, T, top_n = topk.shape
+    cp = is_cp(helper)
+    blk_cu = helper.cp_k_cu_seqlens if cp else helper.k_cu_seqlens
+    n_blocks = helper.cp_k_len if cp else helper.k_len
+    offsets = torch.empty(KH, n_blocks + 1, dtype=torch.int32, device=topk.device)
+    tokens = torch.empty(KH, max(T * top_n, 1), dtype=torch.int32, device=topk.device)
+    cursor = torch.empty(KH, max(n_blocks, 1), dtype=torch.int32, device=topk.device)
+    p = S["NsaK2qParams"]()
+    p.meta, p.hp = seq_meta(helper), hyper()
+    p.hp.top_n = top_n
+    p.topk, p.offsets, p.tokens, p.cursor, p.blk_cu = ptr(topk), ptr(offsets), ptr(tokens), ptr(cursor), ptr(blk_cu)
+    p.Tq, p.KH, p.n_blocks_total = T, KH, n_blocks
+    call("nsa_k2q_index", p, topk)
+    return offsets, tokens

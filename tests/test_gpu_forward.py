@@ -1,0 +1,200 @@
+"""Forward parity of the CUDA kernels (through the flash_nsa Python surface -> C ABI) against the CPU oracle
+and against the golden vectors produced by the reference's torch code.
+
+Tolerances (bf16 compute, fp32 oracle on the same bf16-representable inputs):
+  attention outputs   max abs error <= 2e-2
+  log-sum-exp         max abs error <= 2e-2 (base 2)
+  pooled rows         <= 1 bf16 ulp of the value (8e-3 relative)
+  top-n               identical sets; a differing row is accepted only if the swapped blocks' oracle scores
+                      differ by <= 1e-3 of the row maximum (fp32 mode) -- near-ties can flip with the MMA
+                      accumulation order -- and the differing-row rate must stay below 2e-3
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+from helpers import load_golden, golden_params, sorted_valid, topk_mismatch_report
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2
+
+
+def _mk(lens, QH, KH, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    T = sum(lens)
+    cu = [0]
+    for L in lens:
+        cu.append(cu[-1] + L)
+    q = torch.randn(T, QH, D, generator=g).bfloat16()
+    k = torch.randn(T, KH, D, generator=g).bfloat16()
+    v = torch.randn(T, KH, D, generator=g).bfloat16()
+    w = torch.randn(T, QH, 3, generator=g).bfloat16()
+    return q, k, v, w, cu
+
+
+def _setup(cu, **hp):
+    import flash_nsa
+    from flash_nsa import NSAHelper
+    NSAHelper.reset_context_parallel()
+    NSAHelper.set_hyperparameters(**hp)
+    NSAHelper.init_cu_seqlens(torch.tensor(cu, dtype=torch.int32, device="cuda"))
+    return flash_nsa
+
+
+CASES = [
+    ([320], 4, 1, 64),
+    ([17, 32, 47, 48, 130, 1, 700], 4, 1, 64),
+    ([200, 333], 16, 1, 128),
+    ([1100], 8, 2, 64),
+    ([64, 128, 65], 32, 2, 128),
+    ([96], 6, 2, 64),          # G = 3: rows of a tile do not divide evenly
+]
+
+
+def _err(a, b):
+    return (a.float().cpu() - b.float()).abs().max().item()
+
+
+@pytest.mark.parametrize("lens,QH,KH,D", CASES)
+def test_branches_forward(lens, QH, KH, D):
+    q, k, v, w, cu = _mk(lens, QH, KH, D, seed=sum(lens) + QH)
+    fn = _setup(cu)
+    from flash_nsa.ops import (mean_pooling_fwd, cmp_attn_fwd, slc_topk_indices, slc_attn_fwd, swa_fwd, combine_fwd)
+    ref_o, parts = O.nsa_forward(q.float(), k.float(), v.float(), w.float(), cu, return_parts=True)
+    qd, kd, vd, wd = q.cuda(), k.cuda(), v.cuda(), w.cuda()
+
+    ck, cv = mean_pooling_fwd(kd), mean_pooling_fwd(vd)
+    assert ck.shape == parts["ck"].shape
+    assert _err(ck, parts["ck"]) <= 8e-3 * max(1.0, parts["ck"].abs().max().item())
+    # the branches are checked against the oracle fed with the SAME (bf16-rounded) compressed rows
+    ckf, cvf = ck.float().cpu(), cv.float().cpu()
+    cmp_ref, lse_ref = O.cmp_attn(q.float(), ckf, cvf, cu)
+    cmp_o, cmp_lse = cmp_attn_fwd(qd, ck, cv)
+    assert _err(cmp_o, cmp_ref) <= TOL
+    assert _err(cmp_lse, lse_ref) <= TOL
+
+    swa_o, swa_lse = swa_fwd(qd, kd, vd)
+    assert _err(swa_o, parts["swa_o"]) <= TOL
+    assert _err(swa_lse, parts["swa_lse"]) <= TOL
+
+    # selection: fp32 mode against the oracle's fp32 scores (computed from the GPU's own lse inputs)
+    sc = O.slc_scores(q.float(), ckf, cmp_lse.float().cpu(), cu)
+    ref_topk = O.topk_select(sc, cu)
+    topk, _ = slc_topk_indices(qd, ck, cmp_lse, fp32=True, maybe_efficient_version=True)
+    ign = O.cdiv(max(lens), 64)
+    n_diff, n_bad, n_rows = topk_mismatch_report(topk.cpu(), ref_topk, sc, cu, ign, ign, rel_tol=1e-3)
+    assert n_bad == 0, (n_diff, n_bad)
+    assert n_diff <= max(1, int(2e-3 * n_rows))
+
+    # selected attention on the ORACLE's lists (so the comparison does not depend on near-ties)
+    slc_ref, slc_lse_ref = O.slc_attn(q.float(), k.float(), v.float(), ref_topk, cu)
+    slc_o, slc_lse = slc_attn_fwd(qd, kd, vd, ref_topk.cuda())
+    assert _err(slc_o, slc_ref) <= TOL
+    assert _err(slc_lse, slc_lse_ref) <= TOL
+
+    out = combine_fwd(cmp_o, slc_o, swa_o, wd)
+    ref = O.combine(cmp_o.float().cpu(), slc_o.float().cpu(), swa_o.float().cpu(), w.float())
+    assert _err(out, ref) <= TOL
+
+
+def test_topk_quantised_modes():
+    """Default mode (half of score^3) and plain-half mode against the oracle's restatement of the same rounding."""
+    lens = [2048, 1500]
+    q, k, v, w, cu = _mk(lens, 8, 2, 64, seed=3)
+    _setup(cu)
+    from flash_nsa.ops import mean_pooling_fwd, cmp_attn_fwd, slc_topk_indices
+    qd, kd = q.cuda(), k.cuda()
+    ck = mean_pooling_fwd(kd)
+    cmp_o, cmp_lse = cmp_attn_fwd(qd, ck, mean_pooling_fwd(v.cuda()))
+    ign = O.cdiv(max(lens), 64)
+    for kwargs, quant in ((dict(scale_slc_p=True), "fp16_cubed"), (dict(scale_slc_p=False), "fp16")):
+        sc = O.slc_scores(q.float(), ck.float().cpu(), cmp_lse.float().cpu(), cu, quant=quant)
+        ref_topk = O.topk_select(sc, cu)
+        topk, probs = slc_topk_indices(qd, ck, cmp_lse, maybe_efficient_version=True, return_slc_prob=True, **kwargs)
+        # rounding to half makes exact ties common; a swap is accepted if the rounded oracle scores are within 2 half ulps
+        n_diff, n_bad, n_rows = topk_mismatch_report(topk.cpu(), ref_topk, sc, cu, ign, ign, rel_tol=2e-3)
+        assert n_bad == 0, (quant, n_diff, n_bad)
+        assert n_diff <= int(2e-2 * n_rows), (quant, n_diff, n_rows)
+        # returned scores: same rounding as the oracle up to one half ulp on 99.9% of entries
+        pr = probs.float().cpu()
+        for b, L in enumerate(lens):
+            ref = sc[b]
+            got = pr[:, cu[b]:cu[b + 1], :ref.shape[-1]]
+            # block 0 is excluded: its score is irrelevant (forced) and the "row before" term differs by design
+            close = (got[..., 1:] - ref[..., 1:]).abs() <= 2e-3 * ref[..., 1:].abs() + 1e-7
+            assert close.float().mean().item() > 0.999
+
+
+def test_topk_order_and_ignore():
+    """Slot layout of a row: forced blocks first, unused slots hold ignore_index."""
+    lens = [300]
+    q, k, v, w, cu = _mk(lens, 4, 1, 64, seed=9)
+    _setup(cu)
+    from flash_nsa.ops import mean_pooling_fwd, cmp_attn_fwd, slc_topk_indices
+    ck = mean_pooling_fwd(k.cuda())
+    _, lse = cmp_attn_fwd(q.cuda(), ck, mean_pooling_fwd(v.cuda()))
+    topk, _ = slc_topk_indices(q.cuda(), ck, lse, maybe_efficient_version=True, ignore_index=77)
+    t = topk.cpu()[0]
+    assert t[10].tolist() == [0] + [77] * 15
+    assert t[70].tolist() == [0, 1] + [77] * 14
+    assert t[130].tolist()[:3] == [0, 2, 1] and t[130].tolist()[3:] == [77] * 13
+    assert sorted(t[299].tolist()[:5]) == [0, 1, 2, 3, 4] and t[299].tolist()[1:3] == [4, 3]
+
+
+@pytest.mark.parametrize("name", ["seq320_g4_d64", "seq200_g16_d128", "seq1100_g2_d64", "c0_2048_g4_d64"])
+def test_against_reference_golden(name):
+    g = load_golden(name)
+    p = golden_params(g)
+    cu = [0, p["T"]]
+    _setup(cu)
+    step = int(g["row_step"])
+    from flash_nsa.ops import mean_pooling_fwd, cmp_attn_fwd, slc_topk_indices, slc_attn_fwd
+    q, k, v = g["q"].cuda(), g["k"].cuda(), g["v"].cuda()
+    ck, cv = mean_pooling_fwd(k), mean_pooling_fwd(v)
+    assert _err(ck, torch.from_numpy(g["ck"])) <= 8e-3 * max(1.0, float(np.abs(g["ck"]).max()))
+    cmp_o, lse = cmp_attn_fwd(q, ck, cv)
+    assert _err(cmp_o[::step], torch.from_numpy(g["cmp_o"])) <= TOL
+    topk, _ = slc_topk_indices(q, ck, lse, fp32=True, maybe_efficient_version=True)
+    ref_sorted = torch.sort(torch.from_numpy(g["topk_sorted"].astype(np.int64)), -1)[0]
+    ours = sorted_valid(topk.cpu(), O.cdiv(p["T"], 64))
+    diff_rows = (ours != ref_sorted).any(-1).float().mean().item()
+    assert diff_rows <= 5e-3, diff_rows
+    # selected attention on the reference's own lists
+    ref_topk = torch.from_numpy(g["topk_sorted"].astype(np.int32))
+    ref_topk = torch.where(ref_topk < 0, torch.full_like(ref_topk, O.cdiv(p["T"], 64)), ref_topk)
+    slc_o, _ = slc_attn_fwd(q, k, v, ref_topk.cuda().contiguous())
+    assert _err(slc_o[::step], torch.from_numpy(g["slc_o"])) <= TOL
+
+
+def test_hbm_ops_forward():
+    lens = [100, 31, 64]
+    q, k, v, w, cu = _mk(lens, 4, 2, 64, seed=21)
+    _setup(cu)
+    from flash_nsa.ops import construct_block_fwd, swiglu_fwd, sigmoid_mul_fwd, reorder
+    blk = construct_block_fwd(k.cuda())
+    ref = O.construct_block(k.float(), cu)
+    assert blk.shape == ref.shape and _err(blk, ref) == 0.0
+    g = load_golden("misc")
+    h = g["h"].cuda()
+    assert _err(swiglu_fwd(h), torch.from_numpy(g["swiglu"])) <= 2e-2
+    assert _err(sigmoid_mul_fwd(h), torch.from_numpy(g["sigmoid_mul"])) <= 2e-2
+    x = g["x"].cuda()
+    assert _err(reorder(x, 4, "shuffle"), torch.from_numpy(g["shuffle4"])) == 0.0
+    assert _err(reorder(x, 4, "unshuffle"), torch.from_numpy(g["unshuffle4"])) == 0.0
+    assert _err(reorder(x, 2, "shuffle"), torch.from_numpy(g["shuffle2"])) == 0.0
+
+
+def test_hf_core_forward_end_to_end():
+    lens = [700, 260]
+    q, k, v, w, cu = _mk(lens, 8, 2, 64, seed=33)
+    fn = _setup(cu)
+    cfg = fn.NSAConfig(head_dim=64, num_heads=8, num_kv_heads=2)
+    core = fn.HFNSACore(cfg).cuda()
+    o = core(q.cuda(), k.cuda(), v.cuda(), w.cuda(), torch.tensor(cu, dtype=torch.int32, device="cuda"))
+    ref = O.nsa_forward(q.float(), k.float(), v.float(), w.float(), cu, quant="fp16_cubed")
+    # a flipped near-tie changes one of 16 blocks of one row: judge the bulk and bound the rest
+    err = (o.float().cpu() - ref).abs()
+    assert err.flatten().kthvalue(int(0.999 * err.numel())).values.item() <= TOL
+    assert torch.isfinite(o).all()
