@@ -117,11 +117,12 @@ typedef struct NsaAttnParams {
   const void* dout;  /* bwd: [Tq,QH,D] bf16                                                               */
   float* delta;      /* bwd scratch, same addressing as lse: rowsum(o*dout), written by the call          */
   void* dq;          /* bwd: [Tq,QH,D] bf16                                                               */
-  float* dk;         /* bwd: fp32, same rows as k                                                         */
-  float* dv;         /* bwd: fp32, same rows as v                                                         */
+  float* dk;         /* bwd: fp32, same rows as k; results are ADDED (atomics): zero-fill for a fresh result */
+  float* dv;         /* bwd: fp32, same rows as v; idem                                                   */
   const int32_t* topk; /* selected branch: [KH,Tq,top_n] int32                                            */
   const int32_t* k2q_offsets; /* selected bwd: [KH, n_blocks_total+1] CSR offsets from nsa_k2q_index      */
-  const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows, ascending inside a block  */
+  const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows of each block's list         */
+  const int32_t* k2q_blk_cu;  /* selected bwd: [n_pieces+1] first table row of each piece (as in NsaK2qParams) */
   int64_t q_stride_t, k_stride_t, v_stride_t, o_stride_t, do_stride_t, dq_stride_t, dk_stride_t, dv_stride_t;
   int64_t lse_stride_t, lse_stride_h;
   int64_t topk_stride_h; /* elements between kv heads in topk (= Tq*top_n when contiguous)                */
@@ -129,8 +130,7 @@ typedef struct NsaAttnParams {
   float sm_scale;
   int32_t QH, KH, D;
   int32_t accumulate_dq;   /* bwd: 1 = dq += result, 0 = dq = result                                      */
-  int32_t accumulate_dkdv; /* bwd: 1 = dk/dv += result, 0 = overwrite (compressed branch always adds:
-                              the caller zero-fills)                                                       */
+  int32_t n_q_rows;        /* bwd: total number of local query rows (= piece_cu[n_pieces])                */
   int32_t n_blocks_total;  /* selected bwd: rows of the k2q table per kv head                             */
   int32_t reserved0;
 } NsaAttnParams;

@@ -21,6 +21,13 @@ int check_launch(const char* what);
     }                                           \
   } while (0)
 
+// launch description of the shared dK/dV kernel (dense_bwd.cu), also used by the selected-branch backward
+struct DkdvLaunch {
+  int q_chunk;            // compressed branch: query tokens per CTA slice
+  int splits;             // selected branch: CTAs per key block
+  const int32_t* blk_cu;  // selected branch: first table row of each piece
+};
+
 // ------------------------------------------------------------------ piece lookup
 // A "piece" is a run of local query rows that belongs to one sequence.  Without context parallelism
 // a piece is a whole sequence (offset 0); with it, a piece is the part of a sequence that lies in one

@@ -119,9 +119,9 @@ class NSAFunction(torch.autograd.Function):
 
         dcmp_o, dslc_o, dswa_o, dcombine_weight = combine_bwd(cmp_o, slc_o, swa_o, combine_weight, do)
         dq = torch.empty_like(q)
-        dk = torch.empty(k.shape, device=k.device, dtype=torch.float32)
-        dv = torch.empty(v.shape, device=v.device, dtype=torch.float32)
-        # sliding window writes dq/dk/dv, the other branches add into them
+        dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
+        dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
+        # sliding window writes dq, the other branches add into it; every branch adds into the fp32 dk/dv
         _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper)
         slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper)
         _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper)
@@ -131,13 +131,13 @@ class NSAFunction(torch.autograd.Function):
 
 
 def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper):
-    """Sliding-window backward that OVERWRITES dq (bf16) and dk/dv (fp32)."""
+    """Sliding-window backward that OVERWRITES dq (bf16) and adds into dk/dv (fp32)."""
     from ..ops._common import attn_params, call
     if not (dout.stride(-1) == 1 and dout.stride(1) == dout.size(-1)):
         dout = dout.contiguous()
     delta = torch.empty_like(lse)
     p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=dout, delta=delta, dq=dq, dk=dk, dv=dv)
-    p.accumulate_dq, p.accumulate_dkdv = 0, 0
+    p.accumulate_dq = 0
     if q.size(0) > 0:
         call("nsa_swa_bwd", p, q)
 
@@ -245,7 +245,7 @@ class CPNSAFunction(torch.autograd.Function):
             dcmp_o, dslc_o, dswa_o, _ = combine_bwd(cmp_o, slc_o, swa_o, w_i, do_i,
                                                      dw=dcombine_weight[:, h0 * G:(h0 + stride) * G])
             dk, dv = comm.grad_buffers()  # zero-filled fp32 [t*W, stride, d]
-            _swa_bwd_into_acc(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper)
+            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper)
             slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper)
             _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper)
             _, fk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper, async_dw=True)
@@ -269,18 +269,6 @@ class CPNSAFunction(torch.autograd.Function):
             chunk_dk[:, h0:h0 + stride].copy_(dk_local)
             chunk_dv[:, h0:h0 + stride].copy_(dv_local)
         return chunk_dq, chunk_dk, chunk_dv, dcombine_weight, dwk, dwv, None
-
-
-def _swa_bwd_into_acc(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper):
-    """Sliding-window backward that overwrites dq and ADDS into the (zero-filled, global) dk/dv."""
-    from ..ops._common import attn_params, call
-    if not (dout.stride(-1) == 1 and dout.stride(1) == dout.size(-1)):
-        dout = dout.contiguous()
-    delta = torch.empty_like(lse)
-    p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=dout, delta=delta, dq=dq, dk=dk, dv=dv)
-    p.accumulate_dq, p.accumulate_dkdv = 0, 1
-    if q.size(0) > 0:
-        call("nsa_swa_bwd", p, q)
 
 
 def flash_nsa_varlen_func(q, k, v, combine_weight, cmp_k_weight, cmp_v_weight, sm_scale=None):

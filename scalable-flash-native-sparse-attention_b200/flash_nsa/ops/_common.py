@@ -100,4 +100,5 @@ def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_majo
         p.topk_stride_h = topk.stride(0)
     p.sm_scale = float(sm_scale)
     p.QH, p.KH, p.D = QH, KH, D
+    p.n_q_rows = T
     return p

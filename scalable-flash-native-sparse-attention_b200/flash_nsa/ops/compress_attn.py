@@ -37,7 +37,7 @@ def cmp_attn_bwd(q, k, v, o, lse, do, dq=None, sm_scale=None, fuse_dqdkdv=False,
     if T > 0 and k.size(0) > 0:
         p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, lse_is_head_major=True, dout=do, delta=delta, dq=dq,
                         dk=dk, dv=dv, need_y=True)
-        p.accumulate_dq, p.accumulate_dkdv = int(acc_dq), 1
+        p.accumulate_dq = int(acc_dq)
         call("nsa_cmp_attn_bwd", p, q)
     elif not acc_dq:
         dq.zero_()

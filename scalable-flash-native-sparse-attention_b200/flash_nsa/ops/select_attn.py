@@ -42,7 +42,8 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
         p.k2q_offsets, p.k2q_tokens = ptr(offsets), ptr(tokens)
         p.k2q_stride_h = tokens.stride(0)
         p.n_blocks_total = offsets.size(1) - 1
-        p.accumulate_dq, p.accumulate_dkdv = int(acc_dq), 1
+        p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
+        p.accumulate_dq = int(acc_dq)
         call("nsa_slc_attn_bwd", p, q)
     if own:
         dk, dv = dk.to(k.dtype), dv.to(v.dtype)

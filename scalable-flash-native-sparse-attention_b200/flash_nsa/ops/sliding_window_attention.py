@@ -33,11 +33,11 @@ def swa_bwd(q, k, v, out, lse, dout, sm_scale=None, helper=NSAHelper, dq=None, d
         dq = torch.empty_like(q)
     own = dk is None
     if own:
-        dk = torch.empty(k.shape, device=k.device, dtype=torch.float32)
-        dv = torch.empty(v.shape, device=v.device, dtype=torch.float32)
+        dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
+        dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
     delta = torch.empty_like(lse)
     p = attn_params(q, k, v, helper, sm_scale, o=out, lse=lse, dout=dout, delta=delta, dq=dq, dk=dk, dv=dv)
-    p.accumulate_dq, p.accumulate_dkdv = int(acc_dq), int(not own)
+    p.accumulate_dq = int(acc_dq)
     if T > 0:
         call("nsa_swa_bwd", p, q)
     if own:
