@@ -132,7 +132,8 @@ typedef struct NsaAttnParams {
   int32_t accumulate_dq;   /* bwd: 1 = dq += result, 0 = dq = result                                      */
   int32_t n_q_rows;        /* bwd: total number of local query rows (= piece_cu[n_pieces])                */
   int32_t n_blocks_total;  /* selected bwd: rows of the k2q table per kv head                             */
-  int32_t reserved0;
+  int32_t phases;          /* bwd: 0 = run every kernel of the call; otherwise a mask, bit 0 = delta, bit 1 = dK/dV,
+                              bit 2 = dQ (lets a profiler time the kernels of one call separately)         */
 } NsaAttnParams;
 
 /* compressed attention: replaces cmp_attn_fwd / cmp_attn_bwd, flash_nsa/ops/compress_attn.py:532-741.

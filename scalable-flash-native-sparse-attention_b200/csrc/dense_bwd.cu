@@ -467,14 +467,17 @@ extern "C" int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream) {
   if ((rc = check_bwd(p, "cmp_attn_bwd"))) return rc;
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
-  if (p->meta.y_maxlen > 0) {
+  const int ph = p->phases ? p->phases : 7;
+  if (ph & 1)
+    launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
+  if ((ph & 2) && p->meta.y_maxlen > 0) {
     DkdvLaunch L{2048, 1, nullptr};
     dim3 grid((p->meta.y_maxlen + 63) / 64, (p->meta.max_piece_len + L.q_chunk - 1) / L.q_chunk, p->meta.n_pieces * p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_CMP>(p, st, "cmp_attn_bwd(dkdv)", grid, L)
                        : launch_dkdv<64, MODE_CMP>(p, st, "cmp_attn_bwd(dkdv)", grid, L);
     if (rc) return rc;
   }
+  if (!(ph & 4)) return check_launch("cmp_attn_bwd");
   return (p->D == 128) ? launch_dq<128, MODE_CMP>(p, st, "cmp_attn_bwd(dq)") : launch_dq<64, MODE_CMP>(p, st, "cmp_attn_bwd(dq)");
 }
 
@@ -484,10 +487,15 @@ extern "C" int nsa_swa_bwd(const NsaAttnParams* p, void* stream) {
   if ((rc = check_bwd(p, "swa_bwd"))) return rc;
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
-  DkdvLaunch L{0, 1, nullptr};
-  dim3 grid((p->meta.max_piece_len + p->hp.window + 63) / 64 + 1, 1, p->meta.n_pieces * p->KH);
-  rc = (p->D == 128) ? launch_dkdv<128, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L) : launch_dkdv<64, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L);
-  if (rc) return rc;
+  const int ph = p->phases ? p->phases : 7;
+  if (ph & 1)
+    launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
+  if (ph & 2) {
+    DkdvLaunch L{0, 1, nullptr};
+    dim3 grid((p->meta.max_piece_len + p->hp.window + 63) / 64 + 1, 1, p->meta.n_pieces * p->KH);
+    rc = (p->D == 128) ? launch_dkdv<128, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L) : launch_dkdv<64, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L);
+    if (rc) return rc;
+  }
+  if (!(ph & 4)) return check_launch("swa_bwd");
   return (p->D == 128) ? launch_dq<128, MODE_SWA>(p, st, "swa_bwd(dq)") : launch_dq<64, MODE_SWA>(p, st, "swa_bwd(dq)");
 }

@@ -177,14 +177,17 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   NSA_REQUIRE(p->dk_stride_t % 2 == 0 && p->dv_stride_t % 2 == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: dk/dv row strides must be even");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
-  if (p->n_blocks_total > 0) {
+  const int ph = p->phases ? p->phases : 7;
+  if (ph & 1)
+    launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
+  if ((ph & 2) && p->n_blocks_total > 0) {
     DkdvLaunch L{0, 8, p->k2q_blk_cu};
     dim3 grid(p->n_blocks_total, L.splits, p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L)
                        : launch_dkdv<64, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L);
     if (rc) return rc;
   }
+  if (!(ph & 4)) return check_launch("slc_attn_bwd");
   dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
   if (p->D == 128) slc_dq_kernel<128><<<grid, 128, 0, st>>>(*p);
   else slc_dq_kernel<64><<<grid, 128, 0, st>>>(*p);

@@ -80,9 +80,18 @@ class NsaError(RuntimeError):
     pass
 
 
+# kernels launched by one call of each entry point (used by the benchmark's launch counter)
+KERNELS_PER_CALL = {
+    "nsa_cmp_attn_bwd": 3, "nsa_swa_bwd": 3, "nsa_slc_attn_bwd": 3, "nsa_k2q_index": 4,
+}
+launch_count = 0
+
+
 def call(fn_name, params, stream):
     """Invoke an entry point `int fn(const Params*, void* stream)`; raise on a non-zero status."""
+    global launch_count
     L = lib()
+    launch_count += KERNELS_PER_CALL.get(fn_name, 1)
     rc = getattr(L, fn_name)(ctypes.byref(params), ctypes.c_void_p(stream))
     if rc != 0:
         raise NsaError(f"{fn_name} failed ({rc}): {L.nsa_last_error().decode()}")
