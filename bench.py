@@ -144,6 +144,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tokens-per-gpu", type=int, default=0)
     ap.add_argument("--no-kernel-breakdown", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -235,15 +237,16 @@ def main():
         for n, gname in zip(("q", "k", "v", "w"), grads):
             out_host[n].copy_(gname, non_blocking=True)
 
-    e2e_step()
+    n_e2e = 0 if args.no_e2e else max(2, min(args.steps, 3))
+    if n_e2e:
+        e2e_step()
     sync_all()
     e0.record()
-    n_e2e = max(2, min(args.steps, 3))
     for _ in range(n_e2e):
         e2e_step()
     e1.record()
     sync_all()
-    ms_e2e = e0.elapsed_time(e1) / n_e2e
+    ms_e2e = e0.elapsed_time(e1) / max(n_e2e, 1) if n_e2e else float("nan")
     if world > 1:
         tt = torch.tensor([ms_e2e], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -269,7 +272,7 @@ def main():
     value = T_total / (ms * 1e-3)
     fm_total = flops_model([T_total])
     alg = sum(fm_total[n] for n in ("cmp_fwd", "topk", "slc_fwd", "swa_fwd", "cmp_bwd", "slc_bwd", "swa_bwd"))
-    cpu = cpu_reference(3, 1) if world == 1 else None
+    cpu = cpu_reference(3, 1) if (world == 1 and not args.no_cpu_baseline) else None
     line = {
         "metric": "nsa_fwd_bwd_throughput", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
