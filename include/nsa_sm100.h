@@ -185,6 +185,15 @@ typedef struct NsaK2qParams {
 /* replaces get_bind_from_find, flash_nsa/ops/topk.py:889-945: for every (kv head, key block) the list of local
  * query rows that selected it, as CSR (counts -> exclusive scan -> stable fill) instead of a dense table.  */
 int nsa_k2q_index(const NsaK2qParams* p, void* stream);
+/* No counterpart in the reference.  Same result as nsa_k2q_index, but the fill cursors live in a 1 MiB array inside
+ * the library image instead of `cursor` (which is ignored), so the call needs no scratch allocation at all.
+ * For hosts that cannot allocate at the point of the call: an inference server that gave all free device memory to its
+ * KV-cache pool at start-up, or code between a framework's caching allocator and a region where cudaMalloc is not
+ * allowed.  Limit: KH * n_blocks_total <= 262144 (e.g. 4 kv heads and 4 M tokens), larger sizes are refused with
+ * NSA_ERR_UNSUPPORTED_SHAPE.  The first call on each device looks up the array's device address (make that call
+ * outside any stream capture).  All calls on a device share the array: the cursors are cleared at the start of every
+ * call, and two calls whose kernels overlap on the GPU (different streams) corrupt each other.                  */
+int nsa_k2q_index_static(const NsaK2qParams* p, void* stream);
 
 /* ---- gated combine ---------------------------------------------------------------------------------- */
 typedef struct NsaCombineParams {

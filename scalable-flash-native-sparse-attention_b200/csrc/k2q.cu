@@ -3,9 +3,15 @@
 // count (histogram) -> exclusive scan -> fill.  Memory is O(T*top_n) instead of a dense [KH, blocks, T] table.
 // Block rows are laid out piece by piece: row = blk_cu[piece] + block index inside the sequence.
 // The order of the rows inside one list is not fixed (the fill uses an atomic cursor).
+#include <mutex>
 #include "nsa_common.cuh"
 
 namespace nsa {
+
+// Fill cursors for nsa_k2q_index_static: part of the library image, so every GPU that loads the library carries
+// these 1 MiB until the process exits.  Shared by all calls on a device.
+constexpr int kStaticCursorEntries = 262144;
+static __device__ __align__(256) int32_t g_static_cursor[kStaticCursorEntries];
 
 __device__ __forceinline__ int find_piece(const int32_t* cu, int n, int row) {
   int lo = 0, hi = n;  // largest b with cu[b] <= row
@@ -95,11 +101,56 @@ __global__ void k2q_fill_kernel(NsaK2qParams p) {
 
 using namespace nsa;
 
+static int k2q_launch(const NsaK2qParams* p, cudaStream_t st);
+
 extern "C" int nsa_k2q_index(const NsaK2qParams* p, void* stream) {
   NSA_REQUIRE(p && p->topk && p->offsets && p->tokens && p->cursor && p->blk_cu && p->meta.piece_cu, NSA_ERR_BAD_ARG,
               "k2q_index: null pointer");
   NSA_REQUIRE(p->KH > 0 && p->n_blocks_total >= 0 && p->hp.top_n > 0 && p->hp.block_size > 0, NSA_ERR_BAD_ARG, "k2q_index: bad sizes");
-  cudaStream_t st = (cudaStream_t)stream;
+  return k2q_launch(p, (cudaStream_t)stream);
+}
+
+// Device address of g_static_cursor on the CURRENT device, looked up once per device.  In host code the array's
+// name is only a handle for the runtime, never a pointer a kernel may dereference.
+static int static_cursor_ptr(int32_t** out) {
+  static std::mutex mu;
+  static int32_t* ptrs[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("k2q_index_static: cudaGetDevice failed or device ordinal %d out of range", dev);
+    return NSA_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_static_cursor);
+    if (e != cudaSuccess || !sym) {
+      set_error("k2q_index_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return NSA_ERR_CUDA;
+    }
+    ptrs[dev] = static_cast<int32_t*>(sym);
+  }
+  *out = ptrs[dev];
+  return NSA_OK;
+}
+
+extern "C" int nsa_k2q_index_static(const NsaK2qParams* p, void* stream) {
+  NSA_REQUIRE(p && p->topk && p->offsets && p->tokens && p->blk_cu && p->meta.piece_cu, NSA_ERR_BAD_ARG,
+              "k2q_index_static: null pointer");
+  NSA_REQUIRE(p->KH > 0 && p->n_blocks_total >= 0 && p->hp.top_n > 0 && p->hp.block_size > 0, NSA_ERR_BAD_ARG,
+              "k2q_index_static: bad sizes");
+  const int64_t need = (int64_t)p->KH * p->n_blocks_total;
+  NSA_REQUIRE(need <= kStaticCursorEntries, NSA_ERR_UNSUPPORTED_SHAPE,
+              "k2q_index_static: KH * n_blocks_total = %lld exceeds the built-in scratch of %d entries; use nsa_k2q_index "
+              "with caller-provided scratch", (long long)need, kStaticCursorEntries);
+  NsaK2qParams q = *p;
+  int rc = static_cursor_ptr(&q.cursor);
+  if (rc) return rc;
+  return k2q_launch(&q, (cudaStream_t)stream);
+}
+
+static int k2q_launch(const NsaK2qParams* p, cudaStream_t st) {
   int64_t nz = (int64_t)p->KH * (p->n_blocks_total + 1);
   k2q_zero_kernel<<<(unsigned)((nz + 255) / 256), 256, 0, st>>>(*p);
   int64_t n = p->Tq * p->hp.top_n;

@@ -76,3 +76,26 @@ def get_bind_from_find(topk, helper=NSAHelper):
     p.Tq, p.KH, p.n_blocks_total = T, KH, n_blocks
     call("nsa_k2q_index", p, topk)
     return offsets, tokens
+
+
+@torch.no_grad()
+def k2q_index_into(topk, offsets, tokens, helper=NSAHelper):
+    """Builds the same index as `get_bind_from_find`, but into tensors the caller already owns and without any
+    scratch allocation: the fill cursors live inside the kernel library.  Meant for callers that must not allocate
+    device memory where they call this (a server whose memory pool already owns the whole GPU, a no-allocation
+    region of a runtime).  `offsets` is int32 [kh, blocks+1], `tokens` int32 [kh, >= t*top_n]; kh * blocks must not
+    exceed 262144.  Calls on one GPU share the library's scratch, so do not run two of them concurrently on
+    different streams; issue the first call on a device outside stream capture."""
+    KH, T, top_n = topk.shape
+    cp = is_cp(helper)
+    blk_cu = helper.cp_k_cu_seqlens if cp else helper.k_cu_seqlens
+    n_blocks = helper.cp_k_len if cp else helper.k_len
+    assert offsets.dtype == torch.int32 and tuple(offsets.shape) == (KH, n_blocks + 1) and offsets.is_contiguous()
+    assert tokens.dtype == torch.int32 and tokens.size(0) == KH and tokens.size(1) == T * top_n and tokens.is_contiguous()
+    p = S["NsaK2qParams"]()
+    p.meta, p.hp = seq_meta(helper), hyper()
+    p.hp.top_n = top_n
+    p.topk, p.offsets, p.tokens, p.cursor, p.blk_cu = ptr(topk), ptr(offsets), ptr(tokens), 0, ptr(blk_cu)
+    p.Tq, p.KH, p.n_blocks_total = T, KH, n_blocks
+    call("nsa_k2q_index_static", p, topk)
+    return offsets, tokens
