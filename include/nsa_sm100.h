@@ -123,6 +123,8 @@ typedef struct NsaAttnParams {
   const int32_t* k2q_offsets; /* selected bwd: [KH, n_blocks_total+1] CSR offsets from nsa_k2q_index      */
   const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows of each block's list         */
   const int32_t* k2q_blk_cu;  /* selected bwd: [n_pieces+1] first table row of each piece (as in NsaK2qParams) */
+  int32_t* status;   /* optional device word: kernels OR a bit into it when a bounded wait on the tensor-core
+                        pipeline gives up (NSA_ERR_TIMEOUT condition); never written on success; may be NULL     */
   int64_t q_stride_t, k_stride_t, v_stride_t, o_stride_t, do_stride_t, dq_stride_t, dk_stride_t, dv_stride_t;
   int64_t lse_stride_t, lse_stride_h;
   int64_t topk_stride_h; /* elements between kv heads in topk (= Tq*top_n when contiguous)                */

@@ -25,6 +25,16 @@ int check_launch(const char* what) {
   return NSA_OK;
 }
 
+int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y) {
+  NSA_REQUIRE(p && p->q && p->k && p->v && p->o, NSA_ERR_BAD_ARG, "%s: null tensor pointer", name);
+  NSA_REQUIRE(p->meta.piece_cu && p->meta.x_cu && (!need_y || p->meta.y_cu), NSA_ERR_BAD_ARG, "%s: null metadata pointer", name);
+  NSA_REQUIRE(p->D == 64 || p->D == 128, NSA_ERR_UNSUPPORTED_SHAPE, "%s: head dim %d not supported (64 or 128, qk dim == v dim)", name, p->D);
+  NSA_REQUIRE(p->KH > 0 && p->QH % p->KH == 0, NSA_ERR_BAD_ARG, "%s: QH=%d must be a multiple of KH=%d", name, p->QH, p->KH);
+  NSA_REQUIRE(p->QH / p->KH <= 128, NSA_ERR_UNSUPPORTED_SHAPE, "%s: more than 128 query heads per kv head", name);
+  NSA_REQUIRE(p->hp.kernel_size > 0 && p->hp.stride > 0, NSA_ERR_BAD_ARG, "%s: bad kernel_size/stride", name);
+  return NSA_OK;
+}
+
 }  // namespace nsa
 
 extern "C" const char* nsa_last_error(void) { return nsa::g_err; }

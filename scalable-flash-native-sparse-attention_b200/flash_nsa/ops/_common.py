@@ -58,6 +58,27 @@ def check_bf16_3d(name, t, last_contig=True):
     assert t.stride(-1) == 1 and t.stride(1) == t.size(-1), f"{name}: heads and head_dim must be contiguous"
 
 
+_status = {}
+
+
+def status_word(device):
+    """One int32 per device that kernels OR error bits into (bounded waits that gave up)."""
+    key = torch.device(device).index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device="cuda"):
+    """Synchronises and raises if any kernel reported a pipeline time-out since the last check."""
+    dev = torch.device(device, torch.cuda.current_device()) if torch.device(device).index is None else torch.device(device)
+    w = status_word(dev)
+    v = int(w.item())
+    if v:
+        w.zero_()
+        raise _lib.NsaError(f"a kernel gave up waiting on its tensor-core pipeline (status bits {v:#x})")
+
+
 def call(fn, params, ref_tensor):
     _lib.call(fn, params, stream_ptr(ref_tensor))
 
@@ -100,5 +121,6 @@ def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_majo
         p.topk_stride_h = topk.stride(0)
     p.sm_scale = float(sm_scale)
     p.QH, p.KH, p.D = QH, KH, D
+    p.status = ptr(status_word(q.device))
     p.n_q_rows = T
     return p

@@ -22,3 +22,14 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _kernel_status_is_clean(request):
+    """After every GPU test: no kernel may have reported a pipeline time-out."""
+    yield
+    if "gpu" in request.keywords:
+        import torch
+        if torch.cuda.is_available():
+            from flash_nsa.ops._common import check_status
+            check_status()
