@@ -3,12 +3,7 @@
 //  dense_dq_kernel<D,MODE>   dQ of the compressed / sliding-window branch: one CTA per 128-row query tile
 //                            (tokens x the G heads of a kv head), loops over its K/V tiles:
 //                            S = QK^T, P = exp2(S*c - lse), dP = dO V^T, dS = P*(dP - delta), dQ += dS K.
-//  dkdv_kernel<D,MODE>       dK/dV of all three branches: one CTA per 64-row K/V tile (and a slice of the
-//                            queries that see it), loops over 64-row query tiles (tokens x G heads):
-//                            S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
-//                            Queries come from a contiguous range (compressed, sliding window) or from the
-//                            key-block -> queries lists (selected branch).  Partial results are added to the
-//                            fp32 dK/dV with atomics, because several CTAs can share a K/V tile.
+//  (dK/dV of all three branches live in dkdv_tc.cu; this file launches them.)
 // P and dS are rounded to bf16 before the second-stage products, as in the reference kernels
 // (flash_nsa/ops/compress_attn.py:311-325, flash_nsa/ops/select_attn.py:262-280).
 #include "nsa_common.cuh"
@@ -206,216 +201,8 @@ __global__ void __launch_bounds__(256, 1) dense_dq_kernel(NsaAttnParams p) {
   }
 }
 
-// ------------------------------------------------------------------------------------------------ dK / dV
-__device__ __forceinline__ int find_le(const int32_t* cu, int n, int x) {
-  int lo = 0, hi = n;
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (cu[mid] <= x) lo = mid; else hi = mid;
-  }
-  return lo;
-}
-
 template <int D, int MODE>
-__global__ void __launch_bounds__(128, 2) dkdv_kernel(NsaAttnParams p, DkdvLaunch L) {
-  constexpr int BK = 64, BQ = 64, CH = D / 8, KS = D / 16, NT = D / 8;
-  extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t sK = smem_u32(smem);
-  const uint32_t sV = sK + BK * D * 2;
-  const uint32_t sQ = sV + BK * D * 2;           // 2 stages
-  const uint32_t sO = sQ + 2 * BQ * D * 2;       // 2 stages
-  float* sLse = reinterpret_cast<float*>(smem + (2 * BK + 4 * BQ) * D * 2);  // [2][64]
-  float* sDl = sLse + 2 * BQ;
-  int* sTa = reinterpret_cast<int*>(sDl + 2 * BQ);
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = p.QH / p.KH;
-  const int TOKQ = BQ / G;
-  const int ks = p.hp.kernel_size, st = p.hp.stride, W = p.hp.window;
-
-  int kh, k0, kv_rows;           // first K/V row of the tile inside its sequence, number of valid rows
-  int64_t kv_bos;                // row of the sequence start in the K/V-side tensors
-  int r_lo, r_hi;                // CMP/SWA: local query rows [r_lo, r_hi) of the piece;  SLC: list positions
-  Piece pc;
-  const int32_t* list = nullptr;
-  if (MODE == MODE_SLC) {
-    kh = blockIdx.z;
-    const int row = blockIdx.x;
-    const int b = find_le(L.blk_cu, p.meta.n_pieces, row);
-    pc = load_piece(p.meta, b);
-    k0 = (row - L.blk_cu[b]) * BK;
-    kv_bos = pc.x_bos;
-    kv_rows = min(BK, pc.x_len - k0);
-    const int32_t* offs = p.k2q_offsets + (int64_t)kh * (p.n_blocks_total + 1);
-    const int lo = offs[row], hi = offs[row + 1];
-    const int per = (((hi - lo + L.splits - 1) / L.splits + TOKQ - 1) / TOKQ) * TOKQ;
-    r_lo = lo + blockIdx.y * per;
-    r_hi = min(hi, r_lo + per);
-    list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
-  } else {
-    kh = blockIdx.z % p.KH;
-    pc = load_piece(p.meta, blockIdx.z / p.KH);
-    if (MODE == MODE_CMP) {
-      k0 = blockIdx.x * BK;
-      kv_bos = pc.y_bos;
-      kv_rows = min(BK, pc.y_len - k0);
-      int first = max(0, k0 * st + ks - 1 - pc.off);
-      r_lo = max(first, (int)blockIdx.y * L.q_chunk);
-      r_hi = min(pc.len, ((int)blockIdx.y + 1) * L.q_chunk);
-    } else {
-      k0 = (max(0, pc.off - W) / BK) * BK + blockIdx.x * BK;
-      kv_bos = pc.x_bos;
-      kv_rows = min(BK, pc.x_len - k0);
-      r_lo = max(k0, pc.off) - pc.off;
-      r_hi = min(k0 + BK - 1 + W, pc.off + pc.len - 1) + 1 - pc.off;
-    }
-  }
-  if (kv_rows <= 0 || r_hi <= r_lo) return;
-  const int n_it = (r_hi - r_lo + TOKQ - 1) / TOKQ;
-
-  load_tile_async<D>(sK, reinterpret_cast<const __nv_bfloat16*>(p.k) + (kv_bos + k0) * p.k_stride_t + kh * D, p.k_stride_t, BK,
-                     kv_rows, tid, 128);
-  load_tile_async<D>(sV, reinterpret_cast<const __nv_bfloat16*>(p.v) + (kv_bos + k0) * p.v_stride_t + kh * D, p.v_stride_t, BK,
-                     kv_rows, tid, 128);
-  const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)kh * G * D;
-  const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(p.dout) + (int64_t)kh * G * D;
-
-  auto load_q = [&](int it) {
-    const int stg = it & 1;
-    const uint32_t dQ_ = sQ + stg * BQ * D * 2, dO_ = sO + stg * BQ * D * 2;
-    const int base = r_lo + it * TOKQ;
-    for (int i = tid; i < BQ * CH; i += 128) {
-      int r = i / CH, c = i % CH;
-      int n = r / G, g = r - n * G;
-      bool ok = (n < TOKQ) && (base + n < r_hi);
-      int64_t q_row = 0;
-      if (ok) q_row = (MODE == MODE_SLC) ? (int64_t)__ldg(list + base + n) : (int64_t)pc.q_start + base + n;
-      cp_async16(dQ_ + tile_off<D>(r, c), qb + q_row * p.q_stride_t + (ok ? g * D : 0) + c * 8, ok);
-      cp_async16(dO_ + tile_off<D>(r, c), ob + q_row * p.do_stride_t + (ok ? g * D : 0) + c * 8, ok);
-    }
-    if (tid < BQ) {
-      int r = tid;
-      int n = r / G, g = r - n * G;
-      bool ok = (n < TOKQ) && (base + n < r_hi);
-      float l = 0.f, d = 0.f;
-      int ta = -1;
-      if (ok) {
-        int64_t q_row = (MODE == MODE_SLC) ? (int64_t)__ldg(list + base + n) : (int64_t)pc.q_start + base + n;
-        int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h;
-        l = p.lse[a];
-        d = p.delta[a];
-        ta = pc.off + (int)(q_row - pc.q_start);
-      }
-      sLse[stg * BQ + r] = l;
-      sDl[stg * BQ + r] = d;
-      sTa[stg * BQ + r] = ta;
-    }
-  };
-  load_q(0);
-  cp_async_commit();
-
-  const int g_ = lane >> 2, c_ = lane & 3;
-  const int key_lo = k0 + warp * 16 + g_, key_hi = key_lo + 8;
-  const bool kv_lo_ok = (warp * 16 + g_) < kv_rows, kv_hi_ok = (warp * 16 + g_ + 8) < kv_rows;
-  const float c2 = p.sm_scale * 1.4426950408889634f;
-
-  float dk[NT][4], dv[NT][4];
-#pragma unroll
-  for (int i = 0; i < NT; ++i) {
-    dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f;
-    dv[i][0] = dv[i][1] = dv[i][2] = dv[i][3] = 0.f;
-  }
-
-  for (int it = 0; it < n_it; ++it) {
-    if (it + 1 < n_it) load_q(it + 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    const int stg = it & 1;
-    const uint32_t tQ = sQ + stg * BQ * D * 2, tO = sO + stg * BQ * D * 2;
-    const float* lse_s = sLse + stg * BQ;
-    const float* dl_s = sDl + stg * BQ;
-    const int* ta_s = sTa + stg * BQ;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float s[4][4], dp[4][4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-        dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f;
-      }
-#pragma unroll
-      for (int kk = 0; kk < KS; ++kk) {
-        uint32_t ka[4], va[4];
-        load_a_frag<D>(ka, sK, warp * 16, kk, lane);
-        load_a_frag<D>(va, sV, warp * 16, kk, lane);
-#pragma unroll
-        for (int np = 0; np < 2; ++np) {
-          uint32_t b[4];
-          load_b_frag_nk<D>(b, tQ, half * 32 + np * 16, kk, lane);
-          mma_bf16(s[2 * np], ka, b[0], b[1]);
-          mma_bf16(s[2 * np + 1], ka, b[2], b[3]);
-          load_b_frag_nk<D>(b, tO, half * 32 + np * 16, kk, lane);
-          mma_bf16(dp[2 * np], va, b[0], b[1]);
-          mma_bf16(dp[2 * np + 1], va, b[2], b[3]);
-        }
-      }
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int col = half * 32 + nt * 8 + 2 * c_ + (e & 1);
-          const int key = (e < 2) ? key_lo : key_hi;
-          const bool kok = (e < 2) ? kv_lo_ok : kv_hi_ok;
-          const int ta = ta_s[col];
-          bool vis;
-          if (MODE == MODE_CMP)
-            vis = kok && (key * st + ks - 1 <= ta);
-          else if (MODE == MODE_SWA)
-            vis = kok && (key <= ta) && (ta - key <= W);
-          else
-            vis = kok && (key <= ta);
-          float pv = vis ? fast_exp2(fmaf(s[nt][e], c2, -lse_s[col])) : 0.f;
-          s[nt][e] = pv;
-          dp[nt][e] = pv * (dp[nt][e] - dl_s[col]);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        uint32_t pa0 = pack_bf16(s[2 * u][0], s[2 * u][1]), pa1 = pack_bf16(s[2 * u][2], s[2 * u][3]);
-        uint32_t pa2 = pack_bf16(s[2 * u + 1][0], s[2 * u + 1][1]), pa3 = pack_bf16(s[2 * u + 1][2], s[2 * u + 1][3]);
-        uint32_t da0 = pack_bf16(dp[2 * u][0], dp[2 * u][1]), da1 = pack_bf16(dp[2 * u][2], dp[2 * u][3]);
-        uint32_t da2 = pack_bf16(dp[2 * u + 1][0], dp[2 * u + 1][1]), da3 = pack_bf16(dp[2 * u + 1][2], dp[2 * u + 1][3]);
-#pragma unroll
-        for (int np = 0; np < NT / 2; ++np) {
-          uint32_t b[4];
-          load_b_frag_kn<D>(b, tO, half * 32 + u * 16, np * 16, lane);
-          mma_bf16(dv[2 * np], pa0, pa1, pa2, pa3, b[0], b[1]);
-          mma_bf16(dv[2 * np + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
-          load_b_frag_kn<D>(b, tQ, half * 32 + u * 16, np * 16, lane);
-          mma_bf16(dk[2 * np], da0, da1, da2, da3, b[0], b[1]);
-          mma_bf16(dk[2 * np + 1], da0, da1, da2, da3, b[2], b[3]);
-        }
-      }
-    }
-    __syncthreads();
-  }
-  cp_async_wait<0>();
-
-  float* dkb = p.dk + (kv_bos + k0 + warp * 16) * p.dk_stride_t + kh * D + 2 * c_;
-  float* dvb = p.dv + (kv_bos + k0 + warp * 16) * p.dv_stride_t + kh * D + 2 * c_;
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    if (kv_lo_ok) {
-      atomicAdd(reinterpret_cast<float2*>(dkb + (int64_t)g_ * p.dk_stride_t + nt * 8), make_float2(dk[nt][0] * p.sm_scale, dk[nt][1] * p.sm_scale));
-      atomicAdd(reinterpret_cast<float2*>(dvb + (int64_t)g_ * p.dv_stride_t + nt * 8), make_float2(dv[nt][0], dv[nt][1]));
-    }
-    if (kv_hi_ok) {
-      atomicAdd(reinterpret_cast<float2*>(dkb + (int64_t)(g_ + 8) * p.dk_stride_t + nt * 8), make_float2(dk[nt][2] * p.sm_scale, dk[nt][3] * p.sm_scale));
-      atomicAdd(reinterpret_cast<float2*>(dvb + (int64_t)(g_ + 8) * p.dv_stride_t + nt * 8), make_float2(dv[nt][2], dv[nt][3]));
-    }
-  }
-}
+int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L);  // dkdv_tc.cu
 
 template <typename K>
 static int set_smem(K kernel, size_t smem, const char* name) {
@@ -437,18 +224,6 @@ static int launch_dq(const NsaAttnParams* p, cudaStream_t st, const char* name) 
   dense_dq_kernel<D, MODE><<<grid, 256, smem, st>>>(*p);
   return check_launch(name);
 }
-
-template <int D, int MODE>
-int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L) {
-  size_t smem = (size_t)(2 * 64 + 4 * 64) * D * 2 + 2 * 64 * 4 * 3;
-  int rc = set_smem(dkdv_kernel<D, MODE>, smem, name);
-  if (rc) return rc;
-  dkdv_kernel<D, MODE><<<grid, 128, smem, st>>>(*p, L);
-  return check_launch(name);
-}
-
-template int launch_dkdv<128, MODE_SLC>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
-template int launch_dkdv<64, MODE_SLC>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
 
 static int check_bwd(const NsaAttnParams* p, const char* name) {
   NSA_REQUIRE(p->lse && p->dout && p->delta && p->dq && p->dk && p->dv, NSA_ERR_BAD_ARG, "%s: lse, dout, delta, dq, dk, dv are required", name);

@@ -40,10 +40,10 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t slab_b
   d |= (uint64_t)2 << 61;
   return d;
 }
-// bf16 x bf16 -> fp32, M x N tile, A K-major (or in tensor memory), B K-major or MN-major
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) |
-         ((uint32_t)(M >> 4) << 24);
+// bf16 x bf16 -> fp32, M x N tile; each operand K-major (contraction index contiguous) or MN-major
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool b_mn_major, bool a_mn_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // ------------------------------------------------------------------ MMA issue (one thread)
@@ -127,6 +127,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* bu
   return false;
 }
 constexpr int kWaitBudget = 1 << 22;  // polls; a healthy wait takes a few hundred
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
+}
+// barrier among the `count` threads that use id `id` (warp-group scoped synchronisation)
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
 
 // ------------------------------------------------------------------ operand tile fill (all threads of the CTA)
 // rows x D bf16 from global rows (row i at base + i*stride elements) into slab layout; rows >= valid zero-filled
