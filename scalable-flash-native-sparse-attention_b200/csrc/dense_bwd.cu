@@ -1,12 +1,12 @@
-// Backward kernels on the warp-level tensor-core path.
+// Backward kernels of the dense-range branches on the Blackwell tensor core (tcgen05 + tensor memory).
 //
-//  dense_dq_kernel<D,MODE>   dQ of the compressed / sliding-window branch: one CTA per 128-row query tile
-//                            (tokens x the G heads of a kv head), loops over its K/V tiles:
-//                            S = QK^T, P = exp2(S*c - lse), dP = dO V^T, dS = P*(dP - delta), dQ += dS K.
+//  dense_dq_tc_kernel<D,MODE>  dQ of the compressed / sliding-window branch: one CTA per 128-row query tile
+//                              (tokens x the G heads of a kv head), loops over its K/V tiles:
+//                              S = QK^T, P = exp2(S*c - lse), dP = dO V^T, dS = P*(dP - delta), dQ += dS K.
 //  (dK/dV of all three branches live in dkdv_tc.cu; this file launches them.)
 // P and dS are rounded to bf16 before the second-stage products, as in the reference kernels
 // (flash_nsa/ops/compress_attn.py:311-325, flash_nsa/ops/select_attn.py:262-280).
-#include "nsa_common.cuh"
+#include "tc_common.cuh"
 
 namespace nsa {
 
@@ -19,16 +19,28 @@ void launch_delta(const void* o, const void* dout, float* delta, int64_t T, int 
 int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y);
 
 // ------------------------------------------------------------------------------------------------ dQ
+// CTA = 128 threads = one 128-row query tile; thread i owns row i (tensor-memory lane i).  Per 64-row K/V tile:
+//   S  = Q K^T (TMEM cols 0..63),  dP = dO V^T (cols 64..127)           A from shared memory (K-major)
+//   dS = exp2(S*c - lse) * (dP - delta) -> bf16 -> TMEM cols 0..31 (over S, which has been read)
+//   dQ += dS K (cols 128..128+D)                                        A = dS from tensor memory, B = K tile (MN-major)
+// K tiles are double-buffered, the V tile single-buffered (it is free again as soon as dP has been read); two CTAs
+// share an SM (256 TMEM columns, 112 KB of shared memory each).
 template <int D, int MODE>
-__global__ void __launch_bounds__(256, 1) dense_dq_kernel(NsaAttnParams p) {
-  constexpr int BM = 128, BN = 64, CH = D / 8, KS = D / 16, NT = D / 8;
-  extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t sQ = smem_u32(smem);             // Q staging, later the dQ staging tile
-  const uint32_t sO = sQ + BM * D * 2;            // dO staging
-  const uint32_t sK = sO + BM * D * 2;
-  const uint32_t sV = sK + 2 * BN * D * 2;
+__global__ void __launch_bounds__(128, 2) dense_dq_tc_kernel(NsaAttnParams p) {
+  using namespace tc;
+  constexpr int BM = 128, BN = 64, CH = D / 8;
+  constexpr uint32_t Q_BYTES = BM * D * 2, KV_BYTES = BN * D * 2, K_SLAB = BN * 128, Q_SLAB = BM * 128;
+  constexpr uint32_t TM_S = 0, TM_DP = 64, TM_DQ = 128, TM_COLS = 256;
+  constexpr uint32_t IDESC_S = make_idesc(BM, BN, false), IDESC_Q = make_idesc(BM, D, true);
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  const uint32_t sQ = base, sO = sQ + Q_BYTES;
+  const uint32_t sK = sO + Q_BYTES;          // 2 stages
+  const uint32_t sV = sK + 2 * KV_BYTES;     // 1 stage
+  const uint32_t bar_s = sV + KV_BYTES, bar_o = bar_s + 8, tm_slot = bar_o + 8;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
   const int TOK = BM / G;
   const int tile = gridDim.x - 1 - blockIdx.x;
@@ -36,6 +48,10 @@ __global__ void __launch_bounds__(256, 1) dense_dq_kernel(NsaAttnParams p) {
   const Piece pc = load_piece(p.meta, blockIdx.y);
   const int t0 = tile * TOK;
   if (t0 >= pc.len) return;
+  if (base & 1023u) {  // the operand layout needs 1024-byte aligned tiles
+    if (tid == 0 && p.status) atomicOr(p.status, 8);
+    return;
+  }
   const int ntok = min(TOK, pc.len - t0);
   const int tabs_min = pc.off + t0, tabs_max = tabs_min + ntok - 1;
   const int ks = p.hp.kernel_size, st = p.hp.stride, W = p.hp.window;
@@ -55,150 +71,162 @@ __global__ void __launch_bounds__(256, 1) dense_dq_kernel(NsaAttnParams p) {
   }
   const int ntiles = (kv_hi > kv_lo) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
 
-  {
-    const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)(pc.q_start + t0) * p.q_stride_t +
-                              (int64_t)kh * G * D;
-    const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(p.dout) + (int64_t)(pc.q_start + t0) * p.do_stride_t +
-                              (int64_t)kh * G * D;
-    for (int i = tid; i < BM * CH; i += 256) {
-      int r = i / CH, c = i % CH;
-      int tok = r / G, g = r - tok * G;
-      bool ok = tok < ntok;
-      cp_async16(sQ + tile_off<D>(r, c), qb + (ok ? (int64_t)tok * p.q_stride_t + g * D : 0) + c * 8, ok);
-      cp_async16(sO + tile_off<D>(r, c), ob + (ok ? (int64_t)tok * p.do_stride_t + g * D : 0) + c * 8, ok);
+  const int row = tid;
+  const int tok = row / G, g = row - tok * G;
+  const bool row_ok = tok < ntok;
+  const int t_abs = tabs_min + tok;
+  const int64_t q_row = pc.q_start + t0 + tok;
+  __nv_bfloat16* dq_row = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)(kh * G + g) * D;
+
+  if (ntiles == 0) {
+    if (row_ok && !p.accumulate_dq) {
+      uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) reinterpret_cast<uint4*>(dq_row)[c] = z;
     }
-    cp_async_commit();
+    return;
   }
-  auto load_kv = [&](int it) {
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(tm_slot, TM_COLS);
+  {
+    const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)(pc.q_start + t0) * p.q_stride_t + (int64_t)kh * G * D;
+    const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(p.dout) + (int64_t)(pc.q_start + t0) * p.do_stride_t + (int64_t)kh * G * D;
+    for (int i = tid; i < BM * CH; i += 128) {
+      int r = i / CH, c = i % CH;
+      int tk = r / G, gg = r - tk * G;
+      bool ok = tk < ntok;
+      cp_async16(sQ + slab_off(BM, r, c), qb + (ok ? (int64_t)tk * p.q_stride_t + gg * D : 0) + c * 8, ok);
+      cp_async16(sO + slab_off(BM, r, c), ob + (ok ? (int64_t)tk * p.do_stride_t + gg * D : 0) + c * 8, ok);
+    }
+  }
+  auto load_k = [&](int it) {
     int kv0 = kv_lo + it * BN;
-    int valid = min(BN, kv_hi - kv0);
-    load_tile_async<D>(sK + (it & 1) * BN * D * 2, kbase + (int64_t)kv0 * p.k_stride_t, p.k_stride_t, BN, valid, tid, 256);
-    load_tile_async<D>(sV + (it & 1) * BN * D * 2, vbase + (int64_t)kv0 * p.v_stride_t, p.v_stride_t, BN, valid, tid, 256);
+    fill_tile_async<D>(sK + (it & 1) * KV_BYTES, kbase + (int64_t)kv0 * p.k_stride_t, p.k_stride_t, BN, min(BN, kv_hi - kv0), tid, 128);
   };
-  if (ntiles > 0) load_kv(0);
+  auto load_v = [&](int it) {
+    int kv0 = kv_lo + it * BN;
+    fill_tile_async<D>(sV, vbase + (int64_t)kv0 * p.v_stride_t, p.v_stride_t, BN, min(BN, kv_hi - kv0), tid, 128);
+  };
+  load_k(0);
+  load_v(0);
   cp_async_commit();
-  cp_async_wait<1>();
+  float lse = 0.f, dl = 0.f;
+  if (row_ok) {
+    int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h;
+    lse = p.lse[a];
+    dl = p.delta[a];
+  }
+  fence_before_sync();
   __syncthreads();
-
-  uint32_t qf[KS][4], of[KS][4];
-#pragma unroll
-  for (int kk = 0; kk < KS; ++kk) {
-    load_a_frag<D>(qf[kk], sQ, warp * 16, kk, lane);
-    load_a_frag<D>(of[kk], sO, warp * 16, kk, lane);
-  }
-
-  const int g_ = lane >> 2, c_ = lane & 3;
-  const int row_lo = warp * 16 + g_, row_hi = row_lo + 8;
-  const int tok_lo = row_lo / G, tok_hi = row_hi / G;
-  const int tabs_lo = tabs_min + tok_lo, tabs_hi = tabs_min + tok_hi;
+  fence_after_sync();
+  uint32_t tmem;
+  asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
   const float c2 = p.sm_scale * 1.4426950408889634f;
-  float lse_lo = 0.f, lse_hi = 0.f, dl_lo = 0.f, dl_hi = 0.f;
-  if (tok_lo < ntok) {
-    int64_t a = (int64_t)(pc.q_start + t0 + tok_lo) * p.lse_stride_t + (int64_t)(kh * G + row_lo - tok_lo * G) * p.lse_stride_h;
-    lse_lo = p.lse[a];
-    dl_lo = p.delta[a];
-  }
-  if (tok_hi < ntok) {
-    int64_t a = (int64_t)(pc.q_start + t0 + tok_hi) * p.lse_stride_t + (int64_t)(kh * G + row_hi - tok_hi * G) * p.lse_stride_h;
-    lse_hi = p.lse[a];
-    dl_hi = p.delta[a];
-  }
-
-  float dq[NT][4];
-#pragma unroll
-  for (int i = 0; i < NT; ++i) dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f;
+  int budget = kWaitBudget;
+  bool timed_out = false;
 
   for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) load_kv(it + 1);
-    cp_async_commit();
-    cp_async_wait<1>();
+    // previous tile's dQ MMA done: the S/dS columns and K stage (it+1)&1 are free
+    if (it > 0 && !mbar_wait(bar_o, (it - 1) & 1, &budget)) timed_out = true;
+    cp_async_wait<0>();
+    fence_proxy_async();
     __syncthreads();
-    const uint32_t tK = sK + (it & 1) * BN * D * 2, tV = sV + (it & 1) * BN * D * 2;
+    if (it + 1 < ntiles) load_k(it + 1);
+    cp_async_commit();
+    const uint32_t tK = sK + (it & 1) * KV_BYTES;
     const int kv0 = kv_lo + it * BN;
+    if (tid == 0) {
+      fence_after_sync();
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        uint32_t ao = (k >> 2) * Q_SLAB + (k & 3) * 32, bo = (k >> 2) * K_SLAB + (k & 3) * 32;
+        mma_ss(tmem + TM_S, desc_kmajor(sQ + ao), desc_kmajor(tK + bo), IDESC_S, k > 0);
+      }
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        uint32_t ao = (k >> 2) * Q_SLAB + (k & 3) * 32, bo = (k >> 2) * K_SLAB + (k & 3) * 32;
+        mma_ss(tmem + TM_DP, desc_kmajor(sO + ao), desc_kmajor(sV + bo), IDESC_S, k > 0);
+      }
+      mma_commit(bar_s);
+    }
+    if (!mbar_wait(bar_s, it & 1, &budget)) timed_out = true;
+    fence_after_sync();
+    if (it + 1 < ntiles) load_v(it + 1);  // dP has been computed: the V stage is free
+    cp_async_commit();
+
+    uint32_t ds[32];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      float s[4][4], dp[4][4];
+      uint32_t sv[32], dv[32];
+      tmem_ld32(lane_base + TM_S + half * 32, sv);
+      tmem_ld32(lane_base + TM_DP + half * 32, dv);
+      wait_ld();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-        dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.f;
-      }
+      for (int i = 0; i < 32; i += 2) {
+        float x[2];
 #pragma unroll
-      for (int kk = 0; kk < KS; ++kk) {
-#pragma unroll
-        for (int np = 0; np < 2; ++np) {
-          uint32_t b[4];
-          load_b_frag_nk<D>(b, tK, half * 32 + np * 16, kk, lane);
-          mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
-          mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
-          load_b_frag_nk<D>(b, tV, half * 32 + np * 16, kk, lane);
-          mma_bf16(dp[2 * np], of[kk], b[0], b[1]);
-          mma_bf16(dp[2 * np + 1], of[kk], b[2], b[3]);
-        }
-      }
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          int col = kv0 + half * 32 + nt * 8 + 2 * c_ + (e & 1);
-          int ta = (e < 2) ? tabs_lo : tabs_hi;
+        for (int e = 0; e < 2; ++e) {
+          const int col = kv0 + half * 32 + i + e;
           bool vis;
           if (MODE == MODE_CMP)
-            vis = (col * st + ks - 1 <= ta) && (col < kv_hi);
+            vis = (col * st + ks - 1 <= t_abs) && (col < kv_hi);
           else
-            vis = (col <= ta) && (col >= ta - W) && (col < kv_hi);
-          float pv = vis ? fast_exp2(fmaf(s[nt][e], c2, -((e < 2) ? lse_lo : lse_hi))) : 0.f;
-          dp[nt][e] = pv * (dp[nt][e] - ((e < 2) ? dl_lo : dl_hi));
+            vis = (col <= t_abs) && (col >= t_abs - W) && (col < kv_hi);
+          float pv = (vis && row_ok) ? fast_exp2(fmaf(__uint_as_float(sv[i + e]), c2, -lse)) : 0.f;
+          x[e] = pv * (__uint_as_float(dv[i + e]) - dl);
         }
-      }
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        uint32_t a0 = pack_bf16(dp[2 * u][0], dp[2 * u][1]), a1 = pack_bf16(dp[2 * u][2], dp[2 * u][3]);
-        uint32_t a2 = pack_bf16(dp[2 * u + 1][0], dp[2 * u + 1][1]), a3 = pack_bf16(dp[2 * u + 1][2], dp[2 * u + 1][3]);
-#pragma unroll
-        for (int np = 0; np < NT / 2; ++np) {
-          uint32_t b[4];
-          load_b_frag_kn<D>(b, tK, half * 32 + u * 16, np * 16, lane);
-          mma_bf16(dq[2 * np], a0, a1, a2, a3, b[0], b[1]);
-          mma_bf16(dq[2 * np + 1], a0, a1, a2, a3, b[2], b[3]);
-        }
+        ds[half * 16 + (i >> 1)] = pack_bf16(x[0], x[1]);
       }
     }
+    tmem_st32(lane_base + TM_S, ds);
+    wait_st();
+    fence_before_sync();
     __syncthreads();
+    if (tid == 0) {
+      fence_after_sync();
+#pragma unroll
+      for (int u = 0; u < BN / 16; ++u)
+        mma_ts(tmem + TM_DQ, tmem + TM_S + u * 8, desc_mnmajor(tK + u * 2048, K_SLAB), IDESC_Q, (it > 0 || u > 0));
+      mma_commit(bar_o);
+    }
   }
+  if (!mbar_wait(bar_o, (ntiles - 1) & 1, &budget)) timed_out = true;
+  fence_after_sync();
   cp_async_wait<0>();
 
-  __syncwarp();
+  const float sc = p.sm_scale;
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    uint32_t lo = pack_bf16(dq[nt][0] * p.sm_scale, dq[nt][1] * p.sm_scale);
-    uint32_t hi = pack_bf16(dq[nt][2] * p.sm_scale, dq[nt][3] * p.sm_scale);
-    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(sQ + tile_off<D>(row_lo, nt) + c_ * 4), "r"(lo));
-    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(sQ + tile_off<D>(row_hi, nt) + c_ * 4), "r"(hi));
-  }
-  __syncwarp();
-  {
-    __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(p.dq) + (int64_t)(pc.q_start + t0) * p.dq_stride_t + (int64_t)kh * G * D;
-    for (int i = lane; i < 16 * CH; i += 32) {
-      int r = warp * 16 + i / CH, c = i % CH;
-      int tok = r / G, g = r - tok * G;
-      if (tok < ntok) {
-        uint4 v;
-        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                     : "r"(sQ + tile_off<D>(r, c)));
-        uint4* dst = reinterpret_cast<uint4*>(ob + (int64_t)tok * p.dq_stride_t + g * D + c * 8);
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t o[32];
+    tmem_ld32(lane_base + TM_DQ + c * 32, o);
+    wait_ld();
+    if (row_ok) {
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[q4 * 8 + e]) * sc;
+        uint4* dst = reinterpret_cast<uint4*>(dq_row + c * 32 + q4 * 8);
         if (p.accumulate_dq) {
           uint4 old = *dst;
-          v.x = pack_bf16(bf16_lo(v.x) + bf16_lo(old.x), bf16_hi(v.x) + bf16_hi(old.x));
-          v.y = pack_bf16(bf16_lo(v.y) + bf16_lo(old.y), bf16_hi(v.y) + bf16_hi(old.y));
-          v.z = pack_bf16(bf16_lo(v.z) + bf16_lo(old.z), bf16_hi(v.z) + bf16_hi(old.z));
-          v.w = pack_bf16(bf16_lo(v.w) + bf16_lo(old.w), bf16_hi(v.w) + bf16_hi(old.w));
+          f[0] += bf16_lo(old.x); f[1] += bf16_hi(old.x); f[2] += bf16_lo(old.y); f[3] += bf16_hi(old.y);
+          f[4] += bf16_lo(old.z); f[5] += bf16_hi(old.z); f[6] += bf16_lo(old.w); f[7] += bf16_hi(old.w);
         }
-        *dst = v;
+        uint4 w;
+        w.x = pack_bf16(f[0], f[1]); w.y = pack_bf16(f[2], f[3]); w.z = pack_bf16(f[4], f[5]); w.w = pack_bf16(f[6], f[7]);
+        *dst = w;
       }
     }
   }
+  if (timed_out && p.status) atomicOr(p.status, 4);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TM_COLS);
 }
 
 template <int D, int MODE>
@@ -217,11 +245,11 @@ static int set_smem(K kernel, size_t smem, const char* name) {
 template <int D, int MODE>
 static int launch_dq(const NsaAttnParams* p, cudaStream_t st, const char* name) {
   const int G = p->QH / p->KH, TOK = 128 / G;
-  size_t smem = (size_t)(2 * 128 + 4 * 64) * D * 2;
-  int rc = set_smem(dense_dq_kernel<D, MODE>, smem, name);
+  size_t smem = (size_t)(2 * 128 + 3 * 64) * D * 2 + 64;
+  int rc = set_smem(dense_dq_tc_kernel<D, MODE>, smem, name);
   if (rc) return rc;
   dim3 grid((p->meta.max_piece_len + TOK - 1) / TOK, p->meta.n_pieces, p->KH);
-  dense_dq_kernel<D, MODE><<<grid, 256, smem, st>>>(*p);
+  dense_dq_tc_kernel<D, MODE><<<grid, 128, smem, st>>>(*p);
   return check_launch(name);
 }
 
