@@ -137,6 +137,16 @@ class NSAHelper:
         cls.x_cu_seqlens = None
 
     @classmethod
+    def emulate_context_parallel(cls, rank, world_size, kv_head_stride=1):
+        """Put the helper into the state rank `rank` of `world_size` would have, without a process group.
+        The ops then expect q-side tensors to be that rank's shard and k/v-side tensors the whole (gathered)
+        sequences -- which lets one GPU check every rank's kernels against the unsharded run."""
+        cls.process_group = "emulated"
+        cls.kv_head_stride = kv_head_stride
+        cls.rank, cls.world_size = rank, world_size
+        cls.x_cu_seqlens = None
+
+    @classmethod
     def reset_context_parallel(cls):
         cls.process_group, cls.rank, cls.world_size = None, 0, 1
         cls.cp_cu_seqlens = cls.cp_batch_idx = cls.cp_offset = None
