@@ -41,12 +41,20 @@ typedef struct NsaSeqMeta {
   const int32_t* piece_off; /* [n_pieces] position of the piece's first row in its sequence; NULL = zeros    */
   const int32_t* x_cu;      /* [n_seq+1] token offsets of the sequences in K/V-side tensors                  */
   const int32_t* y_cu;      /* [n_seq+1] offsets of the sequences' compressed rows; may be NULL if unused     */
+  /* Paged K/V (inference): when kv_table is set, token row r of sequence s lives at flat cache row
+   * kv_table[s*kv_table_stride + r/page_size]*page_size + r%page_size instead of x_cu[s]+r (x_cu then only gives the
+   * lengths); cmp_table does the same for compressed rows (y_cu gives their counts).  flash_nsa/inference/*.py
+   * address the cache the same way (e.g. inference/compress_attn.py:93-97).                                     */
+  const int32_t* kv_table;
+  const int32_t* cmp_table;
   int32_t n_pieces;
   int32_t n_seq;
   int32_t max_piece_len; /* longest piece (grid sizing)                                                    */
   int32_t x_maxlen;      /* longest sequence                                                               */
   int32_t y_maxlen;      /* most compressed rows in one sequence                                           */
-  int32_t reserved0;
+  int32_t page_size;     /* rows per cache page (paged mode)                                               */
+  int32_t kv_table_stride;
+  int32_t cmp_table_stride;
 } NsaSeqMeta;
 
 typedef struct NsaHyper {
@@ -212,6 +220,27 @@ typedef struct NsaCombineParams {
 /* replaces combine_fwd / combine_bwd, flash_nsa/ops/combine.py:114-177 */
 int nsa_combine_fwd(const NsaCombineParams* p, void* stream);
 int nsa_combine_bwd(const NsaCombineParams* p, void* stream);
+
+/* ---- paged-KV pooling (inference) ---------------------------------------------------------------------- */
+typedef struct NsaPagedPoolParams {
+  void* cache0;                /* [pages*page_size, H, D] bf16 cache; pooled rows are written IN PLACE at slot rows */
+  void* cache1;                /* optional second cache (V) pooled by the same launch, or NULL                      */
+  const int32_t* slot_mapping; /* prefill: one entry per compressed row of the batch; decode: one per sequence;
+                                  flat cache row to write, -1 = nothing to write                                    */
+  const int32_t* kv_table;     /* [B, table_stride] page ids of the token rows                                      */
+  const int32_t* y_cu;         /* prefill: [B+1] offsets of the sequences' compressed rows                          */
+  const int32_t* context_lens; /* decode: [B] tokens in the cache, the new one included                             */
+  int64_t row_stride;          /* elements between cache rows (H*D)                                                 */
+  int32_t B, H, D;
+  int32_t page_size, table_stride;
+  int32_t y_maxlen;            /* prefill: most compressed rows in one sequence (grid sizing)                       */
+  int32_t kernel_size, stride;
+  int32_t decode;              /* 0: prefill (every row with a slot), 1: decode (only the window ending at the last token) */
+  int32_t reserved0;
+} NsaPagedPoolParams;
+/* replaces mean_pooling_prefill / mean_pooling_decode / kv_mean_pooling_decode,
+ * flash_nsa/inference/compress_kv.py:191-286 */
+int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream);
 
 /* ---- context-parallel chunk reorder ------------------------------------------------------------------ */
 typedef struct NsaReorderParams {

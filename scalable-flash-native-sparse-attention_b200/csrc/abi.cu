@@ -53,6 +53,7 @@ extern "C" int nsa_struct_size(const char* name) {
   NSA_SZ(NsaK2qParams);
   NSA_SZ(NsaCombineParams);
   NSA_SZ(NsaReorderParams);
+  NSA_SZ(NsaPagedPoolParams);
 #undef NSA_SZ
   return 0;
 }

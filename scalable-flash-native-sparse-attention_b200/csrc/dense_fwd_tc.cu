@@ -48,17 +48,14 @@ __global__ void __launch_bounds__(128, 2) dense_fwd_tc_kernel(NsaAttnParams p) {
   const int ks = p.hp.kernel_size, st = p.hp.stride, W = p.hp.window;
 
   int kv_lo, kv_hi;
-  const __nv_bfloat16 *kbase, *vbase;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(p.k) + kh * D;
+  const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(p.v) + kh * D;
   if (MODE == MODE_CMP) {
     kv_lo = 0;
     kv_hi = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
-    kbase = reinterpret_cast<const __nv_bfloat16*>(p.k) + (int64_t)pc.y_bos * p.k_stride_t + kh * D;
-    vbase = reinterpret_cast<const __nv_bfloat16*>(p.v) + (int64_t)pc.y_bos * p.v_stride_t + kh * D;
   } else {
     kv_lo = max(0, tabs_min - W);
     kv_hi = min(tabs_max + 1, pc.x_len);
-    kbase = reinterpret_cast<const __nv_bfloat16*>(p.k) + (int64_t)pc.x_bos * p.k_stride_t + kh * D;
-    vbase = reinterpret_cast<const __nv_bfloat16*>(p.v) + (int64_t)pc.x_bos * p.v_stride_t + kh * D;
   }
   const int ntiles = (kv_hi > kv_lo) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
 
@@ -100,8 +97,8 @@ __global__ void __launch_bounds__(128, 2) dense_fwd_tc_kernel(NsaAttnParams p) {
   auto load_kv = [&](int it) {
     int kv0 = kv_lo + it * BN;
     int valid = min(BN, kv_hi - kv0);
-    fill_tile_async<D>(sK + (it & 1) * KV_BYTES, kbase + (int64_t)kv0 * p.k_stride_t, p.k_stride_t, BN, valid, tid, 128);
-    fill_tile_async<D>(sV + (it & 1) * KV_BYTES, vbase + (int64_t)kv0 * p.v_stride_t, p.v_stride_t, BN, valid, tid, 128);
+    fill_kv_tile_async<D, MODE == MODE_CMP>(sK + (it & 1) * KV_BYTES, kbase, p.k_stride_t, pc, kv0, BN, valid, tid, 128);
+    fill_kv_tile_async<D, MODE == MODE_CMP>(sV + (it & 1) * KV_BYTES, vbase, p.v_stride_t, pc, kv0, BN, valid, tid, 128);
   };
   load_kv(0);
   cp_async_commit();

@@ -268,6 +268,47 @@ __global__ void reorder_kernel(NsaReorderParams p) {
   y[dst * per + within] = x[src * per + within];
 }
 
+// ------------------------------------------------------------------------------------------------ paged pooling
+// prefill: grid (cdiv(y_maxlen*CH,256), B, H*ncache); decode: grid (cdiv(CH,32)... one thread per 16 B of the row
+__global__ void paged_pool_kernel(NsaPagedPoolParams p) {
+  const int CH = p.D / 8;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  int j = idx / CH, c = idx % CH;
+  const int b = blockIdx.y;
+  const int h = blockIdx.z % p.H;
+  __nv_bfloat16* cache = reinterpret_cast<__nv_bfloat16*>(blockIdx.z / p.H ? p.cache1 : p.cache0);
+  int slot;
+  if (p.decode) {
+    if (j > 0) return;
+    slot = p.slot_mapping[b];
+    if (slot < 0) return;
+    int x_len = p.context_lens[b];
+    if (x_len <= p.kernel_size - 1) return;
+    j = (x_len - p.kernel_size) / p.stride;
+  } else {
+    int y_bos = p.y_cu[b], y_len = p.y_cu[b + 1] - y_bos;
+    if (j >= y_len) return;
+    slot = p.slot_mapping[y_bos + j];
+    if (slot < 0) return;
+  }
+  const int32_t* tab = p.kv_table + (int64_t)b * p.table_stride;
+  F8 acc;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
+  const int start = j * p.stride;
+  for (int i = 0; i < p.kernel_size; ++i) {
+    int r = start + i;
+    int64_t row = (int64_t)tab[r / p.page_size] * p.page_size + r % p.page_size;
+    F8 f = unpack8(*reinterpret_cast<const uint4*>(cache + row * p.row_stride + h * p.D + c * 8));
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+  }
+  float inv = 1.f / (float)p.kernel_size;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc.v[e] *= inv;
+  *reinterpret_cast<uint4*>(cache + (int64_t)slot * p.row_stride + h * p.D + c * 8) = pack8(acc);
+}
+
 // ------------------------------------------------------------------------------------------------ delta = rowsum(o*do)
 // one thread per 8 elements of a (t,h) row; used by every attention backward.
 __global__ void delta_kernel(const __nv_bfloat16* o, const __nv_bfloat16* dout, float* delta, int64_t T, int H, int D,
@@ -385,4 +426,17 @@ extern "C" int nsa_reorder(const NsaReorderParams* p, void* stream) {
   if (n == 0) return NSA_OK;
   reorder_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
   return check_launch("reorder");
+}
+
+extern "C" int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream) {
+  NSA_REQUIRE(p && p->cache0 && p->slot_mapping && p->kv_table, NSA_ERR_BAD_ARG, "paged_mean_pool: null pointer");
+  NSA_REQUIRE(p->decode ? p->context_lens != nullptr : p->y_cu != nullptr, NSA_ERR_BAD_ARG, "paged_mean_pool: missing length table");
+  NSA_REQUIRE(p->D % 8 == 0 && p->D > 0 && p->page_size > 0, NSA_ERR_UNSUPPORTED_SHAPE, "paged_mean_pool: D=%d page=%d", p->D, p->page_size);
+  if (p->B <= 0) return NSA_OK;
+  int rows = p->decode ? 1 : p->y_maxlen;
+  if (rows <= 0) return NSA_OK;
+  const int CH = p->D / 8;
+  dim3 grid((unsigned)(((int64_t)rows * CH + 63) / 64), p->B, p->H * (p->cache1 ? 2 : 1));
+  paged_pool_kernel<<<grid, 64, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("paged_mean_pool");
 }

@@ -41,7 +41,18 @@ struct Piece {
   int x_len;     // sequence length
   int y_bos;     // first compressed row of the sequence
   int y_len;     // compressed rows of the sequence
+  const int32_t* x_tab;  // paged mode: this sequence's page list for token rows (else null)
+  const int32_t* y_tab;  // paged mode: this sequence's page list for compressed rows (else null)
+  int page;
 };
+
+// flat row index (in the K/V-side tensor) of token row r / compressed row j of the piece's sequence
+__device__ __forceinline__ int64_t tok_row(const Piece& p, int r) {
+  return p.x_tab ? (int64_t)p.x_tab[r / p.page] * p.page + (r % p.page) : (int64_t)p.x_bos + r;
+}
+__device__ __forceinline__ int64_t cmp_row(const Piece& p, int j) {
+  return p.y_tab ? (int64_t)p.y_tab[j / p.page] * p.page + (j % p.page) : (int64_t)p.y_bos + j;
+}
 
 __device__ __forceinline__ Piece load_piece(const NsaSeqMeta& m, int b) {
   Piece p;
@@ -58,6 +69,9 @@ __device__ __forceinline__ Piece load_piece(const NsaSeqMeta& m, int b) {
     p.y_bos = 0;
     p.y_len = 0;
   }
+  p.page = m.page_size;
+  p.x_tab = m.kv_table ? m.kv_table + (int64_t)p.seq * m.kv_table_stride : nullptr;
+  p.y_tab = m.cmp_table ? m.cmp_table + (int64_t)p.seq * m.cmp_table_stride : nullptr;
   return p;
 }
 

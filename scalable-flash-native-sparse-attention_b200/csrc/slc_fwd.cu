@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   if (tl >= pc.len) return;
   const int t_abs = pc.off + tl;
   const int64_t q_row = pc.q_start + tl;
-  const int nk = t_abs / BS;
+  const int nk = t_abs >= 0 ? t_abs / BS : -1;  // a padded row (empty sequence) attends nothing
   const int n_valid = min(p.hp.top_n, nk + 1);
   const float c2 = p.sm_scale * 1.4426950408889634f;
 
@@ -43,8 +43,8 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
     qa[s] = ldg_nc16(qp + h_lo * D + 32 * s);
     qb[s] = ldg_nc16(qp + h_hi * D + 32 * s);
   }
-  const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(p.k) + (int64_t)pc.x_bos * p.k_stride_t + kh * D + c_ * 8;
-  const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(p.v) + (int64_t)pc.x_bos * p.v_stride_t + kh * D + g_ * 8;
+  const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(p.k) + kh * D + c_ * 8;
+  const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(p.v) + kh * D + g_ * 8;
   const int32_t* idx = p.topk + (int64_t)kh * p.topk_stride_h + q_row * p.hp.top_n;
   const int last_row = pc.x_len - 1;
 
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __nv_bfloat16* kp = kb + (int64_t)min(key0 + nt * 8 + g_, last_row) * p.k_stride_t;
+      const __nv_bfloat16* kp = kb + tok_row(pc, min(key0 + nt * 8 + g_, last_row)) * p.k_stride_t;
       uint4 kk[SS];
 #pragma unroll
       for (int ss = 0; ss < SS; ++ss) kk[ss] = ldg_nc16(kp + 32 * ss);
@@ -127,10 +127,10 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
       uint32_t a0 = pack_bf16(s[2 * u][0], s[2 * u][1]), a1 = pack_bf16(s[2 * u][2], s[2 * u][3]);
       uint32_t a2 = pack_bf16(s[2 * u + 1][0], s[2 * u + 1][1]), a3 = pack_bf16(s[2 * u + 1][2], s[2 * u + 1][3]);
       const int r0 = key0 + 16 * u + 2 * c_;
-      const __nv_bfloat16* v0p = vb + (int64_t)min(r0, last_row) * p.v_stride_t;
-      const __nv_bfloat16* v1p = vb + (int64_t)min(r0 + 1, last_row) * p.v_stride_t;
-      const __nv_bfloat16* v2p = vb + (int64_t)min(r0 + 8, last_row) * p.v_stride_t;
-      const __nv_bfloat16* v3p = vb + (int64_t)min(r0 + 9, last_row) * p.v_stride_t;
+      const __nv_bfloat16* v0p = vb + tok_row(pc, min(r0, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v1p = vb + tok_row(pc, min(r0 + 1, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v2p = vb + tok_row(pc, min(r0 + 8, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v3p = vb + tok_row(pc, min(r0 + 9, last_row)) * p.v_stride_t;
 #pragma unroll
       for (int h = 0; h < HH; ++h) {
         uint4 v0 = ldg_nc16(v0p + 64 * h), v1 = ldg_nc16(v1p + 64 * h), v2 = ldg_nc16(v2p + 64 * h), v3 = ldg_nc16(v3p + 64 * h);

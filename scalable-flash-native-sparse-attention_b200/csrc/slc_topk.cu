@@ -30,9 +30,9 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   const int top_n = p.hp.top_n, ni = p.hp.num_init, nl = p.hp.num_local;
   const int tabs_max = pc.off + t0 + ntok - 1;
   const int nvis_max = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
-  const int ntiles = max((nvis_max + BN - 1) / BN, (tabs_max / bs + 1 + 15) / 16);
+  const int ntiles = max(1, max((nvis_max + BN - 1) / BN, (max(tabs_max, 0) / bs + 1 + 15) / 16));
 
-  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(p.ck) + (int64_t)pc.y_bos * p.ck_stride_t + kh * D;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(p.ck) + kh * D;
   {
     const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)(pc.q_start + t0) * p.q_stride_t +
                               (int64_t)kh * G * D;
@@ -48,7 +48,12 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   auto load_k = [&](int it) {
     int kv0 = it * BN;
     int valid = max(0, min(BN, pc.y_len - kv0));
-    load_tile_async<D>(sK + (it & 1) * BN * D * 2, kbase + (int64_t)kv0 * p.ck_stride_t, p.ck_stride_t, BN, valid, tid, 256);
+    const uint32_t dst = sK + (it & 1) * BN * D * 2;
+    for (int i = tid; i < BN * CH; i += 256) {
+      int r = i / CH, c = i % CH;
+      bool ok = r < valid;
+      cp_async16(dst + tile_off<D>(r, c), kbase + (ok ? cmp_row(pc, kv0 + r) : 0) * p.ck_stride_t + c * 8, ok);
+    }
   };
   load_k(0);
   cp_async_commit();
@@ -64,7 +69,7 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   const int t_abs = pc.off + t0 + warp;
   const int64_t q_row = pc.q_start + t0 + warp;
   const int nvis = (tok_ok && t_abs >= ks - 1) ? min(pc.y_len, (t_abs - (ks - 1)) / st + 1) : 0;
-  const int nk = t_abs / bs;
+  const int nk = t_abs >= 0 ? t_abs / bs : -1;  // a padded row (empty sequence) selects nothing
   const int n_free = tok_ok ? max(0, min(top_n, nk + 1) - ni - nl) : 0;
   const float c2 = p.sm_scale * 1.4426950408889634f;
   // -lse of this thread's two rows (heads g_ and g_+8); rows beyond G contribute nothing

@@ -148,5 +148,18 @@ __device__ __forceinline__ void fill_tile_async(uint32_t tile, const __nv_bfloat
   }
 }
 
+// same, for rows of a sequence's K/V (or compressed K/V) that may live in a paged cache: logical rows row0.. of the piece
+template <int D, bool CMP>
+__device__ __forceinline__ void fill_kv_tile_async(uint32_t tile, const __nv_bfloat16* base, int64_t stride, const Piece& pc, int row0,
+                                                   int rows, int valid, int tid, int nthreads) {
+  constexpr int CH = D / 8;
+  for (int i = tid; i < rows * CH; i += nthreads) {
+    int r = i / CH, c = i % CH;
+    bool ok = r < valid;
+    int64_t phys = ok ? (CMP ? cmp_row(pc, row0 + r) : tok_row(pc, row0 + r)) : 0;
+    cp_async16(tile + slab_off(rows, r, c), base + phys * stride + c * 8, ok);
+  }
+}
+
 }  // namespace tc
 }  // namespace nsa

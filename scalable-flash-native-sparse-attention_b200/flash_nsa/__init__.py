@@ -13,3 +13,5 @@ from .ops.sliding_window_attention import swa_varlen_func
 from .ops.combine import fused_sigmoid_combine
 
 from .modules.megatron_level_nsa import NSACore, flash_nsa_varlen_func, cp_flash_nsa_varlen_func
+
+from .inference import nsa_prefill, nsa_decode

@@ -1,0 +1,57 @@
+"""Paged-KV inference entry points: `nsa_prefill` (chunked prefill) and `nsa_decode`, plus the per-step ops.
+Same signatures as flash_nsa/inference/__init__.py:21-257 of the reference.
+
+The KV cache is `k, v: [pages, page_size, kh, d]`; token p of a sequence lives at page `block_tables[b, p // page_size]`;
+the compressed (mean-pooled) rows live in the SAME tensors, in the pages listed by `cmp_block_tables`, and are written in
+place at the flat rows given by `cmp_slot_mapping` (-1 = already pooled / nothing new).  All kernels are the training
+forward kernels running on a piece table with the paged-row lookup switched on: a prefill chunk or a decode token is a
+"piece" whose first row sits at position context_len - new_tokens of its sequence.  No host synchronisation happens in
+any of these calls, shapes depend only on the arguments, so a decode step can be captured in a CUDA graph.
+"""
+from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
+                  topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
+                  combine_prefill, combine_decode)
+
+
+def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, context_lens, block_tables, cmp_slot_mapping,
+                cmp_block_tables, fixed_y_maxlen=8192, fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64,
+                top_n=16, num_init_blocks=1, num_local_blocks=2, window_size=512, sm_scale=None):
+    """q [t,qh,d] new tokens (t = sum of chunk lengths), k/v caches already holding those tokens, w [t,qh,3] ->
+    o [t,qh,d].  Mutates the caches: pooled rows are written at cmp_slot_mapping."""
+    assert k.size(1) % 128 == 0
+    if sm_scale is None:
+        sm_scale = q.size(-1) ** -0.5
+    hp = dict(kernel_size=kernel_size, stride=stride)
+    mean_pooling_prefill(k, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
+    mean_pooling_prefill(v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
+    cmp_o, lse = cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
+                                  sm_scale=sm_scale, **hp)
+    topk = topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
+                        fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks, sm_scale=sm_scale,
+                        block_size=block_size, top_n=top_n, num_inital=num_init_blocks, num_local=num_local_blocks, **hp)
+    slc_o, _ = slc_attn_prefill(q, k, v, topk, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
+                                block_size=block_size, top_n=top_n, sm_scale=sm_scale)
+    swa_o = swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
+                        window_size=window_size, sm_scale=sm_scale)
+    return combine_prefill(cmp_o, slc_o, swa_o, w)
+
+
+def nsa_decode(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits=0, slc_num_splits=0,
+               fixed_y_maxlen=8192, fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64, top_n=16,
+               num_init_blocks=1, num_local_blocks=2, window_size=512, sm_scale=None):
+    """One new token per sequence: q [b,qh,d], w [b,qh,3] -> o [b,qh,d].  Rows with context_len == 0 (graph padding)
+    produce zeros.  The split arguments are accepted for source compatibility (this build does not split the KV range)."""
+    assert k.size(1) % 128 == 0
+    if sm_scale is None:
+        sm_scale = q.size(-1) ** -0.5
+    hp = dict(kernel_size=kernel_size, stride=stride)
+    kv_mean_pooling_decode(k, v, block_table=block_tables, slot_mapping=cmp_slot_mapping, context_lens=context_lens, **hp)
+    cmp_o, lse = cmp_attn_decode(q, k, v, block_tables=cmp_block_tables, context_lens=context_lens, num_splits=cmp_num_splits,
+                                 sm_scale=sm_scale, **hp)
+    topk = topk_decode(q, k, lse, fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks,
+                       block_tables=cmp_block_tables, context_lens=context_lens, block_size=block_size, top_n=top_n,
+                       num_inital=num_init_blocks, num_local=num_local_blocks, sm_scale=sm_scale, **hp)
+    slc_o, swa_o = fused_slc_swa_attn_decode(q, k, v, topk, num_splits=slc_num_splits, block_tables=block_tables,
+                                             context_lens=context_lens, block_size=block_size, top_n=top_n,
+                                             window_size=window_size, sm_scale=sm_scale)
+    return combine_decode(cmp_o, slc_o, swa_o, w)

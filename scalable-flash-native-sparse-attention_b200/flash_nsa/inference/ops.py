@@ -1,0 +1,241 @@
+"""Per-step paged-KV ops behind nsa_prefill / nsa_decode (Python surface of flash_nsa/inference/{compress_kv,
+compress_attn,topk,select_attn,combine}.py).  Hyper-parameters arrive as arguments here (the reference's inference
+functions do not read NSAHelper)."""
+import torch
+
+from .. import _lib
+from ..ops._common import S, call, ptr, status_word
+from ..ops.combine import combine_fwd
+
+
+def _i32(t):
+    assert t.dtype == torch.int32 and t.is_contiguous() or t.dim() == 2, "int32 tensors expected for lengths / tables"
+    return t
+
+
+def _hyper(kernel_size=32, stride=16, block_size=64, window=512, top_n=16, num_init=1, num_local=2):
+    h = S["NsaHyper"]()
+    h.kernel_size, h.stride, h.block_size, h.window = kernel_size, stride, block_size, window
+    h.top_n, h.num_init, h.num_local = top_n, num_init, num_local
+    return h
+
+
+class _PagedMeta:
+    """Piece table of an inference step, built with device-side ops only (no synchronisation)."""
+
+    def __init__(self, context_lens, x_cu_seqlens, x_maxlen, kv_table, cmp_table, page_size, kernel_size, stride):
+        dev = context_lens.device
+        B = context_lens.numel()
+        ctx = context_lens.to(torch.int32)
+        if x_cu_seqlens is None:      # decode: one row per sequence
+            self.piece_cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+            x_len = torch.ones(B, dtype=torch.int32, device=dev)
+            x_maxlen = 1
+        else:
+            self.piece_cu = x_cu_seqlens.to(torch.int32).contiguous()
+            x_len = self.piece_cu[1:] - self.piece_cu[:-1]
+        self.piece_off = (ctx - x_len).contiguous()                     # position of the first new token; -1 for padding rows
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.x_cu = torch.cat([zero, torch.cumsum(ctx, 0, dtype=torch.int32)]).contiguous()
+        y_len = torch.clamp((ctx - kernel_size) // stride + 1, min=0).to(torch.int32)
+        self.y_cu = torch.cat([zero, torch.cumsum(y_len, 0, dtype=torch.int32)]).contiguous()
+        self.kv_table = kv_table
+        self.cmp_table = cmp_table
+        m = S["NsaSeqMeta"]()
+        m.piece_cu, m.piece_seq, m.piece_off = ptr(self.piece_cu), 0, ptr(self.piece_off)
+        m.x_cu, m.y_cu = ptr(self.x_cu), ptr(self.y_cu)
+        m.n_pieces = m.n_seq = B
+        m.max_piece_len = int(x_maxlen)
+        m.x_maxlen, m.y_maxlen = 0, 0          # only used by training-side grids
+        m.page_size = page_size
+        if kv_table is not None:
+            assert kv_table.dtype == torch.int32 and kv_table.stride(-1) == 1
+            m.kv_table, m.kv_table_stride = ptr(kv_table), kv_table.stride(0)
+        if cmp_table is not None:
+            assert cmp_table.dtype == torch.int32 and cmp_table.stride(-1) == 1
+            m.cmp_table, m.cmp_table_stride = ptr(cmp_table), cmp_table.stride(0)
+        self.struct = m
+
+
+def _flat(cache):
+    """[pages, page, h, d] -> ([pages*page, h, d] view, page_size)"""
+    assert cache.dim() == 4 and cache.is_contiguous() and cache.dtype == torch.bfloat16
+    return cache.view(-1, cache.size(2), cache.size(3)), cache.size(1)
+
+
+def _attn_params(q, kf, vf, meta, hp, sm_scale, o, lse, lse_head_major, topk=None):
+    T, QH, D = q.shape
+    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1 and q.stride(1) == D
+    KH = kf.size(1)
+    p = S["NsaAttnParams"]()
+    p.meta, p.hp = meta.struct, hp
+    p.q, p.k, p.v, p.o, p.lse = ptr(q), ptr(kf), ptr(vf), ptr(o), ptr(lse)
+    p.q_stride_t, p.k_stride_t, p.v_stride_t, p.o_stride_t = q.stride(0), kf.stride(0), vf.stride(0), o.stride(0)
+    if lse_head_major:
+        p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
+    else:
+        p.lse_stride_t, p.lse_stride_h = lse.stride(0), 1
+    if topk is not None:
+        assert topk.dtype == torch.int32 and topk.is_contiguous()
+        p.topk, p.topk_stride_h = ptr(topk), topk.stride(0)
+        p.hp.top_n = topk.size(-1)
+    p.sm_scale = float(sm_scale)
+    p.QH, p.KH, p.D = QH, KH, D
+    p.status = ptr(status_word(q.device))
+    p.n_q_rows = T
+    return p
+
+
+# ------------------------------------------------------------------------------------------------ pooling into the cache
+def _pool(cache0, cache1, slot_mapping, block_table, y_cu_seqlens, y_maxlen, context_lens, kernel_size, stride, decode):
+    f0, page = _flat(cache0)
+    p = S["NsaPagedPoolParams"]()
+    p.cache0 = ptr(f0)
+    p.cache1 = ptr(_flat(cache1)[0]) if cache1 is not None else 0
+    p.slot_mapping, p.kv_table = ptr(slot_mapping), ptr(block_table)
+    p.y_cu, p.context_lens = ptr(y_cu_seqlens), ptr(context_lens)
+    p.row_stride = f0.stride(0)
+    p.B = block_table.size(0)
+    p.H, p.D = f0.size(1), f0.size(2)
+    p.page_size, p.table_stride = page, block_table.stride(0)
+    p.y_maxlen = int(y_maxlen) if y_maxlen is not None else 0
+    p.kernel_size, p.stride, p.decode = kernel_size, stride, int(decode)
+    assert slot_mapping.dtype == torch.int32 and block_table.dtype == torch.int32
+    call("nsa_paged_mean_pool", p, cache0)
+
+
+def mean_pooling_prefill(x, y_cu_seqlens, y_maxlen, slot_mapping, block_table, kernel_size=32, stride=16):
+    """Pool every compressed row that has a slot (slot_mapping != -1) from the paged tokens, in place."""
+    _pool(x, None, slot_mapping, block_table, y_cu_seqlens, y_maxlen, None, kernel_size, stride, False)
+    return x
+
+
+def mean_pooling_decode(x, slot_mapping, block_table, context_lens=None, kernel_size=32, stride=16):
+    _pool(x, None, slot_mapping, block_table, None, None, context_lens, kernel_size, stride, True)
+    return x
+
+
+def kv_mean_pooling_decode(k, v, slot_mapping, block_table, context_lens=None, kernel_size=32, stride=16):
+    """K and V in one launch: the window ending at the newest token, when it completes a compressed row."""
+    assert k.shape == v.shape
+    _pool(k, v, slot_mapping, block_table, None, None, context_lens, kernel_size, stride, True)
+
+
+# ------------------------------------------------------------------------------------------------ compressed attention
+def cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables, context_lens, kernel_size=32, stride=16, sm_scale=None):
+    """-> (o [t,qh,d], lse [qh,t]); `block_tables` are the pages of the compressed rows."""
+    T, QH, D = q.shape
+    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+    kf, page = _flat(k)
+    vf, _ = _flat(v)
+    meta = _PagedMeta(context_lens, x_cu_seqlens, x_maxlen, None, block_tables, page, kernel_size, stride)
+    o = torch.empty(T, QH, D, device=q.device, dtype=q.dtype)
+    lse = torch.empty(QH, T, device=q.device, dtype=torch.float32)
+    if T:
+        call("nsa_cmp_attn_fwd", _attn_params(q, kf, vf, meta, _hyper(kernel_size, stride), sm_scale, o, lse, True), q)
+    return o, lse
+
+
+def cmp_attn_decode(q, k, v, block_tables, context_lens, out=None, num_splits=0, max_num_splits=4, kernel_size=32, stride=16,
+                    sm_scale=None, tma=True, bench=False):
+    """-> (o [b,qh,d], lse [b,qh])"""
+    B, QH, D = q.shape
+    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+    kf, page = _flat(k)
+    vf, _ = _flat(v)
+    meta = _PagedMeta(context_lens, None, 1, None, block_tables, page, kernel_size, stride)
+    o = torch.empty(B, QH, D, device=q.device, dtype=q.dtype) if out is None else out
+    lse = torch.empty(B, QH, device=q.device, dtype=torch.float32)
+    if B:
+        call("nsa_cmp_attn_fwd", _attn_params(q, kf, vf, meta, _hyper(kernel_size, stride), sm_scale, o, lse, False), q)
+    return o, lse
+
+
+# ------------------------------------------------------------------------------------------------ top-n
+def _topk(q, k, lse, lse_head_major, meta_args, block_size, top_n, num_inital, num_local, kernel_size, stride, sm_scale):
+    T, QH, D = q.shape
+    kf, page = _flat(k)
+    KH = kf.size(1)
+    meta = _PagedMeta(*meta_args, page, kernel_size, stride)
+    topk = torch.empty(KH, T, top_n, dtype=torch.int32, device=q.device)
+    p = S["NsaTopkParams"]()
+    p.meta, p.hp = meta.struct, _hyper(kernel_size, stride, block_size, 0, top_n, num_inital, num_local)
+    p.q, p.ck, p.lse, p.topk, p.probs = ptr(q), ptr(kf), ptr(lse), ptr(topk), 0
+    p.q_stride_t, p.ck_stride_t = q.stride(0), kf.stride(0)
+    if lse_head_major:
+        p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
+    else:
+        p.lse_stride_t, p.lse_stride_h = lse.stride(0), 1
+    p.sm_scale = float(D ** -0.5 if sm_scale is None else sm_scale)
+    p.QH, p.KH, p.D = QH, KH, D
+    p.ignore_index, p.quant = -1, 0        # block scores stay in fp32 here (the reference rounds per-row scores to half)
+    if T:
+        call("nsa_slc_topk", p, q)
+    return topk
+
+
+@torch.no_grad()
+def topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables, context_lens, fixed_y_maxlen=8192,
+                 fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64, top_n=16, num_inital=1, num_local=2,
+                 sm_scale=None, fp32=False):
+    """-> topk [kh,t,top_n] int32, unused slots = -1"""
+    return _topk(q, k, lse, True, (context_lens, x_cu_seqlens, x_maxlen, None, block_tables), block_size, top_n, num_inital,
+                 num_local, kernel_size, stride, sm_scale)
+
+
+@torch.no_grad()
+def topk_decode(q, k, lse, block_tables, context_lens, kernel_size=32, stride=16, block_size=64, top_n=16, num_inital=1,
+                num_local=2, fixed_num_slc_blocks=2048, fixed_y_maxlen=8192, sm_scale=None, persistent=False, workers=4):
+    """-> topk [kh,b,top_n] int32, unused slots = -1; lse is [b,qh]"""
+    return _topk(q, k, lse, False, (context_lens, None, 1, None, block_tables), block_size, top_n, num_inital, num_local,
+                 kernel_size, stride, sm_scale)
+
+
+# ------------------------------------------------------------------------------------------------ selected + window attention
+def _token_branch(fn, q, k, v, meta_args, hp, sm_scale, topk=None):
+    T, QH, D = q.shape
+    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+    kf, page = _flat(k)
+    vf, _ = _flat(v)
+    meta = _PagedMeta(*meta_args, page, hp.kernel_size, hp.stride)
+    o = torch.empty(T, QH, D, device=q.device, dtype=q.dtype)
+    lse = torch.empty(T, QH, device=q.device, dtype=torch.float32)
+    if T:
+        call(fn, _attn_params(q, kf, vf, meta, hp, sm_scale, o, lse, False, topk), q)
+    return o, lse
+
+
+def slc_attn_prefill(q, k, v, topk, x_cu_seqlens, x_maxlen, block_tables, context_lens, block_size=64, top_n=16, sm_scale=None):
+    return _token_branch("nsa_slc_attn_fwd", q, k, v, (context_lens, x_cu_seqlens, x_maxlen, block_tables, None),
+                         _hyper(block_size=block_size, top_n=top_n), sm_scale, topk)
+
+
+def slc_attn_decode(q, k, v, topk, block_tables, context_lens, block_size=64, top_n=16, num_splits=4, out=None, sm_scale=None,
+                    bench=False):
+    return _token_branch("nsa_slc_attn_fwd", q, k, v, (context_lens, None, 1, block_tables, None),
+                         _hyper(block_size=block_size, top_n=top_n), sm_scale, topk)
+
+
+def swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables, context_lens, window_size=512, sm_scale=None):
+    """Sliding-window attention of the new tokens over the paged cache (the reference calls flash-attn here,
+    flash_nsa/inference/__init__.py:125-155)."""
+    return _token_branch("nsa_swa_fwd", q, k, v, (context_lens, x_cu_seqlens, x_maxlen, block_tables, None),
+                         _hyper(window=window_size), sm_scale)[0]
+
+
+def fused_slc_swa_attn_decode(q, k, v, topk, block_tables, context_lens, out=None, num_splits=0, max_num_splits=4, block_size=64,
+                              top_n=16, window_size=512, sm_scale=None, bench=False):
+    """-> (slc_o, swa_o), each [b,qh,d].  Two launches here (selected blocks, window)."""
+    slc_o, _ = slc_attn_decode(q, k, v, topk, block_tables, context_lens, block_size, top_n, sm_scale=sm_scale)
+    swa_o, _ = _token_branch("nsa_swa_fwd", q, k, v, (context_lens, None, 1, block_tables, None), _hyper(window=window_size),
+                             sm_scale)
+    return slc_o, swa_o
+
+
+# ------------------------------------------------------------------------------------------------ combine
+def combine_prefill(a, b, c, w, out=None):
+    return combine_fwd(a, b, c, w, out=out)
+
+
+def combine_decode(a, b, c, w, out=None):
+    return combine_fwd(a, b, c, w, out=out)

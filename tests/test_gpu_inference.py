@@ -1,0 +1,169 @@
+"""Paged-KV prefill / chunked prefill / decode against the CPU oracle run on the un-paged sequences
+(the reference validates its paged ops the same way: against the training ops on the same tokens)."""
+import pytest
+import torch
+
+from oracle import nsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+PAGE = 128
+
+
+class Cache:
+    """A toy block manager: token pages and compressed-row pages come from one shuffled free list."""
+
+    def __init__(self, lens, KH, D, seed):
+        g = torch.Generator().manual_seed(seed)
+        self.lens = lens
+        self.y_lens = [max((L - 32) // 16 + 1, 0) for L in lens]
+        n_tok = [O.cdiv(L, PAGE) for L in lens]
+        n_cmp = [max(O.cdiv(y, PAGE), 1) for y in self.y_lens]
+        total = sum(n_tok) + sum(n_cmp) + 3
+        free = torch.randperm(total, generator=g).tolist()
+        self.k = torch.zeros(total, PAGE, KH, D, dtype=torch.bfloat16)
+        self.v = torch.zeros(total, PAGE, KH, D, dtype=torch.bfloat16)
+        w1, w2 = max(n_tok), max(n_cmp)
+        self.block_tables = torch.full((len(lens), w1), -1, dtype=torch.int32)
+        self.cmp_block_tables = torch.full((len(lens), w2), -1, dtype=torch.int32)
+        for b in range(len(lens)):
+            for i in range(n_tok[b]):
+                self.block_tables[b, i] = free.pop()
+            for i in range(n_cmp[b]):
+                self.cmp_block_tables[b, i] = free.pop()
+
+    def store(self, b, k, v, start=0):
+        for i in range(k.size(0)):
+            p = start + i
+            pg = int(self.block_tables[b, p // PAGE])
+            self.k[pg, p % PAGE] = k[i]
+            self.v[pg, p % PAGE] = v[i]
+
+    def cmp_slot(self, b, j):
+        return int(self.cmp_block_tables[b, j // PAGE]) * PAGE + j % PAGE
+
+    def cuda(self):
+        self.k, self.v = self.k.cuda(), self.v.cuda()
+        self.block_tables, self.cmp_block_tables = self.block_tables.cuda(), self.cmp_block_tables.cuda()
+        return self
+
+
+def _seqs(lens, QH, KH, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for L in lens:
+        out.append(dict(q=torch.randn(L, QH, D, generator=g).bfloat16(), k=torch.randn(L, KH, D, generator=g).bfloat16(),
+                        v=torch.randn(L, KH, D, generator=g).bfloat16(), w=torch.randn(L, QH, 3, generator=g).bfloat16()))
+    return out
+
+
+def _oracle(s, L):
+    """oracle output for the first L tokens of one sequence, computed with bf16-rounded pooled rows like the kernels"""
+    q, k, v, w = s["q"][:L].float(), s["k"][:L].float(), s["v"][:L].float(), s["w"][:L].float()
+    cu = [0, L]
+    ck = O.mean_pool(k, cu).bfloat16().float()
+    cv = O.mean_pool(v, cu).bfloat16().float()
+    cmp_o, lse = O.cmp_attn(q, ck, cv, cu)
+    topk = O.topk_select(O.slc_scores(q, ck, lse, cu), cu)
+    slc_o, _ = O.slc_attn(q, k, v, topk, cu)
+    swa_o, _ = O.swa(q, k, v, cu)
+    return O.combine(cmp_o, slc_o, swa_o, w)
+
+
+def _bulk_ok(got, ref):
+    err = (got.float().cpu() - ref).abs().flatten()
+    # a flipped near-tie of the selection moves single rows; judge the bulk and require finiteness
+    return err.kthvalue(max(1, int(0.998 * err.numel()))).values.item() <= TOL and bool(torch.isfinite(got).all())
+
+
+@pytest.mark.parametrize("QH,KH,D", [(8, 2, 64), (16, 4, 128)])
+def test_prefill_chunked_prefill_and_decode(QH, KH, D):
+    import flash_nsa
+    from flash_nsa import nsa_prefill, nsa_decode
+    lens = [700, 330, 1025]
+    seqs = _seqs(lens, QH, KH, D, seed=3 + D)
+    # ------------------------------------------------------------------ 1. one-shot prefill of a prefix
+    prefix = [448, 100, 777]
+    cache = Cache([L + 4 for L in lens], KH, D, seed=9)
+    for b, s in enumerate(seqs):
+        cache.store(b, s["k"][:prefix[b]], s["v"][:prefix[b]])
+    cache.cuda()
+
+    def prefill(start, end):
+        x_len = [e - s_ for s_, e in zip(start, end)]
+        x_cu = torch.tensor([0] + torch.tensor(x_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+        y_len = [max((e - 32) // 16 + 1, 0) for e in end]
+        y_cu = torch.tensor([0] + torch.tensor(y_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+        slots = []
+        for b in range(len(lens)):
+            for j in range(y_len[b]):
+                new = 16 * j + 31 >= start[b]          # the window ends inside the new tokens
+                slots.append(cache.cmp_slot(b, j) if new else -1)
+        q = torch.cat([seqs[b]["q"][start[b]:end[b]] for b in range(len(lens))]).cuda()
+        w = torch.cat([seqs[b]["w"][start[b]:end[b]] for b in range(len(lens))]).cuda()
+        o = nsa_prefill(q, cache.k, cache.v, w, x_cu, y_cu, max(x_len), max(y_len),
+                        torch.tensor(end, dtype=torch.int32, device="cuda"), cache.block_tables,
+                        torch.tensor(slots, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+        return o, x_len
+
+    o, x_len = prefill([0, 0, 0], prefix)
+    off = 0
+    for b in range(len(lens)):
+        assert _bulk_ok(o[off:off + x_len[b]], _oracle(seqs[b], prefix[b])), f"prefill seq {b}"
+        off += x_len[b]
+
+    # ------------------------------------------------------------------ 2. chunked prefill of the rest on top of the prefix
+    end = [L - 1 for L in lens]
+    for b, s in enumerate(seqs):
+        cache_cpu_k, cache_cpu_v = s["k"][prefix[b]:end[b]], s["v"][prefix[b]:end[b]]
+        for i in range(cache_cpu_k.size(0)):
+            p = prefix[b] + i
+            pg = int(cache.block_tables[b, p // PAGE])
+            cache.k[pg, p % PAGE] = cache_cpu_k[i].cuda()
+            cache.v[pg, p % PAGE] = cache_cpu_v[i].cuda()
+    o, x_len = prefill(prefix, end)
+    off = 0
+    for b in range(len(lens)):
+        ref = _oracle(seqs[b], end[b])[prefix[b]:]
+        assert _bulk_ok(o[off:off + x_len[b]], ref), f"chunked prefill seq {b}"
+        off += x_len[b]
+
+    # ------------------------------------------------------------------ 3. decode the last token (+ one padding row)
+    for b, s in enumerate(seqs):
+        p = lens[b] - 1
+        pg = int(cache.block_tables[b, p // PAGE])
+        cache.k[pg, p % PAGE] = s["k"][p].cuda()
+        cache.v[pg, p % PAGE] = s["v"][p].cuda()
+    ctx = lens + [0]
+    slot = []
+    for b, L in enumerate(lens):
+        has_new = (L % 16 == 0) and L >= 32
+        slot.append(cache.cmp_slot(b, (L - 32) // 16) if has_new else -1)
+    slot.append(-1)
+    pad = lambda t: torch.cat([t, torch.full((1, t.size(1)), -1, dtype=torch.int32, device="cuda")])
+    q = torch.stack([seqs[b]["q"][lens[b] - 1] for b in range(len(lens))] + [torch.zeros(QH, D).bfloat16()]).cuda()
+    w = torch.stack([seqs[b]["w"][lens[b] - 1] for b in range(len(lens))] + [torch.zeros(QH, 3).bfloat16()]).cuda()
+    o = nsa_decode(q, cache.k, cache.v, w, torch.tensor(ctx, dtype=torch.int32, device="cuda"), pad(cache.block_tables),
+                   torch.tensor(slot, dtype=torch.int32, device="cuda"), pad(cache.cmp_block_tables))
+    for b in range(len(lens)):
+        ref = _oracle(seqs[b], lens[b])[-1:]
+        assert (o[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"decode seq {b}"
+    assert float(o[-1].float().abs().max()) == 0.0      # padding row: no tokens -> zeros
+
+
+def test_decode_writes_the_new_compressed_row():
+    from flash_nsa.inference import kv_mean_pooling_decode
+    KH, D = 2, 64
+    L = 160                                   # multiple of 16: the decode step completes compressed row (160-32)/16 = 8
+    s = _seqs([L], 4, KH, D, seed=5)[0]
+    cache = Cache([L], KH, D, seed=1)
+    cache.store(0, s["k"], s["v"])
+    cache.cuda()
+    slot = cache.cmp_slot(0, 8)
+    kv_mean_pooling_decode(cache.k, cache.v, torch.tensor([slot], dtype=torch.int32, device="cuda"), cache.block_tables,
+                           torch.tensor([L], dtype=torch.int32, device="cuda"))
+    ref_k = O.mean_pool(s["k"].float(), [0, L])[8]
+    ref_v = O.mean_pool(s["v"].float(), [0, L])[8]
+    got_k = cache.k.view(-1, KH, D)[slot].float().cpu()
+    got_v = cache.v.view(-1, KH, D)[slot].float().cpu()
+    assert (got_k - ref_k).abs().max().item() <= 8e-3 and (got_v - ref_v).abs().max().item() <= 8e-3
