@@ -146,6 +146,7 @@ def main():
     ap.add_argument("--no-kernel-breakdown", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
+    ap.add_argument("--no-inference", action="store_true", help="skip the paged decode / chunked prefill measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -290,11 +291,95 @@ def main():
     if roofline:
         line["roofline"] = roofline
         line["kernels_ms"] = kernels
+    if world == 1 and not args.no_inference:
+        line["inference"] = inference_bench(dev)
     if cpu:
         line["cpu_baseline"] = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def inference_bench(dev):
+    """BASELINE config 4: paged decode (batch 64, contexts U[4096,8192]) and a chunked prefill of 2048 new tokens on a
+    6144-token prefix; 32 q heads / 8 kv heads / d = 128, page 256, shuffled page table, seeded N(0,1) cache contents."""
+    import random
+    from flash_nsa import nsa_decode, nsa_prefill
+    qh, kh, d, page = 32, 8, 128, 256
+    rng = random.Random(1004)
+    B = 64
+    ctx = [rng.randint(4096, 8192) for _ in range(B)]
+    n_tok = [-(-L // page) for L in ctx]
+    n_cmp = [-(-max((L - 32) // 16 + 1, 1) // page) for L in ctx]
+    P, Cn = 6144, 2048                     # the chunked-prefill sequence gets page lists of its own
+    L1 = P + Cn
+    pre_tok, pre_cmp = -(-L1 // page), -(-((L1 - 32) // 16 + 1) // page)
+    total = sum(n_tok) + sum(n_cmp) + pre_tok + pre_cmp
+    free = list(range(total))
+    rng.shuffle(free)
+    g = torch.Generator(device=dev).manual_seed(1004)
+    kc = torch.randn(total, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+    vc = torch.randn(total, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+    bt = torch.full((B, max(n_tok)), -1, dtype=torch.int32)
+    cbt = torch.full((B, max(n_cmp)), -1, dtype=torch.int32)
+    for b in range(B):
+        for i in range(n_tok[b]):
+            bt[b, i] = free.pop()
+        for i in range(n_cmp[b]):
+            cbt[b, i] = free.pop()
+    slot = torch.tensor([(int(cbt[b, ((L - 32) // 16) // page]) * page + ((L - 32) // 16) % page) if L % 16 == 0 else -1
+                         for b, L in enumerate(ctx)], dtype=torch.int32, device=dev)
+    pbt = torch.tensor([[free.pop() for _ in range(pre_tok)]], dtype=torch.int32, device=dev)
+    pcbt = torch.tensor([[free.pop() for _ in range(pre_cmp)]], dtype=torch.int32, device=dev)
+    assert not free
+    bt, cbt = bt.to(dev), cbt.to(dev)
+    ctx_d = torch.tensor(ctx, dtype=torch.int32, device=dev)
+    q = torch.randn(B, qh, d, device=dev, dtype=torch.bfloat16, generator=g)
+    w = torch.randn(B, qh, 3, device=dev, dtype=torch.bfloat16, generator=g)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    dec = lambda: nsa_decode(q, kc, vc, w, ctx_d, bt, slot, cbt)
+    ms_eager = timed(dec, 20)
+    graph = torch.cuda.CUDAGraph()
+    dec()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        out = dec()
+    ms_graph = timed(graph.replay, 50)
+    # bytes a decode step must read: compressed K (twice: attention and scoring) + compressed V, 16 selected blocks and
+    # 513 window rows of K and V, per sequence and kv head
+    row = kh * d * 2
+    alg_bytes = sum(3 * ((L - 32) // 16 + 1) * row + 2 * (16 * 64 + 513) * row for L in ctx)
+    # chunked prefill: one sequence, 2048 new tokens after 6144 cached ones
+    L = L1
+    xcu = torch.tensor([0, Cn], dtype=torch.int32, device=dev)
+    ylen = (L - 32) // 16 + 1
+    ycu = torch.tensor([0, ylen], dtype=torch.int32, device=dev)
+    pc_host = pcbt[0].tolist()
+    slots = torch.tensor([(pc_host[j // page] * page + j % page) if 16 * j + 31 >= P else -1 for j in range(ylen)],
+                         dtype=torch.int32, device=dev)
+    qp = torch.randn(Cn, qh, d, device=dev, dtype=torch.bfloat16, generator=g)
+    wp = torch.randn(Cn, qh, 3, device=dev, dtype=torch.bfloat16, generator=g)
+    ctx1 = torch.tensor([L], dtype=torch.int32, device=dev)
+    ms_pre = timed(lambda: nsa_prefill(qp, kc, vc, wp, xcu, ycu, Cn, ylen, ctx1, pbt, slots, pcbt), 10)
+    peak_tf, peak_gbs, src = load_peaks()
+    return {"workload": "decode batch 64, contexts U[4096,8192] (seed 1004), 32 q heads / 8 kv heads / d=128, page 256, shuffled "
+                        "page table; chunked prefill 2048 new tokens on a 6144-token prefix",
+            "decode_ms_eager": ms_eager, "decode_ms_cuda_graph": ms_graph, "decode_tokens_per_s": B / (ms_graph * 1e-3),
+            "decode_algorithmic_gb": alg_bytes / 1e9, "decode_hbm_gbs": alg_bytes / (ms_graph * 1e-3) / 1e9,
+            "decode_hbm_frac": alg_bytes / (ms_graph * 1e-3) / 1e9 / peak_gbs, "hbm_peak_gbs": peak_gbs, "peak_source": src,
+            "prefill_chunk_ms": ms_pre, "prefill_tokens_per_s": Cn / (ms_pre * 1e-3)}
 
 
 def kernel_breakdown(q, k, v, w, do, lens):
