@@ -167,17 +167,20 @@ typedef struct NsaTopkParams {
   const float* lse; /* log-sum-exp of the compressed branch (addressing as in NsaAttnParams)              */
   int32_t* topk;    /* out [KH,Tq,top_n]; unused slots keep ignore_index                                  */
   void* probs;      /* optional out [KH,Tq,probs_stride_t] block scores (fp16 or fp32 per quant), or NULL  */
+  int32_t* status;  /* optional device word for pipeline time-outs, as in NsaAttnParams                   */
   int64_t q_stride_t, ck_stride_t, lse_stride_t, lse_stride_h, probs_stride_t;
   float sm_scale;
   int32_t QH, KH, D;
   int32_t ignore_index;
   int32_t quant; /* what the selection compares: 0 = fp32 score, 1 = score rounded to fp16,
                     2 = score^3 rounded to fp16 (the reference default below 128K tokens)                  */
-  int32_t reserved0;
-  int32_t reserved1;
+  int32_t q_rows;  /* rows of the q tensor and of the ck tensor: bounds of the bulk tensor loads           */
+  int32_t ck_rows;
 } NsaTopkParams;
 /* replaces slc_topk_indices_for_32_16_64 (kernel pair _slc_probs_kernel + _topk_kernel),
- * flash_nsa/ops/topk.py:499-628; scores and selection are fused, no [KH,T,blocks] scratch is needed.      */
+ * flash_nsa/ops/topk.py:499-628; scores and selection are fused, no [KH,T,blocks] scratch is needed.
+ * Contiguous (non-paged) inputs with top_n - num_init - num_local == 13 run on the TMA + tcgen05 kernel (any number
+ * of query heads per kv head); paged caches and other list sizes run on the warp-MMA kernel (<= 16 heads per kv head). */
 int nsa_slc_topk(const NsaTopkParams* p, void* stream);
 
 typedef struct NsaK2qParams {

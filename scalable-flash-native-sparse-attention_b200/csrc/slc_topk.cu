@@ -193,12 +193,15 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
 
 using namespace nsa;
 
+namespace nsa {
+int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, cudaStream_t st);  // slc_topk_tc.cu
+}
+
 extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
   NSA_REQUIRE(p && p->q && p->ck && p->lse && p->topk, NSA_ERR_BAD_ARG, "slc_topk: null tensor pointer");
   NSA_REQUIRE(p->meta.piece_cu && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "slc_topk: null metadata pointer");
   NSA_REQUIRE(p->D == 64 || p->D == 128, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: head dim %d not supported (64 or 128)", p->D);
   NSA_REQUIRE(p->KH > 0 && p->QH % p->KH == 0, NSA_ERR_BAD_ARG, "slc_topk: QH=%d must be a multiple of KH=%d", p->QH, p->KH);
-  NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: at most 16 query heads per kv head (got %d)", p->QH / p->KH);
   NSA_REQUIRE(p->hp.kernel_size == 32 && p->hp.stride == 16 && p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE,
               "slc_topk: only kernel_size=32, stride=16, block_size=64 is implemented (got %d/%d/%d)", p->hp.kernel_size,
               p->hp.stride, p->hp.block_size);
@@ -207,6 +210,13 @@ extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
               "slc_topk: num_init + num_local exceeds top_n");
   NSA_REQUIRE(p->quant >= 0 && p->quant <= 2, NSA_ERR_BAD_ARG, "slc_topk: quant=%d", p->quant);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
+  if (p->q_rows > 0 && p->ck_rows > 0 && p->QH / p->KH <= 64) {
+    int rc = launch_slc_topk_tc(p, p->q_rows, p->ck_rows, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+  }
+  NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE,
+              "slc_topk: this configuration runs on the warp-MMA kernel, which takes at most 16 query heads per kv head (got %d)",
+              p->QH / p->KH);
   const int D = p->D;
   size_t smem = (size_t)128 * D * 2 + 2 * 64 * D * 2 + 8 * 72 * sizeof(float);
   cudaError_t e = cudaSuccess;

@@ -1,0 +1,317 @@
+// Block-importance scores + top-n selection on the Blackwell tensor core, operands staged by TMA.
+//
+// CTA = 128 consecutive query tokens x one kv head.  MMA rows are TOKENS (one query head per MMA), so a thread owns
+// one token for the whole kernel and everything after the MMA is thread-local:
+//   for each tile of 128 compressed rows, for each query head h of the kv head (in order h = 0..G-1):
+//       S_h = Q_h K^T                      tcgen05.mma, Q_h tile [128 tokens x d] and K tile [128 rows x d] loaded by TMA
+//       acc[c] += exp2(S_h[c]*c - lse_h)   the thread's 128 columns, fp32, heads accumulated in order
+//   mask the rows the token cannot see yet, pool 4 -> 1 (+ the row before) into 31 selection blocks and merge them
+//   into the thread's sorted list of the best free blocks (value descending, block index ascending).
+// A tile starts one compressed row early and advances by 124 rows, so the "row before" of its first block is inside
+// the tile and tiles are independent.  Two warp groups take the even / odd tiles of the SAME tokens, so one TMA load of
+// Q_h feeds two MMAs; a ninth warp issues all TMA loads and MMAs.  At the end group 1's list is merged into group 0's.
+// Nothing but the [kh, t, top_n] indices is written (optionally the block scores, for inspection).
+#include <cuda.h>
+#include "tc_common.cuh"
+
+namespace nsa {
+
+namespace {
+
+constexpr int kList = 13;  // free slots per row handled by this kernel: top_n - num_init - num_local
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool better(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
+
+struct TopList {
+  float v[kList];
+  int i[kList];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int k = 0; k < kList; ++k) {
+      v[k] = -1.f;
+      i[k] = 0x7fffffff;
+    }
+  }
+  __device__ __forceinline__ void insert(float cv, int ci) {
+    if (!better(cv, ci, v[kList - 1], i[kList - 1])) return;
+    v[kList - 1] = cv;
+    i[kList - 1] = ci;
+#pragma unroll
+    for (int k = kList - 1; k > 0; --k) {
+      bool up = better(v[k], i[k], v[k - 1], i[k - 1]);
+      float tv = v[k - 1];
+      int ti = i[k - 1];
+      v[k - 1] = up ? v[k] : tv;
+      i[k - 1] = up ? i[k] : ti;
+      v[k] = up ? tv : v[k];
+      i[k] = up ? ti : i[k];
+    }
+  }
+};
+
+}  // namespace
+
+template <int D>
+__global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, const __grid_constant__ CUtensorMap tmq,
+                                                             const __grid_constant__ CUtensorMap tmk) {
+  using namespace tc;
+  constexpr int BM = 128, BN = 128, STEP = 124, NQ = 4, SLABS = D / 64;
+  constexpr uint32_t TILE_BYTES = BM * D * 2, SLAB_BYTES = 128 * 128;
+  constexpr uint32_t IDESC = make_idesc(BM, BN, false);
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  const uint32_t sQ = base;                       // NQ stages
+  const uint32_t sK = sQ + NQ * TILE_BYTES;       // one tile per warp group
+  const uint32_t bars = sK + 2 * TILE_BYTES;
+  const uint32_t q_full = bars, q_free = bars + 8 * NQ, k_full = bars + 16 * NQ, k_free = k_full + 16;
+  const uint32_t s_full = k_free + 16, s_free = s_full + 32, tm_slot = s_free + 32;   // s_*[wg][buf]
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int G = p.QH / p.KH;
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int kh = blockIdx.z;
+  const Piece pc = load_piece(p.meta, blockIdx.y);
+  const int t0 = tile * BM;
+  if (t0 >= pc.len) return;
+  if (base & 1023u) {
+    if (tid == 0 && p.status) atomicOr(p.status, 8);
+    return;
+  }
+  const int ntok = min(BM, pc.len - t0);
+  const int ks = p.hp.kernel_size, st = p.hp.stride, bs = p.hp.block_size;
+  const int top_n = p.hp.top_n, ni = p.hp.num_init, nl = p.hp.num_local;
+  const int tabs_max = pc.off + t0 + ntok - 1;
+  const int nvis_max = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
+  const int n_tiles = max(nvis_max / STEP + 1, max(tabs_max, 0) / bs / 31 + 1);
+  const int n_pairs = (n_tiles + 1) / 2;
+  const int N = n_pairs * G;  // MMA steps per warp group
+
+  if (tid == 0) {
+    for (int s = 0; s < NQ; ++s) {
+      mbar_init(q_full + 8 * s, 1);
+      mbar_init(q_free + 8 * s, 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(k_full + 8 * w, 1);
+      mbar_init(k_free + 8 * w, 1);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full + 8 * (2 * w + b), 1);
+        mbar_init(s_free + 8 * (2 * w + b), 128);
+      }
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(tm_slot, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  uint32_t tmem;
+  asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
+  int budget = kWaitBudget;
+  bool timed_out = false;
+
+  if (warp == 8) {
+    if ((tid & 31) == 0) {
+      // ============================================ producer: TMA loads and MMA issue
+      const int q_row0 = pc.q_start + t0;
+      int nl_ = 0;  // next step whose Q tile is to be loaded
+      auto top_up = [&](int upto) {
+        while (nl_ < N && nl_ < upto) {
+          const int s = nl_ % NQ;
+          if (nl_ >= NQ && !mbar_wait(q_free + 8 * s, ((nl_ / NQ) - 1) & 1, &budget)) timed_out = true;
+          mbar_expect_tx(q_full + 8 * s, TILE_BYTES);
+          const int head = kh * G + (nl_ % G);
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) tma_load_3d(sQ + s * TILE_BYTES + sl * SLAB_BYTES, &tmq, sl * 64, head, q_row0, q_full + 8 * s);
+          ++nl_;
+        }
+      };
+      top_up(NQ - 1);
+      for (int jp = 0; jp < n_pairs; ++jp) {
+        for (int w = 0; w < 2; ++w) {
+          if (jp > 0 && !mbar_wait(k_free + 8 * w, (jp - 1) & 1, &budget)) timed_out = true;
+          mbar_expect_tx(k_full + 8 * w, TILE_BYTES);
+          const int row = pc.y_bos + STEP * (2 * jp + w) - 1;
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) tma_load_3d(sK + w * TILE_BYTES + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, k_full + 8 * w);
+        }
+        for (int h = 0; h < G; ++h) {
+          const int n = jp * G + h, s = n % NQ, b = n & 1;
+          if (!mbar_wait(q_full + 8 * s, (n / NQ) & 1, &budget)) timed_out = true;
+          for (int w = 0; w < 2; ++w) {
+            if (h == 0 && !mbar_wait(k_full + 8 * w, jp & 1, &budget)) timed_out = true;
+            if (n >= 2 && !mbar_wait(s_free + 8 * (2 * w + b), ((n >> 1) - 1) & 1, &budget)) timed_out = true;
+            fence_after_sync();
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+              const uint32_t off = (k >> 2) * SLAB_BYTES + (k & 3) * 32;
+              mma_ss(tmem + (2 * w + b) * 128, desc_kmajor(sQ + s * TILE_BYTES + off), desc_kmajor(sK + w * TILE_BYTES + off), IDESC, k > 0);
+            }
+            mma_commit(s_full + 8 * (2 * w + b));
+            if (h == G - 1) mma_commit(k_free + 8 * w);
+          }
+          mma_commit(q_free + 8 * s);
+          top_up(n + NQ);
+        }
+      }
+    }
+  } else {
+    // ============================================ two warp groups: even / odd tiles of the same 128 tokens
+    const int wg = warp >> 2, t = tid & 127;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const bool tok_ok = t < ntok;
+    const int t_abs = pc.off + t0 + t;
+    const int64_t q_row = pc.q_start + t0 + (tok_ok ? t : 0);
+    const int nvis = (tok_ok && t_abs >= ks - 1) ? min(pc.y_len, (t_abs - (ks - 1)) / st + 1) : 0;
+    const int nk = (tok_ok && t_abs >= 0) ? t_abs / bs : -1;
+    const float c2 = p.sm_scale * 1.4426950408889634f;
+    const float* lse_p = p.lse + q_row * p.lse_stride_t + (int64_t)kh * G * p.lse_stride_h;
+    const int64_t Tq = p.meta.piece_cu[p.meta.n_pieces];
+    TopList lst;
+    lst.init();
+    float acc[BN];
+
+    for (int jp = 0; jp < n_pairs; ++jp) {
+      const int j = 2 * jp + wg;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      float nlse = -__ldg(lse_p);
+      for (int h = 0; h < G; ++h) {
+        const int n = jp * G + h, b = n & 1;
+        const float cur = nlse;
+        if (h + 1 < G) nlse = -__ldg(lse_p + (int64_t)(h + 1) * p.lse_stride_h);
+        if (!mbar_wait(s_full + 8 * (2 * wg + b), (n >> 1) & 1, &budget)) timed_out = true;
+        fence_after_sync();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t sv[32];
+          tmem_ld32(lane_base + (2 * wg + b) * 128 + q4 * 32, sv);
+          wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[q4 * 32 + i] += fast_exp2(fmaf(__uint_as_float(sv[i]), c2, cur));
+        }
+        fence_before_sync();
+        mbar_arrive(s_free + 8 * (2 * wg + b));
+      }
+      // ---- this tile's 31 blocks: column c is compressed row STEP*j - 1 + c
+      const int row0 = STEP * j - 1;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        const int r = row0 + c;
+        acc[c] = (r >= 0 && r < nvis) ? acc[c] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 31; ++i) {
+        float pv = acc[4 * i] + ((2.f * acc[4 * i + 1] + 2.f * acc[4 * i + 2]) + (2.f * acc[4 * i + 3] + acc[4 * i + 4]));
+        if (p.quant == 1) pv = __half2float(__float2half_rn(pv));
+        else if (p.quant == 2) pv = __half2float(__float2half_rn(pv * pv * pv));
+        const int blk = 31 * j + i;
+        if (p.probs && tok_ok && blk < (int)p.probs_stride_t) {
+          const int64_t a = ((int64_t)kh * Tq + q_row) * p.probs_stride_t + blk;
+          if (p.quant == 0) reinterpret_cast<float*>(p.probs)[a] = pv;
+          else reinterpret_cast<__half*>(p.probs)[a] = __float2half_rn(pv);
+        }
+        if (blk >= ni && blk <= nk - nl) lst.insert(pv, blk);
+      }
+    }
+    // ---- merge group 1's list into group 0's and write the row
+    __syncwarp();
+    float* mv = reinterpret_cast<float*>(smem_raw);            // the Q stages are idle now (all MMAs have completed)
+    int* mi = reinterpret_cast<int*>(smem_raw + 128 * kList * 4);
+    named_barrier(1, 256);
+    if (wg == 1) {
+#pragma unroll
+      for (int k = 0; k < kList; ++k) {
+        mv[k * 128 + t] = lst.v[k];
+        mi[k * 128 + t] = lst.i[k];
+      }
+    }
+    named_barrier(1, 256);
+    if (wg == 0) {
+#pragma unroll
+      for (int k = 0; k < kList; ++k) lst.insert(mv[k * 128 + t], mi[k * 128 + t]);
+      if (tok_ok) {
+        const int n_free = max(0, min(top_n, nk + 1) - ni - nl);
+        int32_t* out = p.topk + ((int64_t)kh * Tq + q_row) * top_n;
+        for (int s = 0; s < ni; ++s) out[s] = (s <= nk) ? s : p.ignore_index;
+        for (int s = 0; s < nl; ++s) out[ni + s] = (ni + s <= nk) ? nk - s : p.ignore_index;
+#pragma unroll
+        for (int r = 0; r < kList; ++r) out[ni + nl + r] = (r < n_free) ? lst.i[r] : p.ignore_index;
+      }
+    }
+  }
+  if (timed_out && p.status) atomicOr(p.status, 16);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------------- host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [rows, heads, D] bf16 tensor, box = 128 rows x 1 head x 64 elements, 128-byte swizzle, out-of-range rows read as zero
+bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, int64_t row_stride_elems) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride_elems * 2};
+  cuuint32_t box[3] = {64, 1, 128};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// returns 1 when this kernel does not cover the call (caller then uses the warp-MMA kernel), 0 on launch, <0 on error
+int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, cudaStream_t st) {
+  if (p->meta.kv_table || p->meta.cmp_table) return 1;                       // paged rows cannot be fetched as one box
+  if (p->hp.top_n - p->hp.num_init - p->hp.num_local != kList) return 1;
+  if ((p->q_stride_t * 2) % 16 || (p->ck_stride_t * 2) % 16 || ((uintptr_t)p->q & 15) || ((uintptr_t)p->ck & 15)) return 1;
+  if (ck_rows <= 0) return 1;
+  CUtensorMap tmq, tmk;
+  if (!make_map(&tmq, p->q, q_rows, p->QH, p->D, p->q_stride_t) || !make_map(&tmk, p->ck, ck_rows, p->KH, p->D, p->ck_stride_t)) {
+    set_error("slc_topk: cuTensorMapEncodeTiled failed or is unavailable");
+    return NSA_ERR_CUDA;
+  }
+  const int D = p->D;
+  size_t smem = (size_t)6 * 128 * D * 2 + 256;
+  cudaError_t e = (D == 128) ? cudaFuncSetAttribute(slc_topk_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                             : cudaFuncSetAttribute(slc_topk_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("slc_topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    return NSA_ERR_CUDA;
+  }
+  dim3 grid((p->meta.max_piece_len + 127) / 128, p->meta.n_pieces, p->KH);
+  if (D == 128) slc_topk_tc_kernel<128><<<grid, 288, smem, st>>>(*p, tmq, tmk);
+  else slc_topk_tc_kernel<64><<<grid, 288, smem, st>>>(*p, tmq, tmk);
+  return check_launch("slc_topk");
+}
+
+}  // namespace nsa

@@ -162,6 +162,7 @@ def _topk(q, k, lse, lse_head_major, meta_args, block_size, top_n, num_inital, n
     p.meta, p.hp = meta.struct, _hyper(kernel_size, stride, block_size, 0, top_n, num_inital, num_local)
     p.q, p.ck, p.lse, p.topk, p.probs = ptr(q), ptr(kf), ptr(lse), ptr(topk), 0
     p.q_stride_t, p.ck_stride_t = q.stride(0), kf.stride(0)
+    p.status = ptr(status_word(q.device))
     if lse_head_major:
         p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
     else:

@@ -3,7 +3,7 @@ selected-attention backward.  Python surface of flash_nsa/ops/topk.py."""
 import torch
 
 from ..utils import NSAHelper, cdiv
-from ._common import S, call, check_bf16_3d, hyper, is_cp, local_rows, ptr, seq_meta
+from ._common import S, call, check_bf16_3d, hyper, is_cp, local_rows, ptr, seq_meta, status_word
 
 
 @torch.no_grad()
@@ -46,12 +46,14 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     p.meta, p.hp = seq_meta(helper), hyper()
     p.q, p.ck, p.lse, p.topk, p.probs = ptr(q), ptr(k), ptr(lse), ptr(topk), ptr(probs)
     p.q_stride_t, p.ck_stride_t = q.stride(0), k.stride(0)
+    p.status = ptr(status_word(q.device))
     assert lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (QH, T)
     p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
     p.probs_stride_t = pad_blocks if probs is not None else 0
     p.sm_scale = float(sm_scale)
     p.QH, p.KH, p.D = QH, KH, D
     p.ignore_index, p.quant = ignore_index, quant
+    p.q_rows, p.ck_rows = T, k.size(0)
     call("nsa_slc_topk", p, q)
     return topk, probs
 
