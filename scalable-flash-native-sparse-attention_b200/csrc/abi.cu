@@ -32,6 +32,8 @@ int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y) {
   NSA_REQUIRE(p->KH > 0 && p->QH % p->KH == 0, NSA_ERR_BAD_ARG, "%s: QH=%d must be a multiple of KH=%d", name, p->QH, p->KH);
   NSA_REQUIRE(p->QH / p->KH <= 128, NSA_ERR_UNSUPPORTED_SHAPE, "%s: more than 128 query heads per kv head", name);
   NSA_REQUIRE(p->hp.kernel_size > 0 && p->hp.stride > 0, NSA_ERR_BAD_ARG, "%s: bad kernel_size/stride", name);
+  NSA_REQUIRE(!(p->meta.kv_table || p->meta.cmp_table) || (p->meta.page_size > 0 && (p->meta.page_size & (p->meta.page_size - 1)) == 0),
+              NSA_ERR_UNSUPPORTED_SHAPE, "%s: page_size=%d must be a power of two", name, p->meta.page_size);
   return NSA_OK;
 }
 

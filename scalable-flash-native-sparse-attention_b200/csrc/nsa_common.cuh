@@ -43,15 +43,17 @@ struct Piece {
   int y_len;     // compressed rows of the sequence
   const int32_t* x_tab;  // paged mode: this sequence's page list for token rows (else null)
   const int32_t* y_tab;  // paged mode: this sequence's page list for compressed rows (else null)
-  int page;
+  int page_shift;        // log2(page size); page sizes are powers of two
 };
 
 // flat row index (in the K/V-side tensor) of token row r / compressed row j of the piece's sequence
 __device__ __forceinline__ int64_t tok_row(const Piece& p, int r) {
-  return p.x_tab ? (int64_t)p.x_tab[r / p.page] * p.page + (r % p.page) : (int64_t)p.x_bos + r;
+  if (!p.x_tab) return (int64_t)p.x_bos + r;
+  return ((int64_t)p.x_tab[r >> p.page_shift] << p.page_shift) + (r & ((1 << p.page_shift) - 1));
 }
 __device__ __forceinline__ int64_t cmp_row(const Piece& p, int j) {
-  return p.y_tab ? (int64_t)p.y_tab[j / p.page] * p.page + (j % p.page) : (int64_t)p.y_bos + j;
+  if (!p.y_tab) return (int64_t)p.y_bos + j;
+  return ((int64_t)p.y_tab[j >> p.page_shift] << p.page_shift) + (j & ((1 << p.page_shift) - 1));
 }
 
 __device__ __forceinline__ Piece load_piece(const NsaSeqMeta& m, int b) {
@@ -69,7 +71,7 @@ __device__ __forceinline__ Piece load_piece(const NsaSeqMeta& m, int b) {
     p.y_bos = 0;
     p.y_len = 0;
   }
-  p.page = m.page_size;
+  p.page_shift = 31 - __clz(max(m.page_size, 1));
   p.x_tab = m.kv_table ? m.kv_table + (int64_t)p.seq * m.kv_table_stride : nullptr;
   p.y_tab = m.cmp_table ? m.cmp_table + (int64_t)p.seq * m.cmp_table_stride : nullptr;
   return p;

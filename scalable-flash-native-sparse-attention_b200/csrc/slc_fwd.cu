@@ -19,7 +19,7 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 }
 __device__ __forceinline__ uint32_t u4_get(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-template <int D>
+template <int D, bool PAGED>
 __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   constexpr int SS = D / 32, HH = D / 64, BS = 64;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(p.v) + kh * D + g_ * 8;
   const int32_t* idx = p.topk + (int64_t)kh * p.topk_stride_h + q_row * p.hp.top_n;
   const int last_row = pc.x_len - 1;
+  auto krow = [&](int r) -> int64_t { return PAGED ? tok_row(pc, r) : (int64_t)pc.x_bos + r; };
 
   float o[HH][8][4];
 #pragma unroll
@@ -64,7 +65,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __nv_bfloat16* kp = kb + tok_row(pc, min(key0 + nt * 8 + g_, last_row)) * p.k_stride_t;
+      const __nv_bfloat16* kp = kb + krow(min(key0 + nt * 8 + g_, last_row)) * p.k_stride_t;
       uint4 kk[SS];
 #pragma unroll
       for (int ss = 0; ss < SS; ++ss) kk[ss] = ldg_nc16(kp + 32 * ss);
@@ -127,10 +128,10 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
       uint32_t a0 = pack_bf16(s[2 * u][0], s[2 * u][1]), a1 = pack_bf16(s[2 * u][2], s[2 * u][3]);
       uint32_t a2 = pack_bf16(s[2 * u + 1][0], s[2 * u + 1][1]), a3 = pack_bf16(s[2 * u + 1][2], s[2 * u + 1][3]);
       const int r0 = key0 + 16 * u + 2 * c_;
-      const __nv_bfloat16* v0p = vb + tok_row(pc, min(r0, last_row)) * p.v_stride_t;
-      const __nv_bfloat16* v1p = vb + tok_row(pc, min(r0 + 1, last_row)) * p.v_stride_t;
-      const __nv_bfloat16* v2p = vb + tok_row(pc, min(r0 + 8, last_row)) * p.v_stride_t;
-      const __nv_bfloat16* v3p = vb + tok_row(pc, min(r0 + 9, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v0p = vb + krow(min(r0, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v1p = vb + krow(min(r0 + 1, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v2p = vb + krow(min(r0 + 8, last_row)) * p.v_stride_t;
+      const __nv_bfloat16* v3p = vb + krow(min(r0 + 9, last_row)) * p.v_stride_t;
 #pragma unroll
       for (int h = 0; h < HH; ++h) {
         uint4 v0 = ldg_nc16(v0p + 64 * h), v1 = ldg_nc16(v1p + 64 * h), v2 = ldg_nc16(v2p + 64 * h), v3 = ldg_nc16(v3p + 64 * h);
@@ -192,7 +193,13 @@ extern "C" int nsa_slc_attn_fwd(const NsaAttnParams* p, void* stream) {
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_fwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
   dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
-  if (p->D == 128) slc_fwd_kernel<128><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
-  else slc_fwd_kernel<64><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+  const bool paged = p->meta.kv_table != nullptr;
+  if (p->D == 128) {
+    if (paged) slc_fwd_kernel<128, true><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    else slc_fwd_kernel<128, false><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+  } else {
+    if (paged) slc_fwd_kernel<64, true><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+    else slc_fwd_kernel<64, false><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);
+  }
   return check_launch("slc_attn_fwd");
 }

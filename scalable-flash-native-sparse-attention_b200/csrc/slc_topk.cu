@@ -209,6 +209,8 @@ extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
   NSA_REQUIRE(p->hp.num_init >= 0 && p->hp.num_local >= 0 && p->hp.num_init + p->hp.num_local <= p->hp.top_n, NSA_ERR_BAD_ARG,
               "slc_topk: num_init + num_local exceeds top_n");
   NSA_REQUIRE(p->quant >= 0 && p->quant <= 2, NSA_ERR_BAD_ARG, "slc_topk: quant=%d", p->quant);
+  NSA_REQUIRE(!p->meta.cmp_table || (p->meta.page_size > 0 && (p->meta.page_size & (p->meta.page_size - 1)) == 0),
+              NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: page_size=%d must be a power of two", p->meta.page_size);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
   if (p->q_rows > 0 && p->ck_rows > 0 && p->QH / p->KH <= 64) {
     int rc = launch_slc_topk_tc(p, p->q_rows, p->ck_rows, (cudaStream_t)stream);

@@ -153,6 +153,10 @@ template <int D, bool CMP>
 __device__ __forceinline__ void fill_kv_tile_async(uint32_t tile, const __nv_bfloat16* base, int64_t stride, const Piece& pc, int row0,
                                                    int rows, int valid, int tid, int nthreads) {
   constexpr int CH = D / 8;
+  if ((CMP ? pc.y_tab : pc.x_tab) == nullptr) {  // contiguous rows: plain strided fill
+    fill_tile_async<D>(tile, base + ((int64_t)(CMP ? pc.y_bos : pc.x_bos) + row0) * stride, stride, rows, valid, tid, nthreads);
+    return;
+  }
   for (int i = tid; i < rows * CH; i += nthreads) {
     int r = i / CH, c = i % CH;
     bool ok = r < valid;
