@@ -245,6 +245,32 @@ typedef struct NsaPagedPoolParams {
  * flash_nsa/inference/compress_kv.py:191-286 */
 int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream);
 
+/* ---- fused paged decode step ---------------------------------------------------------------------------- */
+typedef struct NsaDecodeParams {
+  const void* q;               /* [B,QH,D] bf16: one new token per sequence                                          */
+  void* k_cache;               /* [pages*page_size, KH, D] bf16; also receives the new compressed row (in place)     */
+  void* v_cache;               /* same layout                                                                        */
+  const void* w;               /* [B,QH,3] bf16 gate logits                                                          */
+  void* o;                     /* [B,QH,D] bf16 out                                                                  */
+  const int32_t* context_lens; /* [B] tokens in the cache including the new one; 0 = padding row (output zeros)      */
+  const int32_t* kv_table;     /* [B, kv_table_stride] pages of the tokens                                           */
+  const int32_t* cmp_table;    /* [B, cmp_table_stride] pages of the compressed rows                                 */
+  const int32_t* slot_mapping; /* [B] flat cache row for the compressed row completed by this token, -1 = none       */
+  int32_t* topk_out;           /* optional [KH,B,top_n] selected blocks (-1 = unused slot), or NULL                  */
+  int32_t* status;             /* optional error word (bit 32: a sequence has more compressed rows than y_cap)       */
+  NsaHyper hp;
+  int64_t q_stride_t, o_stride_t, w_stride_t, cache_stride_t;
+  float sm_scale;
+  int32_t B, QH, KH, D;
+  int32_t page_size, kv_table_stride, cmp_table_stride;
+  int32_t y_cap;               /* most compressed rows a sequence may have (sizes the shared-memory score array)      */
+  int32_t reserved0;
+} NsaDecodeParams;
+/* replaces the whole body of nsa_decode, flash_nsa/inference/__init__.py:160-257 (8 launches there): pooling of the new
+ * compressed row, compressed attention, block scores + top-n, selected and sliding-window attention, gated combine,
+ * one CTA per (sequence, kv head).  Needs kernel 32 / stride 16 / block 64 and at most 16 query heads per kv head.   */
+int nsa_decode_fused(const NsaDecodeParams* p, void* stream);
+
 /* ---- context-parallel chunk reorder ------------------------------------------------------------------ */
 typedef struct NsaReorderParams {
   const void* x; /* [2*world_size chunks of chunk_bytes bytes]                                            */

@@ -10,7 +10,7 @@ any of these calls, shapes depend only on the arguments, so a decode step can be
 """
 from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
                   topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
-                  combine_prefill, combine_decode)
+                  combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported)
 
 
 def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, context_lens, block_tables, cmp_slot_mapping,
@@ -40,8 +40,25 @@ def nsa_decode(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_blo
                fixed_y_maxlen=8192, fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64, top_n=16,
                num_init_blocks=1, num_local_blocks=2, window_size=512, sm_scale=None):
     """One new token per sequence: q [b,qh,d], w [b,qh,3] -> o [b,qh,d].  Rows with context_len == 0 (graph padding)
-    produce zeros.  The split arguments are accepted for source compatibility (this build does not split the KV range)."""
+    produce zeros.  Runs as one fused launch when the configuration allows (kernel 32 / stride 16 / block 64, at most 16
+    query heads per kv head), otherwise as the sequence of per-branch ops.  The split arguments are accepted for source
+    compatibility (the fused kernel splits the KV ranges over the warps of a CTA by itself)."""
     assert k.size(1) % 128 == 0
+    if sm_scale is None:
+        sm_scale = q.size(-1) ** -0.5
+    if decode_fused_supported(q, k, kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks):
+        return nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, fixed_y_maxlen,
+                                kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks, window_size, sm_scale)
+    return nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits,
+                              slc_num_splits, fixed_y_maxlen, fixed_num_slc_blocks, kernel_size, stride, block_size, top_n,
+                              num_init_blocks, num_local_blocks, window_size, sm_scale)
+
+
+def nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits=0,
+                       slc_num_splits=0, fixed_y_maxlen=8192, fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64,
+                       top_n=16, num_init_blocks=1, num_local_blocks=2, window_size=512, sm_scale=None):
+    """The decode step as the sequence of per-branch ops (the reference's structure); used for configurations the fused
+    kernel does not cover and as a cross-check of it."""
     if sm_scale is None:
         sm_scale = q.size(-1) ** -0.5
     hp = dict(kernel_size=kernel_size, stride=stride)

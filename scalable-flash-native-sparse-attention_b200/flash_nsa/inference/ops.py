@@ -240,3 +240,41 @@ def combine_prefill(a, b, c, w, out=None):
 
 def combine_decode(a, b, c, w, out=None):
     return combine_fwd(a, b, c, w, out=out)
+
+
+# ------------------------------------------------------------------------------------------------ fused decode step
+def decode_fused_supported(q, k, kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks):
+    QH, KH, D = q.size(1), k.size(2), q.size(2)
+    page = k.size(1)
+    return (kernel_size == 32 and stride == 16 and block_size == 64 and QH % KH == 0 and QH // KH <= 16 and D in (64, 128)
+            and top_n <= 32 and num_init_blocks + num_local_blocks <= top_n and page >= 64 and page & (page - 1) == 0)
+
+
+def nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, fixed_y_maxlen=8192,
+                     kernel_size=32, stride=16, block_size=64, top_n=16, num_init_blocks=1, num_local_blocks=2, window_size=512,
+                     sm_scale=None, return_topk=False):
+    """The whole decode step in ONE launch (pooling of the new compressed row, the three branches, top-n, combine).
+    `fixed_y_maxlen` bounds the compressed rows of a sequence (it sizes a shared-memory array; 8192 = 128K tokens)."""
+    B, QH, D = q.shape
+    kf, page = _flat(k)
+    vf, _ = _flat(v)
+    KH = kf.size(1)
+    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1 and q.stride(1) == D and w.stride(-1) == 1 and w.stride(1) == 3
+    o = torch.empty(B, QH, D, device=q.device, dtype=q.dtype)
+    topk = torch.empty(KH, B, top_n, dtype=torch.int32, device=q.device) if return_topk else None
+    p = S["NsaDecodeParams"]()
+    p.q, p.k_cache, p.v_cache, p.w, p.o = ptr(q), ptr(kf), ptr(vf), ptr(w), ptr(o)
+    p.context_lens, p.kv_table, p.cmp_table = ptr(context_lens), ptr(block_tables), ptr(cmp_block_tables)
+    p.slot_mapping, p.topk_out, p.status = ptr(cmp_slot_mapping), ptr(topk), ptr(status_word(q.device))
+    p.hp = _hyper(kernel_size, stride, block_size, window_size, top_n, num_init_blocks, num_local_blocks)
+    p.q_stride_t, p.o_stride_t, p.w_stride_t, p.cache_stride_t = q.stride(0), o.stride(0), w.stride(0), kf.stride(0)
+    p.sm_scale = float(D ** -0.5 if sm_scale is None else sm_scale)
+    p.B, p.QH, p.KH, p.D = B, QH, KH, D
+    p.page_size, p.kv_table_stride, p.cmp_table_stride = page, block_tables.stride(0), cmp_block_tables.stride(0)
+    fit = ((8 * (32 + 16 * D) - 16) * 4 // 5) // 4 * 4        # what the kernel's shared-memory score array can hold
+    p.y_cap = min((int(fixed_y_maxlen) + 3) // 4 * 4, fit)
+    for t_ in (context_lens, block_tables, cmp_block_tables, cmp_slot_mapping):
+        assert t_.dtype == torch.int32
+    if B:
+        call("nsa_decode_fused", p, q)
+    return (o, topk) if return_topk else o

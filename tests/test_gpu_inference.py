@@ -143,8 +143,20 @@ def test_prefill_chunked_prefill_and_decode(QH, KH, D):
     pad = lambda t: torch.cat([t, torch.full((1, t.size(1)), -1, dtype=torch.int32, device="cuda")])
     q = torch.stack([seqs[b]["q"][lens[b] - 1] for b in range(len(lens))] + [torch.zeros(QH, D).bfloat16()]).cuda()
     w = torch.stack([seqs[b]["w"][lens[b] - 1] for b in range(len(lens))] + [torch.zeros(QH, 3).bfloat16()]).cuda()
-    o = nsa_decode(q, cache.k, cache.v, w, torch.tensor(ctx, dtype=torch.int32, device="cuda"), pad(cache.block_tables),
-                   torch.tensor(slot, dtype=torch.int32, device="cuda"), pad(cache.cmp_block_tables))
+    from flash_nsa.inference import nsa_decode_unfused, nsa_decode_fused
+    args = (q, cache.k, cache.v, w, torch.tensor(ctx, dtype=torch.int32, device="cuda"), pad(cache.block_tables),
+            torch.tensor(slot, dtype=torch.int32, device="cuda"), pad(cache.cmp_block_tables))
+    o_unfused = nsa_decode_unfused(*args)
+    o, tk = nsa_decode_fused(*args, return_topk=True)
+    assert torch.equal(o, nsa_decode(*args))           # the public entry point takes the fused path here
+    assert (o.float() - o_unfused.float()).abs().max().item() <= TOL
+    for b in range(len(lens)):                         # slot layout of the selection: forced blocks first
+        nkb = (lens[b] - 1) // 64
+        row = tk[0, b].tolist()
+        nv = min(16, nkb + 1)
+        assert row[0] == 0 and row[1] == nkb and row[2] == nkb - 1 and max(row) <= nkb
+        assert len(set(row[:nv])) == nv and min(row[:nv]) >= 0 and all(x == -1 for x in row[nv:])
+    assert tk[:, -1].eq(-1).all()
     for b in range(len(lens)):
         ref = _oracle(seqs[b], lens[b])[-1:]
         assert (o[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"decode seq {b}"
