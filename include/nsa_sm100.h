@@ -141,6 +141,8 @@ typedef struct NsaAttnParams {
   int32_t QH, KH, D;
   int32_t accumulate_dq;   /* bwd: 1 = dq += result, 0 = dq = result                                      */
   int32_t n_q_rows;        /* bwd: total number of local query rows (= piece_cu[n_pieces])                */
+  int32_t n_k_rows;        /* bwd: rows of the k / v tensors (bounds of the bulk tensor loads)            */
+  int32_t reserved1;
   int32_t n_blocks_total;  /* selected bwd: rows of the k2q table per kv head                             */
   int32_t phases;          /* bwd: 0 = run every kernel of the call; otherwise a mask, bit 0 = delta, bit 1 = dK/dV,
                               bit 2 = dQ (lets a profiler time the kernels of one call separately)         */

@@ -2,7 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
-#include "nsa_common.cuh"
+#include "tma.cuh"
 
 namespace nsa {
 
@@ -36,6 +36,37 @@ int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y) {
               NSA_ERR_UNSUPPORTED_SHAPE, "%s: page_size=%d must be a power of two", name, p->meta.page_size);
   return NSA_OK;
 }
+
+namespace tma {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, int64_t row_stride_elems, int box_rows, int box_heads) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || rows <= 0 || box_rows > 256 || box_heads > 256) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride_elems * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tma
 
 }  // namespace nsa
 

@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(128, 2) dense_dq_tc_kernel(NsaAttnParams p) {
 
 template <int D, int MODE>
 int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L);  // dkdv_tc.cu
+int launch_dkdv128(const NsaAttnParams* p, cudaStream_t st, const char* name, bool cmp, int q_chunk);   // dkdv128_tc.cu
 
 template <typename K>
 static int set_smem(K kernel, size_t smem, const char* name) {
@@ -274,6 +275,10 @@ extern "C" int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream) {
   if (ph & 1)
     launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
   if ((ph & 2) && p->meta.y_maxlen > 0) {
+    rc = launch_dkdv128(p, st, "cmp_attn_bwd(dkdv)", true, 2048);
+    if (rc < 0) return rc;
+  }
+  if ((ph & 2) && p->meta.y_maxlen > 0 && rc == 1) {
     DkdvLaunch L{2048, 1, nullptr};
     dim3 grid((p->meta.y_maxlen + 63) / 64, (p->meta.max_piece_len + L.q_chunk - 1) / L.q_chunk, p->meta.n_pieces * p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_CMP>(p, st, "cmp_attn_bwd(dkdv)", grid, L)
@@ -294,6 +299,10 @@ extern "C" int nsa_swa_bwd(const NsaAttnParams* p, void* stream) {
   if (ph & 1)
     launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
   if (ph & 2) {
+    rc = launch_dkdv128(p, st, "swa_bwd(dkdv)", false, 0);
+    if (rc < 0) return rc;
+  }
+  if ((ph & 2) && rc == 1) {
     DkdvLaunch L{0, 1, nullptr};
     dim3 grid((p->meta.max_piece_len + p->hp.window + 63) / 64 + 1, 1, p->meta.n_pieces * p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L) : launch_dkdv<64, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L);

@@ -11,8 +11,7 @@
 // the tile and tiles are independent.  Two warp groups take the even / odd tiles of the SAME tokens, so one TMA load of
 // Q_h feeds two MMAs; a ninth warp issues all TMA loads and MMAs.  At the end group 1's list is merged into group 0's.
 // Nothing but the [kh, t, top_n] indices is written (optionally the block scores, for inspection).
-#include <cuda.h>
-#include "tc_common.cuh"
+#include "tma.cuh"
 
 namespace nsa {
 
@@ -20,15 +19,6 @@ namespace {
 
 constexpr int kList = 13;  // free slots per row handled by this kernel: top_n - num_init - num_local
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ bool better(float av, int ai, float bv, int bi) { return av > bv || (av == bv && ai < bi); }
 
 struct TopList {
@@ -129,10 +119,10 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
         while (nl_ < N && nl_ < upto) {
           const int s = nl_ % NQ;
           if (nl_ >= NQ && !mbar_wait(q_free + 8 * s, ((nl_ / NQ) - 1) & 1, &budget)) timed_out = true;
-          mbar_expect_tx(q_full + 8 * s, TILE_BYTES);
+          tma::expect_tx(q_full + 8 * s, TILE_BYTES);
           const int head = kh * G + (nl_ % G);
 #pragma unroll
-          for (int sl = 0; sl < SLABS; ++sl) tma_load_3d(sQ + s * TILE_BYTES + sl * SLAB_BYTES, &tmq, sl * 64, head, q_row0, q_full + 8 * s);
+          for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sQ + s * TILE_BYTES + sl * SLAB_BYTES, &tmq, sl * 64, head, q_row0, q_full + 8 * s);
           ++nl_;
         }
       };
@@ -140,10 +130,10 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
       for (int jp = 0; jp < n_pairs; ++jp) {
         for (int w = 0; w < 2; ++w) {
           if (jp > 0 && !mbar_wait(k_free + 8 * w, (jp - 1) & 1, &budget)) timed_out = true;
-          mbar_expect_tx(k_full + 8 * w, TILE_BYTES);
+          tma::expect_tx(k_full + 8 * w, TILE_BYTES);
           const int row = pc.y_bos + STEP * (2 * jp + w) - 1;
 #pragma unroll
-          for (int sl = 0; sl < SLABS; ++sl) tma_load_3d(sK + w * TILE_BYTES + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, k_full + 8 * w);
+          for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sK + w * TILE_BYTES + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, k_full + 8 * w);
         }
         for (int h = 0; h < G; ++h) {
           const int n = jp * G + h, s = n % NQ, b = n & 1;
@@ -257,38 +247,6 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-namespace {
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// [rows, heads, D] bf16 tensor, box = 128 rows x 1 head x 64 elements, 128-byte swizzle, out-of-range rows read as zero
-bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, int64_t row_stride_elems) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)rows};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride_elems * 2};
-  cuuint32_t box[3] = {64, 1, 128};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-}  // namespace
-
 // returns 1 when this kernel does not cover the call (caller then uses the warp-MMA kernel), 0 on launch, <0 on error
 int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, cudaStream_t st) {
   if (p->meta.kv_table || p->meta.cmp_table) return 1;                       // paged rows cannot be fetched as one box
@@ -296,7 +254,8 @@ int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, 
   if ((p->q_stride_t * 2) % 16 || (p->ck_stride_t * 2) % 16 || ((uintptr_t)p->q & 15) || ((uintptr_t)p->ck & 15)) return 1;
   if (ck_rows <= 0) return 1;
   CUtensorMap tmq, tmk;
-  if (!make_map(&tmq, p->q, q_rows, p->QH, p->D, p->q_stride_t) || !make_map(&tmk, p->ck, ck_rows, p->KH, p->D, p->ck_stride_t)) {
+  if (!tma::make_map(&tmq, p->q, q_rows, p->QH, p->D, p->q_stride_t, 128, 1) ||
+      !tma::make_map(&tmk, p->ck, ck_rows, p->KH, p->D, p->ck_stride_t, 128, 1)) {
     set_error("slc_topk: cuTensorMapEncodeTiled failed or is unavailable");
     return NSA_ERR_CUDA;
   }

@@ -1,0 +1,26 @@
+// TMA (bulk tensor copy) helpers: tensor-map creation on the host through the driver entry point, and the device-side
+// load + transaction-count barrier instructions.  Only plain per-CTA loads are used (no cluster multicast).
+#pragma once
+#include <cuda.h>
+#include "tc_common.cuh"
+
+namespace nsa {
+namespace tma {
+
+__device__ __forceinline__ void load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Map of a [rows, heads, D] bf16 tensor (row stride given in elements) with a box of box_rows x box_heads x 64 elements and
+// the 128-byte swizzle: the box lands in shared memory as (box_rows*box_heads) rows of 128 bytes, row-major over
+// (row, head), in the operand layout of tc_common.cuh.  Out-of-range rows read as zero.  Returns false on failure.
+bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, int64_t row_stride_elems, int box_rows, int box_heads);
+
+}  // namespace tma
+}  // namespace nsa

@@ -122,5 +122,5 @@ def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_majo
     p.sm_scale = float(sm_scale)
     p.QH, p.KH, p.D = QH, KH, D
     p.status = ptr(status_word(q.device))
-    p.n_q_rows = T
+    p.n_q_rows, p.n_k_rows = T, k.size(0)
     return p
