@@ -10,6 +10,7 @@ namespace nsa {
 constexpr int MODE_SLC = 2;
 template <int D, int MODE>
 int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L);
+int launch_slc_tma(const NsaAttnParams* p, cudaStream_t st, bool backward);   // slc_tma.cu
 void launch_delta(const void* o, const void* dout, float* delta, int64_t T, int H, int D, int64_t o_stride_t,
                   int64_t do_stride_t, int64_t lse_stride_t, int64_t lse_stride_h, cudaStream_t st);
 int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y);
@@ -188,6 +189,8 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
     if (rc) return rc;
   }
   if (!(ph & 4)) return check_launch("slc_attn_bwd");
+  rc = launch_slc_tma(p, st, true);
+  if (rc != 1) return rc;
   dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
   if (p->D == 128) slc_dq_kernel<128><<<grid, 128, 0, st>>>(*p);
   else slc_dq_kernel<64><<<grid, 128, 0, st>>>(*p);

@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
 }
 
 int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y);
+int launch_slc_tma(const NsaAttnParams* p, cudaStream_t st, bool backward);   // slc_tma.cu
 
 }  // namespace nsa
 
@@ -192,6 +193,8 @@ extern "C" int nsa_slc_attn_fwd(const NsaAttnParams* p, void* stream) {
   NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_fwd: at most 16 query heads per kv head (got %d)", p->QH / p->KH);
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_fwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
+  rc = launch_slc_tma(p, (cudaStream_t)stream, false);   // contiguous K/V: TMA-staged tiles
+  if (rc != 1) return rc;
   dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
   const bool paged = p->meta.kv_table != nullptr;
   if (p->D == 128) {
