@@ -13,7 +13,7 @@ namespace nsa {
 
 namespace {
 
-constexpr int kWarps = 6;
+constexpr int kWarps = 7;
 
 // 16 x 16 A fragments of a [16 heads x D] row-major global matrix (row r at base + r*D), rows >= G clamped
 template <int D>
