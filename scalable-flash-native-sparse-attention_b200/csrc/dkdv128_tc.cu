@@ -10,7 +10,9 @@
 //     dV  += P^T dO          A = P^T from tensor memory, B = dO tile read MN-major
 //     dK  += dS^T Q
 // S^T/dP^T are double-buffered in tensor memory (2 x 128 columns) next to dV and dK (2 x 128 columns); Q/dO tiles go
-// through a 3-stage shared-memory ring filled by TMA.  Warp 4 (one lane) issues all TMA loads and MMAs.
+// through a 3-stage shared-memory ring filled by TMA.  Warp 8 (one lane) issues all TMA loads and MMAs; warps 0-3 and
+// 4-7 are two compute groups that take the even and the odd query tiles, so the softmax arithmetic of one tile overlaps the
+// tensor-memory round trips of the other.
 #include "tma.cuh"
 
 namespace nsa {
@@ -19,7 +21,7 @@ constexpr int MODE_CMP = 0;
 constexpr int MODE_SWA = 1;
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(288, 1)
     dkdv128_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
                       const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
@@ -34,10 +36,10 @@ __global__ void __launch_bounds__(160, 1)
   const uint32_t sQ = sV + KV_BYTES;            // NS stages
   const uint32_t sO = sQ + NS * Q_BYTES;        // NS stages
   const uint32_t meta_off = 2 * KV_BYTES + 2 * NS * Q_BYTES;
-  float* sLse = reinterpret_cast<float*>(smem_raw + meta_off);   // [2][64]
-  float* sDl = sLse + 2 * BQ;
-  int* sTa = reinterpret_cast<int*>(sDl + 2 * BQ);
-  const uint32_t bars = base + meta_off + 6 * BQ * 4;
+  float* sLse = reinterpret_cast<float*>(smem_raw + meta_off);   // [4][64]: two buffers per compute warp group
+  float* sDl = sLse + 4 * BQ;
+  int* sTa = reinterpret_cast<int*>(sDl + 4 * BQ);
+  const uint32_t bars = base + meta_off + 12 * BQ * 4;
   const uint32_t kv_full = bars, q_full = bars + 8, q_free = q_full + 8 * NS, sd_full = q_free + 8 * NS, pds_full = sd_full + 16,
                  done = pds_full + 16, tm_slot = done + 8;
 
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(160, 1)
   int budget = kWaitBudget;
   bool timed_out = false;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if ((tid & 31) == 0) {
       // ============================================ producer: TMA loads + MMA issue
       tma::expect_tx(kv_full, 2 * KV_BYTES);
@@ -152,13 +154,14 @@ __global__ void __launch_bounds__(160, 1)
       mma_commit(done);
     }
   } else {
-    // ============================================ compute warp group: thread = K/V row
-    const int t = tid;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    // ============================================ two compute warp groups: group w takes the tiles of parity w;
+    // thread = K/V row (tensor-memory lane)
+    const int t = tid & 127, wg = warp >> 2;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int key = k0 + t;
     const bool key_ok = t < kv_rows;
     const float c2 = p.sm_scale * 1.4426950408889634f;
-    // column metadata of a tile: lse, delta, absolute position (-1 = no such query row); loaded one tile ahead
+    // column metadata of a tile: -lse, delta, absolute position (-1 = no such query row); loaded one tile ahead
     float m_lse = 0.f, m_dl = 0.f;
     int m_ta = -1;
     auto fetch_meta = [&](int i) {
@@ -169,78 +172,96 @@ __global__ void __launch_bounds__(160, 1)
         if (n < TOKQ && tok < r_hi) {
           const int64_t q_row = (int64_t)pc.q_start + tok;
           const int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h;
-          m_lse = p.lse[a];
+          m_lse = -p.lse[a];
           m_dl = p.delta[a];
           m_ta = pc.off + tok;
         }
       }
     };
-    fetch_meta(0);
-    for (int i = 0; i < n_it; ++i) {
-      const int b = i & 1;
+    fetch_meta(wg);
+    int j = 0;
+    for (int i = wg; i < n_it; i += 2, ++j) {
+      const int b = wg, mb = 2 * wg + (j & 1);   // mb: metadata buffer, last read two of this group's tiles ago
       if (t < BQ) {
-        sLse[b * BQ + t] = m_lse;
-        sDl[b * BQ + t] = m_dl;
-        sTa[b * BQ + t] = m_ta;
+        sLse[mb * BQ + t] = m_lse;
+        sDl[mb * BQ + t] = m_dl;
+        sTa[mb * BQ + t] = m_ta;
       }
-      fetch_meta(i + 1);
-      named_barrier(1, 128);  // metadata of tile i visible to the group (buffer b was last read for tile i-2)
+      fetch_meta(i + 2);
+      named_barrier(1 + wg, 128);
+      // every (key, query) pair of the tile visible?  then the position test is skipped
+      const int tok0 = r_lo + i * TOKQ, ta_min = pc.off + tok0, ta_max = ta_min + TOKQ - 1;
+      bool full = kv_rows == BK && tok0 + TOKQ <= r_hi;
+      if (MODE == MODE_CMP) full = full && ((k0 + BK - 1) * st + ks - 1 <= ta_min);
+      else full = full && (k0 + BK - 1 <= ta_min) && (ta_max - k0 <= W);
       if (!mbar_wait(sd_full + 8 * b, (i >> 1) & 1, &budget)) timed_out = true;
       fence_after_sync();
-      const float* lse_s = sLse + b * BQ;
-      const float* dl_s = sDl + b * BQ;
-      const int* ta_s = sTa + b * BQ;
-      uint32_t pp[32], dd[32];
+      const float4* lse4 = reinterpret_cast<const float4*>(sLse + mb * BQ);
+      const float4* dl4 = reinterpret_cast<const float4*>(sDl + mb * BQ);
+      const int4* ta4 = reinterpret_cast<const int4*>(sTa + mb * BQ);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dv[32];
+        uint32_t sv[32], dv[32], pp[16], dd[16];
         tmem_ld32(lane_base + 128 * b + half * 32, sv);
         tmem_ld32(lane_base + 128 * b + 64 + half * 32, dv);
         wait_ld();
+        if (full) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = half * 32 + c + e;
-            const int ta = ta_s[col];
-            bool vis = key_ok;
-            if (MODE == MODE_CMP) vis = vis && (key * st + ks - 1 <= ta);
-            else vis = vis && (key <= ta) && (ta - key <= W);
-            const float x = vis ? fast_exp2(fmaf(__uint_as_float(sv[c + e]), c2, -lse_s[col])) : 0.f;
-            pv[e] = x;
-            ds[e] = x * (__uint_as_float(dv[c + e]) - dl_s[col]);
+          for (int c = 0; c < 32; c += 4) {
+            const float4 nl = lse4[half * 8 + (c >> 2)], dl = dl4[half * 8 + (c >> 2)];
+            const float x0 = fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x));
+            const float x1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y));
+            const float x2 = fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z));
+            const float x3 = fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w));
+            pp[c >> 1] = pack_bf16(x0, x1);
+            pp[(c >> 1) + 1] = pack_bf16(x2, x3);
+            dd[c >> 1] = pack_bf16(x0 * (__uint_as_float(dv[c]) - dl.x), x1 * (__uint_as_float(dv[c + 1]) - dl.y));
+            dd[(c >> 1) + 1] = pack_bf16(x2 * (__uint_as_float(dv[c + 2]) - dl.z), x3 * (__uint_as_float(dv[c + 3]) - dl.w));
           }
-          pp[half * 16 + (c >> 1)] = pack_bf16(pv[0], pv[1]);
-          dd[half * 16 + (c >> 1)] = pack_bf16(ds[0], ds[1]);
+        } else {
+          // visible iff lo <= ta <= hi for this thread's key
+          int lo, hi;
+          if (MODE == MODE_CMP) { lo = key * st + ks - 1; hi = 0x7fffffff; }
+          else { lo = key; hi = key + W; }
+          if (!key_ok) lo = 0x7fffffff;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const float4 nl = lse4[half * 8 + (c >> 2)], dl = dl4[half * 8 + (c >> 2)];
+            const int4 ta = ta4[half * 8 + (c >> 2)];
+            const float x0 = (ta.x >= lo && ta.x <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x)) : 0.f;
+            const float x1 = (ta.y >= lo && ta.y <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y)) : 0.f;
+            const float x2 = (ta.z >= lo && ta.z <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z)) : 0.f;
+            const float x3 = (ta.w >= lo && ta.w <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w)) : 0.f;
+            pp[c >> 1] = pack_bf16(x0, x1);
+            pp[(c >> 1) + 1] = pack_bf16(x2, x3);
+            dd[c >> 1] = pack_bf16(x0 * (__uint_as_float(dv[c]) - dl.x), x1 * (__uint_as_float(dv[c + 1]) - dl.y));
+            dd[(c >> 1) + 1] = pack_bf16(x2 * (__uint_as_float(dv[c + 2]) - dl.z), x3 * (__uint_as_float(dv[c + 3]) - dl.w));
+          }
         }
+        tmem_st16(lane_base + 128 * b + half * 16, pp);        // P^T over the consumed S^T columns
+        tmem_st16(lane_base + 128 * b + 64 + half * 16, dd);   // dS^T over dP^T
       }
-      tmem_st32(lane_base + 128 * b, pp);        // P^T over S^T (columns 0..31 of the buffer half)
-      tmem_st32(lane_base + 128 * b + 64, dd);   // dS^T over dP^T
       wait_st();
       fence_before_sync();
       mbar_arrive(pds_full + 8 * b);
     }
     if (!mbar_wait(done, 0, &budget)) timed_out = true;
     fence_after_sync();
-    // ---- my K/V row of dV and dK
-    float* dvp = p.dv + (kv_bos + k0 + t) * p.dv_stride_t + kh * D;
-    float* dkp = p.dk + (kv_bos + k0 + t) * p.dk_stride_t + kh * D;
+    // ---- my K/V row: group 0 adds dV, group 1 adds dK
+    float* dst = (wg == 0 ? p.dv + (kv_bos + k0 + t) * p.dv_stride_t : p.dk + (kv_bos + k0 + t) * p.dk_stride_t) + kh * D;
+    const float sc = wg == 0 ? 1.f : p.sm_scale;
+    const uint32_t src = lane_base + (wg == 0 ? TM_DV : TM_DK);
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
-      uint32_t v[32], k[32];
-      tmem_ld32(lane_base + TM_DV + c * 32, v);
-      tmem_ld32(lane_base + TM_DK + c * 32, k);
+      uint32_t v[32];
+      tmem_ld32(src + c * 32, v);
       wait_ld();
       if (key_ok) {
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          atomicAdd(reinterpret_cast<float4*>(dvp + c * 32 + q4 * 4),
-                    make_float4(__uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]), __uint_as_float(v[q4 * 4 + 2]), __uint_as_float(v[q4 * 4 + 3])));
-          atomicAdd(reinterpret_cast<float4*>(dkp + c * 32 + q4 * 4),
-                    make_float4(__uint_as_float(k[q4 * 4]) * p.sm_scale, __uint_as_float(k[q4 * 4 + 1]) * p.sm_scale,
-                                __uint_as_float(k[q4 * 4 + 2]) * p.sm_scale, __uint_as_float(k[q4 * 4 + 3]) * p.sm_scale));
-        }
+        for (int q4 = 0; q4 < 8; ++q4)
+          atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + q4 * 4),
+                    make_float4(__uint_as_float(v[q4 * 4]) * sc, __uint_as_float(v[q4 * 4 + 1]) * sc, __uint_as_float(v[q4 * 4 + 2]) * sc,
+                                __uint_as_float(v[q4 * 4 + 3]) * sc));
       }
     }
   }
@@ -268,7 +289,7 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, 
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable", name);
     return NSA_ERR_CUDA;
   }
-  size_t smem = (size_t)(2 * 128 + 6 * 64) * D * 2 + 6 * 64 * 4 + 256;
+  size_t smem = (size_t)(2 * 128 + 6 * 64) * D * 2 + 12 * 64 * 4 + 256;
   cudaError_t e = cudaFuncSetAttribute(dkdv128_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
@@ -278,7 +299,7 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, 
   dim3 grid;
   if (MODE == MODE_CMP) grid = dim3((p->meta.y_maxlen + 127) / 128, (p->meta.max_piece_len + q_chunk - 1) / q_chunk, p->meta.n_pieces * p->KH);
   else grid = dim3((p->meta.max_piece_len + p->hp.window + 127) / 128 + 1, 1, p->meta.n_pieces * p->KH);
-  dkdv128_tc_kernel<D, MODE><<<grid, 160, smem, st>>>(*p, L, tmq, tmo, tmk, tmv);
+  dkdv128_tc_kernel<D, MODE><<<grid, 288, smem, st>>>(*p, L, tmq, tmo, tmk, tmv);
   return check_launch(name);
 }
 
