@@ -1,18 +1,18 @@
 // dK/dV of the compressed and sliding-window branches with 128-row K/V tiles (tcgen05 + tensor memory, TMA loads).
 //
 // These two branches read their queries from a CONTIGUOUS token range, so a query tile is one TMA box
-// (64 d) x (G heads) x (64/G tokens) per 64-wide slab, and a 128-row K/V tile halves the number of times every Q/dO row is
-// streamed compared with a 64-row tile.  The MMA M dimension is the K/V row, so thread i of the compute warp group owns
-// K/V row i (tensor-memory lane i) and the gradients accumulate un-transposed:
-//     S^T  = K Q^T           M = 128 keys, N = 64 query rows   (A = K tile, B = Q tile, both K-major from shared memory)
+// (64 d) x (G heads) x (128/G tokens) per 64-wide slab.  The MMA M dimension is the K/V row, so thread i of a compute
+// warp group owns K/V row i (tensor-memory lane i) and the gradients accumulate un-transposed:
+//     S^T  = K Q^T           M = 128 keys, N = 128 query rows  (A = K tile, B = Q tile, both K-major from shared memory)
 //     dP^T = V dO^T
 //     P^T  = exp2(S^T*c - lse[col]),  dS^T = P^T * (dP^T - delta[col])  -> bf16, written over S^T / dP^T in tensor memory
 //     dV  += P^T dO          A = P^T from tensor memory, B = dO tile read MN-major
 //     dK  += dS^T Q
-// S^T/dP^T are double-buffered in tensor memory (2 x 128 columns) next to dV and dK (2 x 128 columns); Q/dO tiles go
-// through a 3-stage shared-memory ring filled by TMA.  Warp 8 (one lane) issues all TMA loads and MMAs; warps 0-3 and
-// 4-7 are two compute groups that take the even and the odd query tiles, so the softmax arithmetic of one tile overlaps the
-// tensor-memory round trips of the other.
+// N = 128 halves the shared-memory reads per query row of the two score products (the A tile is re-read by every MMA).
+// Tensor memory holds S^T, dP^T, dV, dK (4 x 128 columns), so the products of one tile are ordered
+//     S^T | dP^T | dV | dK      with   exp2 running under dP^T,   dS^T under dV,   and S^T of the next tile under dK.
+// Warp 8 (one lane) issues all TMA loads and MMAs; warps 0-3 and 4-7 are two compute groups that take the query columns
+// 0-63 and 64-127 of every tile.  Q/dO tiles go through a 2-stage shared-memory ring.
 #include "tma.cuh"
 
 namespace nsa {
@@ -25,10 +25,10 @@ __global__ void __launch_bounds__(288, 1)
     dkdv128_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
                       const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
-  constexpr int BK = 128, BQ = 64, NS = 3, SLABS = D / 64;
+  constexpr int BK = 128, BQ = 128, NS = 2, SLABS = D / 64;
   constexpr uint32_t KV_BYTES = BK * D * 2, Q_BYTES = BQ * D * 2, K_SLAB = BK * 128, Q_SLAB = BQ * 128;
   constexpr uint32_t IDESC_SD = make_idesc(BK, BQ, false), IDESC_KV = make_idesc(BK, D, true);
-  constexpr uint32_t TM_DV = 256, TM_DK = 384;
+  constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
@@ -36,12 +36,12 @@ __global__ void __launch_bounds__(288, 1)
   const uint32_t sQ = sV + KV_BYTES;            // NS stages
   const uint32_t sO = sQ + NS * Q_BYTES;        // NS stages
   const uint32_t meta_off = 2 * KV_BYTES + 2 * NS * Q_BYTES;
-  float* sLse = reinterpret_cast<float*>(smem_raw + meta_off);   // [4][64]: two buffers per compute warp group
-  float* sDl = sLse + 4 * BQ;
-  int* sTa = reinterpret_cast<int*>(sDl + 4 * BQ);
-  const uint32_t bars = base + meta_off + 12 * BQ * 4;
-  const uint32_t kv_full = bars, q_full = bars + 8, q_free = q_full + 8 * NS, sd_full = q_free + 8 * NS, pds_full = sd_full + 16,
-                 done = pds_full + 16, tm_slot = done + 8;
+  float* sLse = reinterpret_cast<float*>(smem_raw + meta_off);   // [2][128]: -lse of the tile's query rows, two buffers
+  float* sDl = sLse + 2 * BQ;
+  int* sTa = reinterpret_cast<int*>(sDl + 2 * BQ);
+  const uint32_t bars = base + meta_off + 6 * BQ * 4;
+  const uint32_t kv_full = bars, q_full = bars + 8, s_full = q_full + 8 * NS, dp_full = s_full + 8, p_ready = dp_full + 8,
+                 ds_ready = p_ready + 16, dv_done = ds_ready + 16, kv_done = dv_done + 8, done = kv_done + 8, tm_slot = done + 8;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -74,14 +74,15 @@ __global__ void __launch_bounds__(288, 1)
 
   if (tid == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(q_full + 8 * s, 1);
-      mbar_init(q_free + 8 * s, 1);
+    for (int s = 0; s < NS; ++s) mbar_init(q_full + 8 * s, 1);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(p_ready + 8 * w, 128);
+      mbar_init(ds_ready + 8 * w, 128);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(sd_full + 8 * b, 1);
-      mbar_init(pds_full + 8 * b, 128);
-    }
+    mbar_init(dv_done, 1);
+    mbar_init(kv_done, 1);
     mbar_init(done, 1);
     fence_mbar_init();
   }
@@ -103,73 +104,90 @@ __global__ void __launch_bounds__(288, 1)
         tma::load_3d(sK + sl * K_SLAB, &tmk, sl * 64, kh, (int)(kv_bos + k0), kv_full);
         tma::load_3d(sV + sl * K_SLAB, &tmv, sl * 64, kh, (int)(kv_bos + k0), kv_full);
       }
-      int nl_ = 0;
-      auto top_up = [&](int upto) {
-        while (nl_ < n_it && nl_ < upto) {
-          const int s = nl_ % NS;
-          if (nl_ >= NS && !mbar_wait(q_free + 8 * s, ((nl_ / NS) - 1) & 1, &budget)) timed_out = true;
-          tma::expect_tx(q_full + 8 * s, 2 * Q_BYTES);
-          const int row = pc.q_start + r_lo + nl_ * TOKQ;
+      auto load_q = [&](int i) {  // tile i into stage i % NS (the caller has made sure the stage is free)
+        const int s = i % NS;
+        tma::expect_tx(q_full + 8 * s, 2 * Q_BYTES);
+        const int row = pc.q_start + r_lo + i * TOKQ;
 #pragma unroll
-          for (int sl = 0; sl < SLABS; ++sl) {
-            tma::load_3d(sQ + s * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, row, q_full + 8 * s);
-            tma::load_3d(sO + s * Q_BYTES + sl * Q_SLAB, &tmo, sl * 64, kh * G, row, q_full + 8 * s);
-          }
-          ++nl_;
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma::load_3d(sQ + s * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, row, q_full + 8 * s);
+          tma::load_3d(sO + s * Q_BYTES + sl * Q_SLAB, &tmo, sl * 64, kh * G, row, q_full + 8 * s);
         }
       };
-      top_up(NS - 1);
+      load_q(0);
+      if (n_it > 1) load_q(1);
       if (!mbar_wait(kv_full, 0, &budget)) timed_out = true;
-      auto issue_kv = [&](int i) {  // dV += P^T dO, dK += dS^T Q for tile i
-        const int s = i % NS, b = i & 1;
-        if (!mbar_wait(pds_full + 8 * b, (i >> 1) & 1, &budget)) timed_out = true;
-        fence_after_sync();
-#pragma unroll
-        for (int u = 0; u < BQ / 16; ++u)
-          mma_ts(tmem + TM_DV, tmem + 128 * b + u * 8, desc_mnmajor(sO + s * Q_BYTES + u * 2048, Q_SLAB), IDESC_KV, (i > 0 || u > 0));
-#pragma unroll
-        for (int u = 0; u < BQ / 16; ++u)
-          mma_ts(tmem + TM_DK, tmem + 128 * b + 64 + u * 8, desc_mnmajor(sQ + s * Q_BYTES + u * 2048, Q_SLAB), IDESC_KV, (i > 0 || u > 0));
-        mma_commit(q_free + 8 * s);
-      };
       for (int i = 0; i < n_it; ++i) {
-        const int s = i % NS, b = i & 1;
+        const int s = i % NS, ph = i & 1;
         if (!mbar_wait(q_full + 8 * s, (i / NS) & 1, &budget)) timed_out = true;
+        // S^T region: read as P^T by dV of the previous tile
+        if (i > 0 && !mbar_wait(dv_done, (i - 1) & 1, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ao = (k >> 2) * K_SLAB + (k & 3) * 32, bo = (k >> 2) * Q_SLAB + (k & 3) * 32;
-          mma_ss(tmem + 128 * b, desc_kmajor(sK + ao), desc_kmajor(sQ + s * Q_BYTES + bo), IDESC_SD, k > 0);
+          mma_ss(tmem + TM_S, desc_kmajor(sK + ao), desc_kmajor(sQ + s * Q_BYTES + bo), IDESC_SD, k > 0);
+        }
+        mma_commit(s_full);
+        // dP^T region: read as dS^T by dK of the previous tile, which also frees that tile's Q/dO stage
+        if (i > 0) {
+          if (!mbar_wait(kv_done, (i - 1) & 1, &budget)) timed_out = true;
+          fence_after_sync();
+          if (i + 1 < n_it) load_q(i + 1);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ao = (k >> 2) * K_SLAB + (k & 3) * 32, bo = (k >> 2) * Q_SLAB + (k & 3) * 32;
-          mma_ss(tmem + 128 * b + 64, desc_kmajor(sV + ao), desc_kmajor(sO + s * Q_BYTES + bo), IDESC_SD, k > 0);
+          mma_ss(tmem + TM_DP, desc_kmajor(sV + ao), desc_kmajor(sO + s * Q_BYTES + bo), IDESC_SD, k > 0);
         }
-        mma_commit(sd_full + 8 * b);
-        if (i > 0) issue_kv(i - 1);
-        top_up(i + NS);
+        mma_commit(dp_full);
+        // dV += P^T dO: k-step u covers query rows 16u..16u+15; group w = u / 4 wrote them at columns 64w + 32h + 8e
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          if (!mbar_wait(p_ready + 8 * w, ph, &budget)) timed_out = true;
+          fence_after_sync();
+#pragma unroll
+          for (int u = 4 * w; u < 4 * w + 4; ++u)
+            mma_ts(tmem + TM_DV, tmem + TM_S + 64 * w + 32 * ((u >> 1) & 1) + 8 * (u & 1), desc_mnmajor(sO + s * Q_BYTES + u * 2048, Q_SLAB),
+                   IDESC_KV, (i > 0 || u > 0));
+        }
+        mma_commit(dv_done);
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          if (!mbar_wait(ds_ready + 8 * w, ph, &budget)) timed_out = true;
+          fence_after_sync();
+#pragma unroll
+          for (int u = 4 * w; u < 4 * w + 4; ++u)
+            mma_ts(tmem + TM_DK, tmem + TM_DP + 64 * w + 32 * ((u >> 1) & 1) + 8 * (u & 1), desc_mnmajor(sQ + s * Q_BYTES + u * 2048, Q_SLAB),
+                   IDESC_KV, (i > 0 || u > 0));
+        }
+        mma_commit(kv_done);
       }
-      issue_kv(n_it - 1);
       mma_commit(done);
     }
   } else {
-    // ============================================ two compute warp groups: group w takes the tiles of parity w;
-    // thread = K/V row (tensor-memory lane)
+    // ============================================ two compute warp groups: group w owns query columns 64w..64w+63 of
+    // every tile; thread = K/V row (tensor-memory lane)
     const int t = tid & 127, wg = warp >> 2;
-    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 64 * wg;
     const int key = k0 + t;
     const bool key_ok = t < kv_rows;
     const float c2 = p.sm_scale * 1.4426950408889634f;
+    // visible iff lo <= ta <= hi for this thread's key
+    int lo, hi;
+    if (MODE == MODE_CMP) { lo = key * st + ks - 1; hi = 0x7fffffff; }
+    else { lo = key; hi = key + W; }
+    if (!key_ok) lo = 0x7fffffff;
     // column metadata of a tile: -lse, delta, absolute position (-1 = no such query row); loaded one tile ahead
     float m_lse = 0.f, m_dl = 0.f;
     int m_ta = -1;
     auto fetch_meta = [&](int i) {
       m_lse = 0.f; m_dl = 0.f; m_ta = -1;
-      if (t < BQ && i < n_it) {
-        const int n = t / G, g = t - n * G;
+      if (t < 64 && i < n_it) {
+        const int col = 64 * wg + t;
+        const int n = col / G, g = col - n * G;
         const int tok = r_lo + i * TOKQ + n;
-        if (n < TOKQ && tok < r_hi) {
+        if (tok < r_hi) {
           const int64_t q_row = (int64_t)pc.q_start + tok;
           const int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h;
           m_lse = -p.lse[a];
@@ -178,79 +196,88 @@ __global__ void __launch_bounds__(288, 1)
         }
       }
     };
-    fetch_meta(wg);
-    int j = 0;
-    for (int i = wg; i < n_it; i += 2, ++j) {
-      const int b = wg, mb = 2 * wg + (j & 1);   // mb: metadata buffer, last read two of this group's tiles ago
-      if (t < BQ) {
-        sLse[mb * BQ + t] = m_lse;
-        sDl[mb * BQ + t] = m_dl;
-        sTa[mb * BQ + t] = m_ta;
+    fetch_meta(0);
+    for (int i = 0; i < n_it; ++i) {
+      const int ph = i & 1;
+      const int mo = ph * BQ + 64 * wg;   // this group's 64 columns of metadata buffer ph
+      if (t < 64) {
+        sLse[mo + t] = m_lse;
+        sDl[mo + t] = m_dl;
+        sTa[mo + t] = m_ta;
       }
-      fetch_meta(i + 2);
-      named_barrier(1 + wg, 128);
+      fetch_meta(i + 1);
+      named_barrier(1 + wg, 128);   // buffer ph was last read two tiles ago, before the previous tile's barrier
       // every (key, query) pair of the tile visible?  then the position test is skipped
       const int tok0 = r_lo + i * TOKQ, ta_min = pc.off + tok0, ta_max = ta_min + TOKQ - 1;
       bool full = kv_rows == BK && tok0 + TOKQ <= r_hi;
       if (MODE == MODE_CMP) full = full && ((k0 + BK - 1) * st + ks - 1 <= ta_min);
       else full = full && (k0 + BK - 1 <= ta_min) && (ta_max - k0 <= W);
-      if (!mbar_wait(sd_full + 8 * b, (i >> 1) & 1, &budget)) timed_out = true;
+      const float4* lse4 = reinterpret_cast<const float4*>(sLse + mo);
+      const float4* dl4 = reinterpret_cast<const float4*>(sDl + mo);
+      const int4* ta4 = reinterpret_cast<const int4*>(sTa + mo);
+      float x[64];
+      // ---- P^T = exp2(S^T c - lse), written over S^T while dP^T is being multiplied
+      if (!mbar_wait(s_full, ph, &budget)) timed_out = true;
       fence_after_sync();
-      const float4* lse4 = reinterpret_cast<const float4*>(sLse + mb * BQ);
-      const float4* dl4 = reinterpret_cast<const float4*>(sDl + mb * BQ);
-      const int4* ta4 = reinterpret_cast<const int4*>(sTa + mb * BQ);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dv[32], pp[16], dd[16];
-        tmem_ld32(lane_base + 128 * b + half * 32, sv);
-        tmem_ld32(lane_base + 128 * b + 64 + half * 32, dv);
+        uint32_t sv[32], pp[16];
+        tmem_ld32(lane_base + TM_S + half * 32, sv);
         wait_ld();
         if (full) {
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            const float4 nl = lse4[half * 8 + (c >> 2)], dl = dl4[half * 8 + (c >> 2)];
-            const float x0 = fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x));
-            const float x1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y));
-            const float x2 = fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z));
-            const float x3 = fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w));
-            pp[c >> 1] = pack_bf16(x0, x1);
-            pp[(c >> 1) + 1] = pack_bf16(x2, x3);
-            dd[c >> 1] = pack_bf16(x0 * (__uint_as_float(dv[c]) - dl.x), x1 * (__uint_as_float(dv[c + 1]) - dl.y));
-            dd[(c >> 1) + 1] = pack_bf16(x2 * (__uint_as_float(dv[c + 2]) - dl.z), x3 * (__uint_as_float(dv[c + 3]) - dl.w));
+            const float4 nl = lse4[half * 8 + (c >> 2)];
+            x[half * 32 + c] = fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x));
+            x[half * 32 + c + 1] = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y));
+            x[half * 32 + c + 2] = fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z));
+            x[half * 32 + c + 3] = fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w));
           }
         } else {
-          // visible iff lo <= ta <= hi for this thread's key
-          int lo, hi;
-          if (MODE == MODE_CMP) { lo = key * st + ks - 1; hi = 0x7fffffff; }
-          else { lo = key; hi = key + W; }
-          if (!key_ok) lo = 0x7fffffff;
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            const float4 nl = lse4[half * 8 + (c >> 2)], dl = dl4[half * 8 + (c >> 2)];
+            const float4 nl = lse4[half * 8 + (c >> 2)];
             const int4 ta = ta4[half * 8 + (c >> 2)];
-            const float x0 = (ta.x >= lo && ta.x <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x)) : 0.f;
-            const float x1 = (ta.y >= lo && ta.y <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y)) : 0.f;
-            const float x2 = (ta.z >= lo && ta.z <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z)) : 0.f;
-            const float x3 = (ta.w >= lo && ta.w <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w)) : 0.f;
-            pp[c >> 1] = pack_bf16(x0, x1);
-            pp[(c >> 1) + 1] = pack_bf16(x2, x3);
-            dd[c >> 1] = pack_bf16(x0 * (__uint_as_float(dv[c]) - dl.x), x1 * (__uint_as_float(dv[c + 1]) - dl.y));
-            dd[(c >> 1) + 1] = pack_bf16(x2 * (__uint_as_float(dv[c + 2]) - dl.z), x3 * (__uint_as_float(dv[c + 3]) - dl.w));
+            x[half * 32 + c] = (ta.x >= lo && ta.x <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c]), c2, nl.x)) : 0.f;
+            x[half * 32 + c + 1] = (ta.y >= lo && ta.y <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 1]), c2, nl.y)) : 0.f;
+            x[half * 32 + c + 2] = (ta.z >= lo && ta.z <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 2]), c2, nl.z)) : 0.f;
+            x[half * 32 + c + 3] = (ta.w >= lo && ta.w <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[c + 3]), c2, nl.w)) : 0.f;
           }
         }
-        tmem_st16(lane_base + 128 * b + half * 16, pp);        // P^T over the consumed S^T columns
-        tmem_st16(lane_base + 128 * b + 64 + half * 16, dd);   // dS^T over dP^T
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) pp[c >> 1] = pack_bf16(x[half * 32 + c], x[half * 32 + c + 1]);
+        tmem_st16(lane_base + TM_S + half * 32, pp);
       }
       wait_st();
       fence_before_sync();
-      mbar_arrive(pds_full + 8 * b);
+      mbar_arrive(p_ready + 8 * wg);
+      // ---- dS^T = P^T (dP^T - delta), written over dP^T while dV is being accumulated
+      if (!mbar_wait(dp_full, ph, &budget)) timed_out = true;
+      fence_after_sync();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t dv[32], dd[16];
+        tmem_ld32(lane_base + TM_DP + half * 32, dv);
+        wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float4 dl = dl4[half * 8 + (c >> 2)];
+          dd[c >> 1] = pack_bf16(x[half * 32 + c] * (__uint_as_float(dv[c]) - dl.x), x[half * 32 + c + 1] * (__uint_as_float(dv[c + 1]) - dl.y));
+          dd[(c >> 1) + 1] =
+              pack_bf16(x[half * 32 + c + 2] * (__uint_as_float(dv[c + 2]) - dl.z), x[half * 32 + c + 3] * (__uint_as_float(dv[c + 3]) - dl.w));
+        }
+        tmem_st16(lane_base + TM_DP + half * 32, dd);
+      }
+      wait_st();
+      fence_before_sync();
+      mbar_arrive(ds_ready + 8 * wg);
     }
     if (!mbar_wait(done, 0, &budget)) timed_out = true;
     fence_after_sync();
     // ---- my K/V row: group 0 adds dV, group 1 adds dK
     float* dst = (wg == 0 ? p.dv + (kv_bos + k0 + t) * p.dv_stride_t : p.dk + (kv_bos + k0 + t) * p.dk_stride_t) + kh * D;
     const float sc = wg == 0 ? 1.f : p.sm_scale;
-    const uint32_t src = lane_base + (wg == 0 ? TM_DV : TM_DK);
+    const uint32_t src = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (wg == 0 ? TM_DV : TM_DK);
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       uint32_t v[32];
@@ -275,13 +302,13 @@ __global__ void __launch_bounds__(288, 1)
 template <int D, int MODE>
 static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, int q_chunk) {
   const int G = p->QH / p->KH;
-  if (G > 64 || (64 % G) != 0) return 1;
+  if (G > 128 || (128 % G) != 0) return 1;
   if (p->meta.kv_table || p->meta.cmp_table || p->n_k_rows <= 0 || p->n_q_rows <= 0) return 1;
   if (((uintptr_t)p->q | (uintptr_t)p->dout | (uintptr_t)p->k | (uintptr_t)p->v) & 15) return 1;
   if ((p->q_stride_t * 2) % 16 || (p->do_stride_t * 2) % 16 || (p->k_stride_t * 2) % 16 || (p->v_stride_t * 2) % 16) return 1;
   if ((p->dk_stride_t % 4) || (p->dv_stride_t % 4) || (((uintptr_t)p->dk | (uintptr_t)p->dv) & 15)) return 1;
   CUtensorMap tmq, tmo, tmk, tmv;
-  const int TOKQ = 64 / G;
+  const int TOKQ = 128 / G;
   if (!tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, TOKQ, G) ||
       !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, TOKQ, G) ||
       !tma::make_map(&tmk, p->k, p->n_k_rows, p->KH, D, p->k_stride_t, 128, 1) ||
@@ -289,7 +316,7 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, 
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable", name);
     return NSA_ERR_CUDA;
   }
-  size_t smem = (size_t)(2 * 128 + 6 * 64) * D * 2 + 12 * 64 * 4 + 256;
+  size_t smem = (size_t)(2 * 128 + 4 * 128) * D * 2 + 6 * 128 * 4 + 256;
   cudaError_t e = cudaFuncSetAttribute(dkdv128_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
