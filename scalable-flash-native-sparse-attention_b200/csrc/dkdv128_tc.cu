@@ -10,7 +10,7 @@
 //     dK  += dS^T Q
 // N = 128 halves the shared-memory reads per query row of the two score products (the A tile is re-read by every MMA).
 // Tensor memory holds S^T, dP^T, dV, dK (4 x 128 columns), so the products of one tile are ordered
-//     S^T | dP^T | dV | dK      with   exp2 running under dP^T,   dS^T under dV,   and S^T of the next tile under dK.
+//     S^T(i) | dK(i-1) | dP^T(i) | dV(i)     with exp2 of tile i running under dK(i-1) and dP^T(i), and dS^T under dV(i).
 // Warp 8 (one lane) issues all TMA loads and MMAs; warps 0-3 and 4-7 are two compute groups that take the query columns
 // 0-63 and 64-127 of every tile.  Q/dO tiles go through a 2-stage shared-memory ring.
 #include "tma.cuh"
@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(288, 1)
   int* sTa = reinterpret_cast<int*>(sDl + 2 * BQ);
   const uint32_t bars = base + meta_off + 6 * BQ * 4;
   const uint32_t kv_full = bars, q_full = bars + 8, s_full = q_full + 8 * NS, dp_full = s_full + 8, p_ready = dp_full + 8,
-                 ds_ready = p_ready + 16, dv_done = ds_ready + 16, kv_done = dv_done + 8, done = kv_done + 8, tm_slot = done + 8;
+                 ds_ready = p_ready + 8, kv_done = ds_ready + 8, done = kv_done + 8, tm_slot = done + 8;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -77,11 +77,8 @@ __global__ void __launch_bounds__(288, 1)
     for (int s = 0; s < NS; ++s) mbar_init(q_full + 8 * s, 1);
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(p_ready + 8 * w, 128);
-      mbar_init(ds_ready + 8 * w, 128);
-    }
-    mbar_init(dv_done, 1);
+    mbar_init(p_ready, 256);
+    mbar_init(ds_ready, 256);
     mbar_init(kv_done, 1);
     mbar_init(done, 1);
     fence_mbar_init();
@@ -117,11 +114,21 @@ __global__ void __launch_bounds__(288, 1)
       load_q(0);
       if (n_it > 1) load_q(1);
       if (!mbar_wait(kv_full, 0, &budget)) timed_out = true;
+      auto issue_dk = [&](int i) {  // dK += dS^T Q of tile i; k-step u covers query rows 16u..16u+15, which group
+        const int s = i % NS;       // w = u / 4 wrote at columns 64w + 32h + 8e of the dP^T region
+        if (!mbar_wait(ds_ready, i & 1, &budget)) timed_out = true;
+        fence_after_sync();
+#pragma unroll
+        for (int u = 0; u < BQ / 16; ++u)
+          mma_ts(tmem + TM_DK, tmem + TM_DP + 64 * (u >> 2) + 32 * ((u >> 1) & 1) + 8 * (u & 1),
+                 desc_mnmajor(sQ + s * Q_BYTES + u * 2048, Q_SLAB), IDESC_KV, (i > 0 || u > 0));
+        mma_commit(kv_done);
+      };
+      // MMAs of one thread execute in issue order, so a product may overwrite a tensor-memory region that an earlier
+      // product still reads as its A operand; barriers are needed only against the compute groups and the TMA loads.
       for (int i = 0; i < n_it; ++i) {
         const int s = i % NS, ph = i & 1;
         if (!mbar_wait(q_full + 8 * s, (i / NS) & 1, &budget)) timed_out = true;
-        // S^T region: read as P^T by dV of the previous tile
-        if (i > 0 && !mbar_wait(dv_done, (i - 1) & 1, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -129,40 +136,25 @@ __global__ void __launch_bounds__(288, 1)
           mma_ss(tmem + TM_S, desc_kmajor(sK + ao), desc_kmajor(sQ + s * Q_BYTES + bo), IDESC_SD, k > 0);
         }
         mma_commit(s_full);
-        // dP^T region: read as dS^T by dK of the previous tile, which also frees that tile's Q/dO stage
-        if (i > 0) {
-          if (!mbar_wait(kv_done, (i - 1) & 1, &budget)) timed_out = true;
-          fence_after_sync();
-          if (i + 1 < n_it) load_q(i + 1);
-        }
+        if (i > 0) issue_dk(i - 1);   // runs while the compute groups turn S^T of tile i into P^T
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ao = (k >> 2) * K_SLAB + (k & 3) * 32, bo = (k >> 2) * Q_SLAB + (k & 3) * 32;
           mma_ss(tmem + TM_DP, desc_kmajor(sV + ao), desc_kmajor(sO + s * Q_BYTES + bo), IDESC_SD, k > 0);
         }
         mma_commit(dp_full);
-        // dV += P^T dO: k-step u covers query rows 16u..16u+15; group w = u / 4 wrote them at columns 64w + 32h + 8e
-#pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          if (!mbar_wait(p_ready + 8 * w, ph, &budget)) timed_out = true;
-          fence_after_sync();
-#pragma unroll
-          for (int u = 4 * w; u < 4 * w + 4; ++u)
-            mma_ts(tmem + TM_DV, tmem + TM_S + 64 * w + 32 * ((u >> 1) & 1) + 8 * (u & 1), desc_mnmajor(sO + s * Q_BYTES + u * 2048, Q_SLAB),
-                   IDESC_KV, (i > 0 || u > 0));
+        if (i > 0 && i + 1 < n_it) {  // the stage of tile i-1 is free once its dK is done
+          if (!mbar_wait(kv_done, (i - 1) & 1, &budget)) timed_out = true;
+          load_q(i + 1);
         }
-        mma_commit(dv_done);
+        if (!mbar_wait(p_ready, ph, &budget)) timed_out = true;
+        fence_after_sync();
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          if (!mbar_wait(ds_ready + 8 * w, ph, &budget)) timed_out = true;
-          fence_after_sync();
-#pragma unroll
-          for (int u = 4 * w; u < 4 * w + 4; ++u)
-            mma_ts(tmem + TM_DK, tmem + TM_DP + 64 * w + 32 * ((u >> 1) & 1) + 8 * (u & 1), desc_mnmajor(sQ + s * Q_BYTES + u * 2048, Q_SLAB),
-                   IDESC_KV, (i > 0 || u > 0));
-        }
-        mma_commit(kv_done);
+        for (int u = 0; u < BQ / 16; ++u)
+          mma_ts(tmem + TM_DV, tmem + TM_S + 64 * (u >> 2) + 32 * ((u >> 1) & 1) + 8 * (u & 1), desc_mnmajor(sO + s * Q_BYTES + u * 2048, Q_SLAB),
+                 IDESC_KV, (i > 0 || u > 0));
       }
+      issue_dk(n_it - 1);
       mma_commit(done);
     }
   } else {
@@ -250,7 +242,7 @@ __global__ void __launch_bounds__(288, 1)
       }
       wait_st();
       fence_before_sync();
-      mbar_arrive(p_ready + 8 * wg);
+      mbar_arrive(p_ready);
       // ---- dS^T = P^T (dP^T - delta), written over dP^T while dV is being accumulated
       if (!mbar_wait(dp_full, ph, &budget)) timed_out = true;
       fence_after_sync();
@@ -270,7 +262,7 @@ __global__ void __launch_bounds__(288, 1)
       }
       wait_st();
       fence_before_sync();
-      mbar_arrive(ds_ready + 8 * wg);
+      mbar_arrive(ds_ready);
     }
     if (!mbar_wait(done, 0, &budget)) timed_out = true;
     fence_after_sync();
