@@ -3,7 +3,9 @@
 // One CTA owns a 64-row K/V tile (compressed rows, a 64-key stretch of a sequence, or one selected block) and a slice
 // of the queries that see it.  Query rows come in tiles of 128 = (128/G tokens) x (G heads of the kv head), taken from
 // a contiguous token range (compressed, sliding window) or gathered through the key-block -> queries lists (selected).
-// Two warp groups of 128 threads each work on their own query tile (ping-pong) and a ninth warp issues every MMA:
+// Two warp groups of 128 threads each work on their own query tile (ping-pong), a ninth warp issues every MMA and a
+// tenth fetches the Q / dO tiles with TMA, one (64 d) x (G heads) x (1 token) box per lane, as soon as a group's
+// buffers are free:
 //     S    = Q K^T          M = query rows, N = keys      (A, B from shared memory, K-major)
 //     dP   = dO V^T
 //     P    = exp2(S*c - lse),  dS = P * (dP - delta)      thread i of the group owns row i; bf16 P, dS go to shared memory
@@ -12,7 +14,7 @@
 // Accumulating the TRANSPOSED gradients keeps every MMA at M = 128 although a K/V tile has only 64 rows.  At the end
 // lane j of the accumulator holds column j of dV (dK): each thread adds its 64 values to the fp32 dV (dK) with atomics
 // that are coalesced across a warp.
-#include "tc_common.cuh"
+#include "tma.cuh"
 
 namespace nsa {
 
@@ -30,9 +32,10 @@ __device__ __forceinline__ int find_le_tc(const int32_t* cu, int n, int x) {
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L) {
+__global__ void __launch_bounds__(320, 1)
+    dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo) {
   using namespace tc;
-  constexpr int BK = 64, BQ = 128, CH = D / 8;
+  constexpr int BK = 64, BQ = 128;
   constexpr uint32_t KV_BYTES = BK * D * 2, Q_BYTES = BQ * D * 2, P_BYTES = BQ * BK * 2;
   constexpr uint32_t Q_SLAB = BQ * 128, K_SLAB = BK * 128;
   constexpr uint32_t A_LBO = (D == 128) ? Q_SLAB : 0;  // D = 64: the second half of M re-reads the only slab (rows 64.. of the result are unused)
@@ -99,7 +102,7 @@ __global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLa
   // ---- set-up
   if (tid == 0) {
     for (int w = 0; w < 2; ++w) {
-      mbar_init(bar(0, w), 128);
+      mbar_init(bar(0, w), 1);
       mbar_init(bar(1, w), 1);
       mbar_init(bar(2, w), 128);
       mbar_init(bar(3, w), 1);
@@ -113,6 +116,10 @@ __global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLa
     fill_tile_async<D>(sV, reinterpret_cast<const __nv_bfloat16*>(p.v) + (kv_bos + k0) * p.v_stride_t + kh * D, p.v_stride_t, BK,
                        kv_rows, tid, 256);
     cp_async_commit();
+    if (TOKQ * G < BQ) {  // rows the TMA boxes never write must not hold NaN bit patterns
+      for (int i = tid; i < (int)(4 * Q_BYTES / 16); i += 256)
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(sQ0 + i * 16), "r"(0) : "memory");
+    }
     cp_async_wait<0>();
     fence_proxy_async();
   }
@@ -160,14 +167,41 @@ __global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLa
         }
       }
     }
+  } else if (warp == 9) {
+    // ================================================= TMA producer: tile `it` goes to the buffers of group it & 1
+    const int lane = tid & 31;
+    constexpr int SLABS = D / 64;
+    const int n_box = TOKQ * SLABS * 2;
+    const uint32_t tx = (uint32_t)(TOKQ * G) * D * 2 * 2;
+    for (int it = 0; it < 2 * n_round; ++it) {   // an odd tile count still fills group 1's buffers in the last round
+      const int wg = it & 1, j = it >> 1;
+      const int tok0 = r_lo + it * TOKQ;
+      // tensor rows of my first four boxes now, so that the index loads overlap the wait for the buffers
+      auto row_of = [&](int b) {
+        const int tok = min(tok0 + b / (SLABS * 2), r_hi - 1);   // past the end: a valid row again (its P, dS are zero)
+        return (MODE == MODE_SLC) ? __ldg(list + tok) : pc.q_start + tok;
+      };
+      int rows[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) rows[u] = (lane + 32 * u < n_box) ? row_of(lane + 32 * u) : 0;
+      if (j > 0 && !mbar_wait(bar(3, wg), (j - 1) & 1, &budget)) timed_out = true;   // dV/dK MMAs of tile it-2 have read them
+      if (lane == 0) tma::expect_tx(bar(0, wg), tx);
+      __syncwarp();
+      auto issue = [&](int b, int row) {
+        const int n = b / (SLABS * 2), rest = b - n * (SLABS * 2), sl = rest >> 1, which = rest & 1;
+        const uint32_t dst = (which ? sO0 : sQ0) + wg * Q_BYTES + sl * Q_SLAB + n * G * 128;
+        tma::load_3d(dst, which ? &tmo : &tmq, sl * 64, kh * G, row, bar(0, wg));
+      };
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (lane + 32 * u < n_box) issue(lane + 32 * u, rows[u]);
+      for (int b = lane + 128; b < n_box; b += 32) issue(b, row_of(b));   // only when G < 4
+    }
   } else {
     // ================================================= two warp groups, one query tile each per round
     const int wg = warp >> 2, t = tid & 127;
-    const uint32_t tQ = sQ0 + wg * Q_BYTES, tO = sO0 + wg * Q_BYTES;
     const uint32_t tP = sP0 + wg * P_BYTES, tS = sS0 + wg * P_BYTES;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)kh * G * D;
-    const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(p.dout) + (int64_t)kh * G * D;
     const float c2 = p.sm_scale * 1.4426950408889634f;
     const int my_n = t / G, my_g = t - my_n * G;
 
@@ -175,16 +209,6 @@ __global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLa
       const int it = 2 * j + wg;
       const int tok0 = r_lo + it * TOKQ;  // first token (range position / list position) of my tile
       if (j > 0 && !mbar_wait(bar(3, wg), (j - 1) & 1, &budget)) timed_out = true;  // my buffers are free again
-      for (int i = t; i < BQ * CH; i += 128) {
-        int r = i / CH, c = i % CH;
-        int n = r / G, g = r - n * G;
-        bool ok = (n < TOKQ) && (tok0 + n < r_hi);
-        int64_t q_row = 0;
-        if (ok) q_row = (MODE == MODE_SLC) ? (int64_t)__ldg(list + tok0 + n) : (int64_t)pc.q_start + tok0 + n;
-        cp_async16(tQ + slab_off(BQ, r, c), qb + q_row * p.q_stride_t + (ok ? g * D : 0) + c * 8, ok);
-        cp_async16(tO + slab_off(BQ, r, c), ob + q_row * p.do_stride_t + (ok ? g * D : 0) + c * 8, ok);
-      }
-      cp_async_commit();
       // my own row: lse, delta, absolute position
       const bool row_ok = (my_n < TOKQ) && (tok0 + my_n < r_hi);
       float lse = 0.f, dl = 0.f;
@@ -196,11 +220,6 @@ __global__ void __launch_bounds__(288, 1) dkdv_tc_kernel(NsaAttnParams p, DkdvLa
         dl = p.delta[a];
         ta = pc.off + (int)(q_row - pc.q_start);
       }
-      cp_async_wait<0>();
-      fence_proxy_async();
-      fence_before_sync();
-      mbar_arrive(bar(0, wg));
-
       if (!mbar_wait(bar(1, wg), j & 1, &budget)) timed_out = true;
       fence_after_sync();
 #pragma unroll
@@ -280,7 +299,14 @@ int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 
     set_error("%s: cudaFuncSetAttribute(%zu B) failed: %s", name, smem, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
-  dkdv_tc_kernel<D, MODE><<<grid, 288, smem, st>>>(*p, L);
+  const int G = p->QH / p->KH;
+  CUtensorMap tmq, tmo;
+  if (p->n_q_rows <= 0 || !tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, 1, G) ||
+      !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, 1, G)) {
+    set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q/dout must be 16-byte aligned, n_q_rows set)", name);
+    return NSA_ERR_CUDA;
+  }
+  dkdv_tc_kernel<D, MODE><<<grid, 320, smem, st>>>(*p, L, tmq, tmo);
   return check_launch(name);
 }
 

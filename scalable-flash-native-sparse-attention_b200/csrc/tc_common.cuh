@@ -140,7 +140,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* bu
   *budget = 8;
   return false;
 }
-constexpr int kWaitBudget = 1 << 22;  // polls; a healthy wait takes a few hundred
+constexpr int kWaitBudget = 1 << 18;  // polls (a few milliseconds); a healthy wait takes a few hundred
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}\n" ::"r"(bar) : "memory");
 }
