@@ -220,6 +220,15 @@ __global__ void __launch_bounds__(320, 1)
         dl = p.delta[a];
         ta = pc.off + (int)(q_row - pc.q_start);
       }
+      // keys kc_lo..kc_hi of the tile are visible to my row
+      int kc_lo = 0, kc_hi = -1;
+      if (row_ok) {
+        if (MODE == MODE_CMP) kc_hi = (ta - ks + 1 >= 0) ? (ta - ks + 1) / st - k0 : -1;
+        else kc_hi = ta - k0;
+        if (MODE == MODE_SWA) kc_lo = ta - W - k0;
+        kc_hi = min(kc_hi, kv_rows - 1);
+      }
+      const float nlse = -lse;
       if (!mbar_wait(bar(1, wg), j & 1, &budget)) timed_out = true;
       fence_after_sync();
 #pragma unroll
@@ -229,23 +238,23 @@ __global__ void __launch_bounds__(320, 1)
         tmem_ld32(lane_base + 128 * wg + 64 + half * 32, dv);
         wait_ld();
         uint32_t pp[16], dd[16];
+        if (kc_lo <= 0 && kc_hi >= BK - 1) {   // the whole key tile is visible to my row (the usual case)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kc = half * 32 + i + e;  // key row inside the tile
-            const int key = k0 + kc;
-            bool vis = row_ok && (kc < kv_rows);
-            if (MODE == MODE_CMP) vis = vis && (key * st + ks - 1 <= ta);
-            else if (MODE == MODE_SWA) vis = vis && (key <= ta) && (ta - key <= W);
-            else vis = vis && (key <= ta);
-            float x = vis ? fast_exp2(fmaf(__uint_as_float(sv[i + e]), c2, -lse)) : 0.f;
-            pv[e] = x;
-            ds[e] = x * (__uint_as_float(dv[i + e]) - dl);
+          for (int i = 0; i < 32; i += 2) {
+            const float x0 = fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nlse));
+            const float x1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nlse));
+            pp[i >> 1] = pack_bf16(x0, x1);
+            dd[i >> 1] = pack_bf16(x0 * (__uint_as_float(dv[i]) - dl), x1 * (__uint_as_float(dv[i + 1]) - dl));
           }
-          pp[i >> 1] = pack_bf16(pv[0], pv[1]);
-          dd[i >> 1] = pack_bf16(ds[0], ds[1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int kc = half * 32 + i;
+            const float x0 = (kc >= kc_lo && kc <= kc_hi) ? fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nlse)) : 0.f;
+            const float x1 = (kc + 1 >= kc_lo && kc + 1 <= kc_hi) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nlse)) : 0.f;
+            pp[i >> 1] = pack_bf16(x0, x1);
+            dd[i >> 1] = pack_bf16(x0 * (__uint_as_float(dv[i]) - dl), x1 * (__uint_as_float(dv[i + 1]) - dl));
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
