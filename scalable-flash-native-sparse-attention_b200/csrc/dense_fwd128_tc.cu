@@ -1,0 +1,332 @@
+// Forward of the compressed and sliding-window branches over CONTIGUOUS K/V: two 128-row query tiles per CTA, 128-row
+// K/V tiles, TMA loads, warp-specialised (tcgen05 + tensor memory).
+//
+// A query tile is (128/G consecutive tokens) x (the G query heads of one kv head); a CTA owns two consecutive tiles
+// a and b that walk over the same K/V tiles, so every K/V tile is fetched once for 256 query rows.
+//   warps 0-3 / 4-7   softmax group of tile a / b: thread i owns row i (tensor-memory lane i)
+//   warp 8 (one lane) issues every MMA:   S = Q K^T   (A = Q tile, B = K tile, both K-major from shared memory)
+//                                         O += P V    (A = P from tensor memory, B = V tile read MN-major)
+//   warp 9 (one lane) issues the TMA loads: both Q tiles once, K and V tiles through 2-stage rings
+// Tensor memory: S_a, S_b (128 fp32 columns each; the bf16 P of a tile is written over the S columns it came from)
+// and O_a, O_b.  MMAs of one thread execute in issue order, so S of the next K/V tile may be issued straight after
+// the P.V product that still reads P from the same columns; the order
+//     S_a(0) S_b(0) | PV_a(i) S_a(i+1) PV_b(i) S_b(i+1) | ...
+// keeps the tensor core busy with one tile while the other tile's group does its softmax.
+// The running maximum of a row is only raised when the tile maximum exceeds it by more than 2^8 (the row's thread then
+// rescales its O row in tensor memory); l and the final normalisation use the same reference, so the result is exact.
+#include "tma.cuh"
+
+namespace nsa {
+
+namespace {
+constexpr int MODE_CMP = 0;
+constexpr int MODE_SWA = 1;
+}  // namespace
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(320, 1)
+    dense_fwd128_tc_kernel(NsaAttnParams p, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
+                           const __grid_constant__ CUtensorMap tmv) {
+  using namespace tc;
+  constexpr int BM = 128, BN = 128, SLABS = D / 64;
+  constexpr uint32_t Q_BYTES = BM * D * 2, KV_BYTES = BN * D * 2, Q_SLAB = BM * 128, K_SLAB = BN * 128;
+  constexpr uint32_t TM_S = 0, TM_O = 256;   // + 128 * tile
+  constexpr uint32_t IDESC_S = make_idesc(BM, BN, false), IDESC_O = make_idesc(BM, D, true);
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  const uint32_t sQ = base;                     // 2 tiles
+  const uint32_t sK = sQ + 2 * Q_BYTES;         // 2 stages
+  const uint32_t sV = sK + 2 * KV_BYTES;        // 2 stages
+  const uint32_t bars = sV + 2 * KV_BYTES;
+  const uint32_t q_full = bars, k_full = bars + 8, v_full = k_full + 16, k_free = v_full + 16, v_free = k_free + 16,
+                 s_full = v_free + 16, p_ready = s_full + 16, o_done = p_ready + 16, tm_slot = o_done + 16;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int G = p.QH / p.KH;
+  const int TOK = BM / G;
+  const int pair = gridDim.x - 1 - blockIdx.x;
+  const int kh = blockIdx.z;
+  const Piece pc = load_piece(p.meta, blockIdx.y);
+  const int t0 = pair * 2 * TOK;
+  if (t0 >= pc.len) return;
+  const int ntok = min(2 * TOK, pc.len - t0);
+  const int tabs_min = pc.off + t0, tabs_max = tabs_min + ntok - 1;
+  const int ks = p.hp.kernel_size, st = p.hp.stride, W = p.hp.window;
+
+  int kv_lo, kv_hi, kv_bos;
+  if (MODE == MODE_CMP) {
+    kv_lo = 0;
+    kv_hi = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
+    kv_bos = pc.y_bos;
+  } else {
+    kv_lo = (max(0, tabs_min - W) / BN) * BN;   // tiles on a fixed grid of key positions: a row's result does not
+    kv_hi = min(tabs_max + 1, pc.x_len);        // depend on which rows share its CTA (shards reproduce the full run)
+    kv_bos = pc.x_bos;
+  }
+  const int ntiles = (kv_hi > kv_lo) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
+
+  if (ntiles == 0) {  // nothing visible for the whole pair: zeros
+    if (tid < 256) {
+      const int tok = (tid >> 7) * TOK + (tid & 127) / G, g = (tid & 127) % G;
+      if (tok < ntok) {
+        const int64_t q_row = pc.q_start + t0 + tok;
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) o[c] = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h] = 0.f;
+      }
+    }
+    return;
+  }
+  if (base & 1023u) {
+    if (tid == 0 && p.status) atomicOr(p.status, 8);
+    return;
+  }
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(k_free + 8 * s, 1);
+      mbar_init(v_free + 8 * s, 1);
+      mbar_init(s_full + 8 * s, 1);
+      mbar_init(p_ready + 8 * s, 128);
+      mbar_init(o_done + 8 * s, 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(tm_slot, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  uint32_t tmem;
+  asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
+  int budget = kWaitBudget;
+  bool timed_out = false;
+
+  if (warp == 9) {
+    if ((tid & 31) == 0) {
+      // ============================================ TMA producer
+      tma::expect_tx(q_full, 2 * Q_BYTES);
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma::load_3d(sQ + w * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, pc.q_start + t0 + w * TOK, q_full);
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it & 1, row = kv_bos + kv_lo + it * BN;
+        if (it >= 2 && !mbar_wait(k_free + 8 * s, ((it >> 1) - 1) & 1, &budget)) timed_out = true;
+        tma::expect_tx(k_full + 8 * s, KV_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sK + s * KV_BYTES + sl * K_SLAB, &tmk, sl * 64, kh, row, k_full + 8 * s);
+        if (it >= 2 && !mbar_wait(v_free + 8 * s, ((it >> 1) - 1) & 1, &budget)) timed_out = true;
+        tma::expect_tx(v_full + 8 * s, KV_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sV + s * KV_BYTES + sl * K_SLAB, &tmv, sl * 64, kh, row, v_full + 8 * s);
+      }
+    }
+  } else if (warp == 8) {
+    if ((tid & 31) == 0) {
+      // ============================================ MMA issue
+      auto issue_s = [&](int w, int it) {   // S_w = Q_w K(it)^T
+        const uint32_t tK = sK + (it & 1) * KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ao = (k >> 2) * Q_SLAB + (k & 3) * 32, bo = (k >> 2) * K_SLAB + (k & 3) * 32;
+          mma_ss(tmem + TM_S + 128 * w, desc_kmajor(sQ + w * Q_BYTES + ao), desc_kmajor(tK + bo), IDESC_S, k > 0);
+        }
+        mma_commit(s_full + 8 * w);
+      };
+      auto issue_pv = [&](int w, int it) {  // O_w += P_w V(it); k-step u = keys 16u..16u+15 = P columns 8u..8u+7
+        const uint32_t tV = sV + (it & 1) * KV_BYTES;
+        if (!mbar_wait(p_ready + 8 * w, it & 1, &budget)) timed_out = true;
+        fence_after_sync();
+#pragma unroll
+        for (int u = 0; u < BN / 16; ++u)
+          mma_ts(tmem + TM_O + 128 * w, tmem + TM_S + 128 * w + 8 * u, desc_mnmajor(tV + u * 2048, K_SLAB), IDESC_O, (it > 0 || u > 0));
+        mma_commit(o_done + 8 * w);
+      };
+      if (!mbar_wait(q_full, 0, &budget)) timed_out = true;
+      if (!mbar_wait(k_full, 0, &budget)) timed_out = true;
+      fence_after_sync();
+      issue_s(0, 0);
+      issue_s(1, 0);
+      mma_commit(k_free);
+      for (int it = 0; it < ntiles; ++it) {
+        const int s = it & 1;
+        const bool more = it + 1 < ntiles;
+        if (!mbar_wait(v_full + 8 * s, (it >> 1) & 1, &budget)) timed_out = true;
+        issue_pv(0, it);
+        if (more) {
+          if (!mbar_wait(k_full + 8 * (s ^ 1), ((it + 1) >> 1) & 1, &budget)) timed_out = true;
+          fence_after_sync();
+          issue_s(0, it + 1);
+        }
+        issue_pv(1, it);
+        mma_commit(v_free + 8 * s);
+        if (more) {
+          issue_s(1, it + 1);
+          mma_commit(k_free + 8 * (s ^ 1));
+        }
+      }
+    }
+  } else {
+    // ============================================ softmax group of tile w: thread = query row
+    const int w = warp >> 2, row = tid & 127;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 128 * w;
+    const int tok = w * TOK + row / G, g = row % G;
+    const bool row_ok = tok < ntok;
+    const int t_abs = tabs_min + tok;
+    const int64_t q_row = pc.q_start + t0 + tok;
+    // keys vis_lo..vis_hi (positions in the sequence's K/V rows) are visible to my row
+    int vis_lo = 0, vis_hi = -1;
+    if (row_ok) {
+      if (MODE == MODE_CMP) vis_hi = (t_abs - ks + 1 >= 0) ? (t_abs - ks + 1) / st : -1;
+      else { vis_hi = t_abs; vis_lo = t_abs - W; }
+      vis_hi = min(vis_hi, kv_hi - 1);
+    }
+    const float c2 = p.sm_scale * 1.4426950408889634f;
+    float m_ref = -INFINITY, l_run = 0.f;
+
+    for (int it = 0; it < ntiles; ++it) {
+      const int kv0 = kv_lo + it * BN;
+      const int lo = vis_lo - kv0, hi = vis_hi - kv0;   // visible columns of this tile
+      const bool full = lo <= 0 && hi >= BN - 1;
+      if (!mbar_wait(s_full + 8 * w, it & 1, &budget)) timed_out = true;
+      fence_after_sync();
+      // ---- pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t sv[32];
+        tmem_ld32(lane_base + TM_S + c * 32, sv);
+        wait_ld();
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= lo && c * 32 + i <= hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        }
+      }
+      mx *= c2;
+      // ---- reference maximum: raise it only when the row maximum ran away by more than 2^8
+      float alpha = 1.f;
+      bool need = false;
+      if (m_ref == -INFINITY) {
+        m_ref = mx;  // nothing accumulated yet for this row (its O row is still exactly zero or unwritten)
+      } else if (mx > m_ref + 8.f) {
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+        need = true;
+      }
+      const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      // ---- pass 2: P = exp2(S c - m) -> bf16 over the S columns already consumed
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t sv[32], pk[16];
+        tmem_ld32(lane_base + TM_S + c * 32, sv);
+        wait_ld();
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)), e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu));
+            rs += e0 + e1;
+            pk[i >> 1] = pack_bf16(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int col = c * 32 + i;
+            const float e0 = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)) : 0.f;
+            const float e1 = (col + 1 >= lo && col + 1 <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu)) : 0.f;
+            rs += e0 + e1;
+            pk[i >> 1] = pack_bf16(e0, e1);
+          }
+        }
+        tmem_st16(lane_base + TM_S + c * 16, pk);
+      }
+      l_run = l_run * alpha + rs;
+      if (it > 0 && __any_sync(0xffffffffu, need)) {  // rescale my O row (warp-uniform branch, per-lane factor); the
+#pragma unroll                                        // previous P.V of this tile retired before S of this K/V tile
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(lane_base + TM_O + c * 32, o);
+          wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(lane_base + TM_O + c * 32, o);
+        }
+      }
+      wait_st();
+      fence_before_sync();
+      mbar_arrive(p_ready + 8 * w);
+    }
+    if (!mbar_wait(o_done + 8 * w, (ntiles - 1) & 1, &budget)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue: my row of O
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(lane_base + TM_O + c * 32, o);
+      wait_ld();
+      if (row_ok) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 x;
+          x.x = pack_bf16(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
+          x.y = pack_bf16(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
+          x.z = pack_bf16(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
+          x.w = pack_bf16(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = x;
+        }
+      }
+    }
+    if (row_ok && p.lse)
+      p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h] = l_run > 0.f ? m_ref + log2f(l_run) : 0.f;
+  }
+  if (timed_out && p.status) atomicOr(p.status, 1);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// returns 1 when the configuration is not covered (the 64-row-tile kernel then runs), 0 on launch, < 0 on error
+template <int D, int MODE>
+static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name) {
+  const int G = p->QH / p->KH;
+  if (G > 128 || (128 % G) != 0) return 1;
+  if (p->meta.kv_table || p->meta.cmp_table || p->n_k_rows <= 0 || p->n_q_rows <= 0) return 1;
+  if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v) & 15) return 1;
+  if ((p->q_stride_t * 2) % 16 || (p->k_stride_t * 2) % 16 || (p->v_stride_t * 2) % 16) return 1;
+  const int TOK = 128 / G;
+  CUtensorMap tmq, tmk, tmv;
+  if (!tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, TOK, G) ||
+      !tma::make_map(&tmk, p->k, p->n_k_rows, p->KH, D, p->k_stride_t, 128, 1) ||
+      !tma::make_map(&tmv, p->v, p->n_k_rows, p->KH, D, p->v_stride_t, 128, 1)) {
+    set_error("%s: cuTensorMapEncodeTiled failed or is unavailable", name);
+    return NSA_ERR_CUDA;
+  }
+  const size_t smem = (size_t)6 * 128 * D * 2 + 256;
+  cudaError_t e = cudaFuncSetAttribute(dense_fwd128_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
+    return NSA_ERR_CUDA;
+  }
+  dim3 grid((p->meta.max_piece_len + 2 * TOK - 1) / (2 * TOK), p->meta.n_pieces, p->KH);
+  dense_fwd128_tc_kernel<D, MODE><<<grid, 320, smem, st>>>(*p, tmq, tmk, tmv);
+  return check_launch(name);
+}
+
+int launch_fwd128(const NsaAttnParams* p, cudaStream_t st, const char* name, bool cmp) {
+  if (p->D == 128) return cmp ? launch128<128, MODE_CMP>(p, st, name) : launch128<128, MODE_SWA>(p, st, name);
+  return cmp ? launch128<64, MODE_CMP>(p, st, name) : launch128<64, MODE_SWA>(p, st, name);
+}
+
+}  // namespace nsa

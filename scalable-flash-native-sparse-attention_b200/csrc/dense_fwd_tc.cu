@@ -17,6 +17,7 @@ namespace nsa {
 constexpr int MODE_CMP = 0;
 constexpr int MODE_SWA = 1;
 int check_attn_common(const NsaAttnParams* p, const char* name, bool need_y);
+int launch_fwd128(const NsaAttnParams* p, cudaStream_t st, const char* name, bool cmp);   // dense_fwd128_tc.cu
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(128, 2) dense_fwd_tc_kernel(NsaAttnParams p) {
@@ -279,6 +280,8 @@ extern "C" int nsa_cmp_attn_fwd(const NsaAttnParams* p, void* stream) {
   if (rc) return rc;
   NSA_REQUIRE(p->lse, NSA_ERR_BAD_ARG, "cmp_attn_fwd: lse is required");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
+  rc = launch_fwd128(p, (cudaStream_t)stream, "cmp_attn_fwd", true);   // contiguous K/V: 128-row tiles, TMA
+  if (rc != 1) return rc;
   if (p->D == 128) return launch_fwd_tc<128, MODE_CMP>(p, (cudaStream_t)stream, "cmp_attn_fwd");
   return launch_fwd_tc<64, MODE_CMP>(p, (cudaStream_t)stream, "cmp_attn_fwd");
 }
@@ -288,6 +291,8 @@ extern "C" int nsa_swa_fwd(const NsaAttnParams* p, void* stream) {
   if (rc) return rc;
   NSA_REQUIRE(p->hp.window >= 0, NSA_ERR_BAD_ARG, "swa_fwd: negative window");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
+  rc = launch_fwd128(p, (cudaStream_t)stream, "swa_fwd", false);
+  if (rc != 1) return rc;
   if (p->D == 128) return launch_fwd_tc<128, MODE_SWA>(p, (cudaStream_t)stream, "swa_fwd");
   return launch_fwd_tc<64, MODE_SWA>(p, (cudaStream_t)stream, "swa_fwd");
 }
