@@ -3,11 +3,13 @@
 //
 // A query tile is (128/G consecutive tokens) x (the G query heads of one kv head); a CTA owns two consecutive tiles
 // a and b that walk over the same K/V tiles, so every K/V tile is fetched once for 256 query rows.
-//   warps 0-3 / 4-7   softmax group of tile a / b: thread i owns row i (tensor-memory lane i)
-//   warp 8 (one lane) issues every MMA:   S = Q K^T   (A = Q tile, B = K tile, both K-major from shared memory)
+//   warps 0-7 / 8-15  softmax of tile a / b: two groups of 128 threads per tile, thread i of a group owns row i
+//                     (tensor-memory lane i) and one half of the 128 key columns; the row maximum and the final
+//                     row sum cross the halves through shared memory
+//   warp 16 (one lane) issues every MMA:   S = Q K^T   (A = Q tile, B = K tile, both K-major from shared memory)
 //                                         O += P V    (A = P from tensor memory, B = V tile read MN-major)
-//   warp 9 (one lane) issues the TMA loads: both Q tiles once, K and V tiles through 2-stage rings
-// Tensor memory: S_a, S_b (128 fp32 columns each; the bf16 P of a tile is written over the S columns it came from)
+//   warp 17 (one lane) issues the TMA loads: both Q tiles once, K and V tiles through 2-stage rings
+// Tensor memory: S_a, S_b (128 fp32 columns each; the bf16 P of a column half is written over S columns of that half)
 // and O_a, O_b.  MMAs of one thread execute in issue order, so S of the next K/V tile may be issued straight after
 // the P.V product that still reads P from the same columns; the order
 //     S_a(0) S_b(0) | PV_a(i) S_a(i+1) PV_b(i) S_b(i+1) | ...
@@ -24,7 +26,7 @@ constexpr int MODE_SWA = 1;
 }  // namespace
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
     dense_fwd128_tc_kernel(NsaAttnParams p, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                            const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
@@ -41,6 +43,7 @@ __global__ void __launch_bounds__(320, 1)
   const uint32_t bars = sV + 2 * KV_BYTES;
   const uint32_t q_full = bars, k_full = bars + 8, v_full = k_full + 16, k_free = v_full + 16, v_free = k_free + 16,
                  s_full = v_free + 16, p_ready = s_full + 16, o_done = p_ready + 16, tm_slot = o_done + 16;
+  float* sX = reinterpret_cast<float*>(smem_raw + 2 * Q_BYTES + 4 * KV_BYTES + 256);   // row maxima / sums crossing the two column halves
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -91,7 +94,7 @@ __global__ void __launch_bounds__(320, 1)
       mbar_init(k_free + 8 * s, 1);
       mbar_init(v_free + 8 * s, 1);
       mbar_init(s_full + 8 * s, 1);
-      mbar_init(p_ready + 8 * s, 128);
+      mbar_init(p_ready + 8 * s, 256);
       mbar_init(o_done + 8 * s, 1);
     }
     fence_mbar_init();
@@ -105,7 +108,7 @@ __global__ void __launch_bounds__(320, 1)
   int budget = kWaitBudget;
   bool timed_out = false;
 
-  if (warp == 9) {
+  if (warp == 17) {
     if ((tid & 31) == 0) {
       // ============================================ TMA producer
       tma::expect_tx(q_full, 2 * Q_BYTES);
@@ -126,7 +129,7 @@ __global__ void __launch_bounds__(320, 1)
         for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sV + s * KV_BYTES + sl * K_SLAB, &tmv, sl * 64, kh, row, v_full + 8 * s);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 16) {
     if ((tid & 31) == 0) {
       // ============================================ MMA issue
       auto issue_s = [&](int w, int it) {   // S_w = Q_w K(it)^T
@@ -138,13 +141,13 @@ __global__ void __launch_bounds__(320, 1)
         }
         mma_commit(s_full + 8 * w);
       };
-      auto issue_pv = [&](int w, int it) {  // O_w += P_w V(it); k-step u = keys 16u..16u+15 = P columns 8u..8u+7
+      auto issue_pv = [&](int w, int it) {  // O_w += P_w V(it); k-step u = keys 16u..16u+15; P of keys 64h.. starts at column 64h
         const uint32_t tV = sV + (it & 1) * KV_BYTES;
         if (!mbar_wait(p_ready + 8 * w, it & 1, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
         for (int u = 0; u < BN / 16; ++u)
-          mma_ts(tmem + TM_O + 128 * w, tmem + TM_S + 128 * w + 8 * u, desc_mnmajor(tV + u * 2048, K_SLAB), IDESC_O, (it > 0 || u > 0));
+          mma_ts(tmem + TM_O + 128 * w, tmem + TM_S + 128 * w + 64 * (u >> 2) + 8 * (u & 3), desc_mnmajor(tV + u * 2048, K_SLAB), IDESC_O, (it > 0 || u > 0));
         mma_commit(o_done + 8 * w);
       };
       if (!mbar_wait(q_full, 0, &budget)) timed_out = true;
@@ -172,8 +175,8 @@ __global__ void __launch_bounds__(320, 1)
       }
     }
   } else {
-    // ============================================ softmax group of tile w: thread = query row
-    const int w = warp >> 2, row = tid & 127;
+    // ============================================ softmax: tile w = a / b, column half h; thread = query row
+    const int w = warp >> 3, h = (warp >> 2) & 1, row = tid & 127;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 128 * w;
     const int tok = w * TOK + row / G, g = row % G;
     const bool row_ok = tok < ntok;
@@ -187,31 +190,37 @@ __global__ void __launch_bounds__(320, 1)
       vis_hi = min(vis_hi, kv_hi - 1);
     }
     const float c2 = p.sm_scale * 1.4426950408889634f;
-    float m_ref = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;   // l_run: my half of the columns only
+    float* xmax = sX + (w * 2) * 256;       // [2 buffers][2 halves][128 rows] of this tile
+    constexpr int HN = BN / 2;
 
     for (int it = 0; it < ntiles; ++it) {
-      const int kv0 = kv_lo + it * BN;
-      const int lo = vis_lo - kv0, hi = vis_hi - kv0;   // visible columns of this tile
-      const bool full = lo <= 0 && hi >= BN - 1;
+      const int kv0 = kv_lo + it * BN + h * HN;
+      const int lo = vis_lo - kv0, hi = vis_hi - kv0;   // visible columns of my half of this tile
+      const bool full = lo <= 0 && hi >= HN - 1;
       if (!mbar_wait(s_full + 8 * w, it & 1, &budget)) timed_out = true;
       fence_after_sync();
-      // ---- pass 1: row maximum
-      float mx = -INFINITY;
+      // ---- pass 1: row maximum over my 64 columns, then over both halves through shared memory
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < HN / 32; ++c) {
         uint32_t sv[32];
-        tmem_ld32(lane_base + TM_S + c * 32, sv);
+        tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
         wait_ld();
         if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= lo && c * 32 + i <= hi) mx = fmaxf(mx, __uint_as_float(sv[i]));
+            if (c * 32 + i >= lo && c * 32 + i <= hi) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
         }
       }
-      mx *= c2;
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* xb = xmax + (it & 1) * 256;   // this buffer was last read two tiles ago, before the previous tile's barrier
+      xb[h * 128 + row] = mx;
+      named_barrier(1 + w, 256);
+      mx = fmaxf(mx, xb[(h ^ 1) * 128 + row]) * c2;
       // ---- reference maximum: raise it only when the row maximum ran away by more than 2^8
       float alpha = 1.f;
       bool need = false;
@@ -223,18 +232,19 @@ __global__ void __launch_bounds__(320, 1)
         need = true;
       }
       const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      // ---- pass 2: P = exp2(S c - m) -> bf16 over the S columns already consumed
-      float rs = 0.f;
+      // ---- pass 2: P = exp2(S c - m) -> bf16, written over the first 32 of MY 64 S columns (already consumed)
+      float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < HN / 32; ++c) {
         uint32_t sv[32], pk[16];
-        tmem_ld32(lane_base + TM_S + c * 32, sv);
+        tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
         wait_ld();
         if (full) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)), e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu));
-            rs += e0 + e1;
+            rs0 += e0;
+            rs1 += e1;
             pk[i >> 1] = pack_bf16(e0, e1);
           }
         } else {
@@ -243,38 +253,44 @@ __global__ void __launch_bounds__(320, 1)
             const int col = c * 32 + i;
             const float e0 = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)) : 0.f;
             const float e1 = (col + 1 >= lo && col + 1 <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu)) : 0.f;
-            rs += e0 + e1;
+            rs0 += e0;
+            rs1 += e1;
             pk[i >> 1] = pack_bf16(e0, e1);
           }
         }
-        tmem_st16(lane_base + TM_S + c * 16, pk);
+        tmem_st16(lane_base + TM_S + h * HN + c * 16, pk);
       }
-      l_run = l_run * alpha + rs;
-      if (it > 0 && __any_sync(0xffffffffu, need)) {  // rescale my O row (warp-uniform branch, per-lane factor); the
-#pragma unroll                                        // previous P.V of this tile retired before S of this K/V tile
-        for (int c = 0; c < D / 32; ++c) {
+      l_run = l_run * alpha + (rs0 + rs1);
+      if (it > 0 && __any_sync(0xffffffffu, need)) {  // rescale my half of my O row (warp-uniform branch, per-lane
+#pragma unroll                                        // factor); the previous P.V of this tile retired before this S
+        for (int c = 0; c < D / 64; ++c) {
           uint32_t o[32];
-          tmem_ld32(lane_base + TM_O + c * 32, o);
+          tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, o);
           wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(lane_base + TM_O + c * 32, o);
+          tmem_st32(lane_base + TM_O + h * (D / 2) + c * 32, o);
         }
       }
       wait_st();
       fence_before_sync();
       mbar_arrive(p_ready + 8 * w);
     }
+    // the row's l: both halves
+    float* xl = xmax + (ntiles & 1) * 256;
+    xl[h * 128 + row] = l_run;
+    named_barrier(1 + w, 256);
+    l_run += xl[(h ^ 1) * 128 + row];
     if (!mbar_wait(o_done + 8 * w, (ntiles - 1) & 1, &budget)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue: my row of O
+    // ---- epilogue: my half of my row of O
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D;
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D + h * (D / 2);
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
       uint32_t o[32];
-      tmem_ld32(lane_base + TM_O + c * 32, o);
+      tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, o);
       wait_ld();
       if (row_ok) {
 #pragma unroll
@@ -288,7 +304,7 @@ __global__ void __launch_bounds__(320, 1)
         }
       }
     }
-    if (row_ok && p.lse)
+    if (row_ok && p.lse && h == 0)
       p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h] = l_run > 0.f ? m_ref + log2f(l_run) : 0.f;
   }
   if (timed_out && p.status) atomicOr(p.status, 1);
@@ -313,14 +329,14 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name) 
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable", name);
     return NSA_ERR_CUDA;
   }
-  const size_t smem = (size_t)6 * 128 * D * 2 + 256;
+  const size_t smem = (size_t)6 * 128 * D * 2 + 256 + 4 * 256 * 4;
   cudaError_t e = cudaFuncSetAttribute(dense_fwd128_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
   dim3 grid((p->meta.max_piece_len + 2 * TOK - 1) / (2 * TOK), p->meta.n_pieces, p->KH);
-  dense_fwd128_tc_kernel<D, MODE><<<grid, 320, smem, st>>>(*p, tmq, tmk, tmv);
+  dense_fwd128_tc_kernel<D, MODE><<<grid, 576, smem, st>>>(*p, tmq, tmk, tmv);
   return check_launch(name);
 }
 
