@@ -232,6 +232,7 @@ __global__ void __launch_bounds__(128, 2) dense_dq_tc_kernel(NsaAttnParams p) {
 template <int D, int MODE>
 int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L);  // dkdv_tc.cu
 int launch_dkdv128(const NsaAttnParams* p, cudaStream_t st, const char* name, bool cmp, int q_chunk);   // dkdv128_tc.cu
+int launch_dq128(const NsaAttnParams* p, cudaStream_t st, const char* name, bool cmp);                  // dense_dq128_tc.cu
 
 template <typename K>
 static int set_smem(K kernel, size_t smem, const char* name) {
@@ -286,6 +287,8 @@ extern "C" int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream) {
     if (rc) return rc;
   }
   if (!(ph & 4)) return check_launch("cmp_attn_bwd");
+  rc = launch_dq128(p, st, "cmp_attn_bwd(dq)", true);   // contiguous K/V: 128-row tiles, TMA
+  if (rc != 1) return rc;
   return (p->D == 128) ? launch_dq<128, MODE_CMP>(p, st, "cmp_attn_bwd(dq)") : launch_dq<64, MODE_CMP>(p, st, "cmp_attn_bwd(dq)");
 }
 
@@ -309,5 +312,7 @@ extern "C" int nsa_swa_bwd(const NsaAttnParams* p, void* stream) {
     if (rc) return rc;
   }
   if (!(ph & 4)) return check_launch("swa_bwd");
+  rc = launch_dq128(p, st, "swa_bwd(dq)", false);
+  if (rc != 1) return rc;
   return (p->D == 128) ? launch_dq<128, MODE_SWA>(p, st, "swa_bwd(dq)") : launch_dq<64, MODE_SWA>(p, st, "swa_bwd(dq)");
 }
