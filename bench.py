@@ -438,6 +438,9 @@ def kernel_breakdown(q, k, v, w, do, lens):
         dkf, dvf = torch.zeros(kd.shape, device=kd.device), torch.zeros(vd.shape, device=vd.device)
         dck, dcv = torch.zeros(ck.shape, device=kd.device), torch.zeros(cv.shape, device=kd.device)
 
+        # the combine backward writes the three branches' delta rows as well (the step's branch backwards use them)
+        deltas = [torch.empty_like(cmp_lse).t(), torch.empty_like(slc_lse), torch.empty_like(swa_lse)]
+
         def bwd_call(fn, kk, vv, o, lse, head_major, dk_, dv_, phase, topk_=None):
             delta = torch.empty_like(lse)
             p = attn_params(qd, kk, vv, H, sm, o=o, lse=lse, lse_is_head_major=head_major, dout=do, delta=delta, dq=dq, dk=dk_, dv=dv_,
@@ -456,7 +459,7 @@ def kernel_breakdown(q, k, v, w, do, lens):
             "slc_fwd": lambda: slc_attn_fwd(qd, kd, vd, topk),
             "swa_fwd": lambda: swa_fwd(qd, kd, vd),
             "combine_fwd": lambda: combine_fwd(cmp_o, slc_o, swa_o, wd),
-            "combine_bwd": lambda: combine_bwd(cmp_o, slc_o, swa_o, wd, do),
+            "combine_bwd": lambda: combine_bwd(cmp_o, slc_o, swa_o, wd, do, deltas=deltas),
             "k2q_index": lambda: get_bind_from_find(topk),
             "cmp_dkdv": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 2),
             "cmp_dq": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 4),
@@ -464,7 +467,6 @@ def kernel_breakdown(q, k, v, w, do, lens):
             "slc_dq": bwd_call("nsa_slc_attn_bwd", kd, vd, slc_o, slc_lse, False, dkf, dvf, 4, topk),
             "swa_dkdv": bwd_call("nsa_swa_bwd", kd, vd, swa_o, swa_lse, False, dkf, dvf, 2),
             "swa_dq": bwd_call("nsa_swa_bwd", kd, vd, swa_o, swa_lse, False, dkf, dvf, 4),
-            "delta": bwd_call("nsa_swa_bwd", kd, vd, swa_o, swa_lse, False, dkf, dvf, 1),
             "pool_bwd": lambda: mean_pooling_bwd(kd, dck.bfloat16(), dkf),
         }
         out = {}

@@ -221,6 +221,10 @@ typedef struct NsaCombineParams {
   int64_t a_stride_t, b_stride_t, c_stride_t, w_stride_t, y_stride_t, dy_stride_t, dw_stride_t;
   int64_t T;
   int32_t H, D;
+  /* optional bwd out (all three or none): delta_x[t,h] = sum_d x[t,h,d] * dx[t,h,d] in fp32, the row term the branch
+   * backward kernels need; a branch backward given this runs with phases = 6 (no delta pass of its own) */
+  float *delta_a, *delta_b, *delta_c;
+  int64_t delta_a_stride_t, delta_a_stride_h, delta_b_stride_t, delta_b_stride_h, delta_c_stride_t, delta_c_stride_h;
 } NsaCombineParams;
 /* replaces combine_fwd / combine_bwd, flash_nsa/ops/combine.py:114-177 */
 int nsa_combine_fwd(const NsaCombineParams* p, void* stream);

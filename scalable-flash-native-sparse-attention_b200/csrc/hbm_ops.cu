@@ -224,6 +224,7 @@ __global__ void combine_bwd_kernel(NsaCombineParams p) {
   F8 dy = unpack8(ldg16(reinterpret_cast<const __nv_bfloat16*>(p.dy) + t * p.dy_stride_t + col));
   F8 da, db, dc;
   float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+  float d0 = 0.f, d1 = 0.f, d2 = 0.f;   // delta of each branch, from the bf16-rounded branch gradients that are stored
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     da.v[e] = dy.v[e] * s0;
@@ -232,11 +233,17 @@ __global__ void combine_bwd_kernel(NsaCombineParams p) {
     r0 += dy.v[e] * a.v[e];
     r1 += dy.v[e] * b.v[e];
     r2 += dy.v[e] * cc.v[e];
+    d0 += __bfloat162float(__float2bfloat16(da.v[e])) * a.v[e];
+    d1 += __bfloat162float(__float2bfloat16(db.v[e])) * b.v[e];
+    d2 += __bfloat162float(__float2bfloat16(dc.v[e])) * cc.v[e];
   }
   for (int o = CH / 2; o > 0; o >>= 1) {
     r0 += __shfl_xor_sync(0xffffffffu, r0, o);
     r1 += __shfl_xor_sync(0xffffffffu, r1, o);
     r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+    d0 += __shfl_xor_sync(0xffffffffu, d0, o);
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
   }
   if (!live) return;
   int64_t ocol = (t * p.H + h) * (int64_t)p.D + c * 8;  // da/db/dc are contiguous [T,H,D]
@@ -248,6 +255,11 @@ __global__ void combine_bwd_kernel(NsaCombineParams p) {
     dw[0] = __float2bfloat16(s0 * (1.f - s0) * r0);
     dw[1] = __float2bfloat16(s1 * (1.f - s1) * r1);
     dw[2] = __float2bfloat16(s2 * (1.f - s2) * r2);
+    if (p.delta_a) {
+      p.delta_a[t * p.delta_a_stride_t + h * p.delta_a_stride_h] = d0;
+      p.delta_b[t * p.delta_b_stride_t + h * p.delta_b_stride_h] = d1;
+      p.delta_c[t * p.delta_c_stride_t + h * p.delta_c_stride_h] = d2;
+    }
   }
 }
 
@@ -413,6 +425,8 @@ extern "C" int nsa_combine_bwd(const NsaCombineParams* p, void* stream) {
   NSA_REQUIRE(p && p->a && p->b && p->c && p->w && p->dy && p->da && p->db && p->dc && p->dw, NSA_ERR_BAD_ARG,
               "combine_bwd: null pointer");
   NSA_REQUIRE(p->D == 64 || p->D == 128 || p->D == 256, NSA_ERR_UNSUPPORTED_SHAPE, "combine_bwd: D=%d (64/128/256)", p->D);
+  NSA_REQUIRE((!p->delta_a && !p->delta_b && !p->delta_c) || (p->delta_a && p->delta_b && p->delta_c), NSA_ERR_BAD_ARG,
+              "combine_bwd: give all three delta outputs or none");
   int64_t n = p->T * p->H * (p->D / 8);
   if (n == 0) return NSA_OK;
   combine_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);

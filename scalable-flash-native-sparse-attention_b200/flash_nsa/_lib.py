@@ -91,7 +91,11 @@ def call(fn_name, params, stream):
     """Invoke an entry point `int fn(const Params*, void* stream)`; raise on a non-zero status."""
     global launch_count
     L = lib()
-    launch_count += KERNELS_PER_CALL.get(fn_name, 1)
+    n = KERNELS_PER_CALL.get(fn_name, 1)
+    ph = getattr(params, "phases", 0) if fn_name.endswith("_bwd") else 0
+    if ph:   # a backward entry point asked for a subset of {delta, dK/dV, dQ}
+        n = bin(ph & 7).count("1")
+    launch_count += n
     rc = getattr(L, fn_name)(ctypes.byref(params), ctypes.c_void_p(stream))
     if rc != 0:
         raise NsaError(f"{fn_name} failed ({rc}): {L.nsa_last_error().decode()}")

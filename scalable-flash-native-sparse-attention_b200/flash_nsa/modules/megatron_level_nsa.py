@@ -117,27 +117,35 @@ class NSAFunction(torch.autograd.Function):
         if _empty(swa_o):
             swa_o, swa_lse = swa_fwd(q, k, v, sm_scale=sm_scale, helper=helper)
 
-        dcmp_o, dslc_o, dswa_o, dcombine_weight = combine_bwd(cmp_o, slc_o, swa_o, combine_weight, do)
+        # the combine backward also yields each branch's delta = sum_d o * do, so the branches skip their delta pass
+        deltas = [torch.empty_like(cmp_lse), torch.empty_like(slc_lse), torch.empty_like(swa_lse)]
+        dcmp_o, dslc_o, dswa_o, dcombine_weight = combine_bwd(cmp_o, slc_o, swa_o, combine_weight, do,
+                                                               deltas=[deltas[0].t(), deltas[1], deltas[2]])
         dq = torch.empty_like(q)
         dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
         dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
         # sliding window writes dq, the other branches add into it; every branch adds into the fp32 dk/dv
-        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper)
-        slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper)
-        _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper)
+        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2])
+        slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1])
+        _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
+                                         delta=deltas[0])
         _, dwk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper)
         _, dwv = compress_kv_bwd(v, cmp_v_weight, block_v, hidden_v, dcmp_v, dv, version=vm, helper=helper)
         return dq, dk, dv, dcombine_weight, dwk, dwv, None
 
 
-def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper):
+def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper, delta=None):
     """Sliding-window backward that OVERWRITES dq (bf16) and adds into dk/dv (fp32)."""
     from ..ops._common import attn_params, call
     if not (dout.stride(-1) == 1 and dout.stride(1) == dout.size(-1)):
         dout = dout.contiguous()
-    delta = torch.empty_like(lse)
+    have_delta = delta is not None
+    if not have_delta:
+        delta = torch.empty_like(lse)
     p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=dout, delta=delta, dq=dq, dk=dk, dv=dv)
     p.accumulate_dq = 0
+    if have_delta:
+        p.phases = 6
     if q.size(0) > 0:
         call("nsa_swa_bwd", p, q)
 
@@ -242,12 +250,15 @@ class CPNSAFunction(torch.autograd.Function):
                 slc_o, slc_lse = slc_attn_fwd(q, k, v, topk, sm_scale=sm_scale, helper=helper)
             if swa_o is None:
                 swa_o, swa_lse = swa_fwd(q, k, v, sm_scale=sm_scale, helper=helper)
+            deltas = [torch.empty_like(cmp_lse), torch.empty_like(slc_lse), torch.empty_like(swa_lse)]
             dcmp_o, dslc_o, dswa_o, _ = combine_bwd(cmp_o, slc_o, swa_o, w_i, do_i,
-                                                     dw=dcombine_weight[:, h0 * G:(h0 + stride) * G])
+                                                     dw=dcombine_weight[:, h0 * G:(h0 + stride) * G],
+                                                     deltas=[deltas[0].t(), deltas[1], deltas[2]])
             dk, dv = comm.grad_buffers()  # zero-filled fp32 [t*W, stride, d]
-            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper)
-            slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper)
-            _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper)
+            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2])
+            slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1])
+            _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
+                                             delta=deltas[0])
             _, fk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper, async_dw=True)
             dk_local = comm.reduce_scatter(Comm.GRAD_KEY)
             _, fv = compress_kv_bwd(v, cmp_v_weight, block_v, hidden_v, dcmp_v, dv, version=vm, helper=helper, async_dw=True)

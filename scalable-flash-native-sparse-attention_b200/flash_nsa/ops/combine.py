@@ -38,7 +38,10 @@ def combine_fwd(a, b, c, w, out=None):
     return out
 
 
-def combine_bwd(a, b, c, w, dout, dw=None):
+def combine_bwd(a, b, c, w, dout, dw=None, deltas=None):
+    """Returns (da, db, dc, dw).  `deltas`: optional three fp32 [T,H] tensors (any strides, e.g. a transposed view)
+    that receive sum_d x * dx per (token, head): the row term a branch backward otherwise computes in a pass of its
+    own."""
     _check(a, b, c, w)
     if not (dout.stride(-1) == 1 and dout.stride(1) == dout.size(-1)):
         dout = dout.contiguous()
@@ -49,6 +52,13 @@ def combine_bwd(a, b, c, w, dout, dw=None):
     p = _params(a, b, c, w)
     p.dy, p.dy_stride_t = ptr(dout), dout.stride(0)
     p.da, p.db, p.dc, p.dw, p.dw_stride_t = ptr(da), ptr(db), ptr(dc), ptr(dw), dw.stride(0)
+    if deltas is not None:
+        T, H, _ = a.shape
+        for name, t in zip(("delta_a", "delta_b", "delta_c"), deltas):
+            assert t.dtype == torch.float32 and list(t.shape) == [T, H], f"{name}: fp32 [T,H] (a transposed view is fine)"
+            setattr(p, name, ptr(t))
+            setattr(p, name + "_stride_t", t.stride(0))
+            setattr(p, name + "_stride_h", t.stride(1))
     call("nsa_combine_bwd", p, a)
     return da, db, dc, dw
 

@@ -20,7 +20,7 @@ def cmp_attn_fwd(q, k, v, sm_scale=None, o=None, helper=NSAHelper):
 
 
 def cmp_attn_bwd(q, k, v, o, lse, do, dq=None, sm_scale=None, fuse_dqdkdv=False, dkdv_dtype=torch.float,
-                 dkdv_repeat=False, async_dq=False, helper=NSAHelper):
+                 dkdv_repeat=False, async_dq=False, helper=NSAHelper, delta=None):
     """Returns (dq, dk, dv).  With `dq` given the result is added into it; dk/dv come back in k's dtype.
     `async_dq=True` additionally returns a callable (a no-op here: dq is produced by the same launch sequence)."""
     T, QH, D = q.shape
@@ -33,11 +33,15 @@ def cmp_attn_bwd(q, k, v, o, lse, do, dq=None, sm_scale=None, fuse_dqdkdv=False,
         dq = torch.empty_like(q)
     dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
     dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
-    delta = torch.empty_like(lse)
+    have_delta = delta is not None   # sum_d o * do per (head, token), laid out like lse (e.g. from combine_bwd)
+    if not have_delta:
+        delta = torch.empty_like(lse)
     if T > 0 and k.size(0) > 0:
         p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, lse_is_head_major=True, dout=do, delta=delta, dq=dq,
                         dk=dk, dv=dv, need_y=True)
         p.accumulate_dq = int(acc_dq)
+        if have_delta:
+            p.phases = 6
         call("nsa_cmp_attn_bwd", p, q)
     elif not acc_dq:
         dq.zero_()

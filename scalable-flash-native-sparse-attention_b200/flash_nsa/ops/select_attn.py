@@ -20,7 +20,7 @@ def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
 
 
 def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=None, fuse_dqdkdv=False,
-                 dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper):
+                 dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None):
     """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
     otherwise dq is new and dk/dv come back in k's dtype.  Deterministic: one CTA owns a key block."""
     T, QH, D = q.shape
@@ -35,7 +35,9 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
     if own:
         dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
         dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
-    delta = torch.empty_like(lse)
+    have_delta = delta is not None   # sum_d o * do per (token, head), laid out like lse (e.g. from combine_bwd)
+    if not have_delta:
+        delta = torch.empty_like(lse)
     if T > 0:
         offsets, tokens = get_bind_from_find(topk, helper=helper)
         p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=do, delta=delta, dq=dq, dk=dk, dv=dv, topk=topk)
@@ -44,6 +46,8 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
         p.n_blocks_total = offsets.size(1) - 1
         p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
         p.accumulate_dq = int(acc_dq)
+        if have_delta:
+            p.phases = 6
         call("nsa_slc_attn_bwd", p, q)
     if own:
         dk, dv = dk.to(k.dtype), dv.to(v.dtype)
