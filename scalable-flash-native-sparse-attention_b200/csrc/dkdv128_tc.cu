@@ -71,6 +71,15 @@ __global__ void __launch_bounds__(288, 1)
     return;
   }
   const int n_it = (r_hi - r_lo + TOKQ - 1) / TOKQ;
+  // Order of the query tiles.  Sliding window: neighbouring key tiles see overlapping query ranges, and their CTAs run
+  // at the same time; step i of every CTA takes the tile whose absolute tile number is i modulo the tile count, so the
+  // CTAs that share a query tile read it at about the same time and it is served from L2.
+  int rot = 0;
+  if (MODE == MODE_SWA) {
+    const int abs0 = (pc.off + r_lo) / TOKQ;
+    rot = (n_it - abs0 % n_it) % n_it;
+  }
+  auto tile_of = [&](int i) { return MODE == MODE_SWA ? (i + rot) % n_it : i; };
 
   if (tid == 0) {
     mbar_init(kv_full, 1);
@@ -104,7 +113,7 @@ __global__ void __launch_bounds__(288, 1)
       auto load_q = [&](int i) {  // tile i into stage i % NS (the caller has made sure the stage is free)
         const int s = i % NS;
         tma::expect_tx(q_full + 8 * s, 2 * Q_BYTES);
-        const int row = pc.q_start + r_lo + i * TOKQ;
+        const int row = pc.q_start + r_lo + tile_of(i) * TOKQ;
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
           tma::load_3d(sQ + s * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, row, q_full + 8 * s);
@@ -178,7 +187,7 @@ __global__ void __launch_bounds__(288, 1)
       if (t < 64 && i < n_it) {
         const int col = 64 * wg + t;
         const int n = col / G, g = col - n * G;
-        const int tok = r_lo + i * TOKQ + n;
+        const int tok = r_lo + tile_of(i) * TOKQ + n;
         if (tok < r_hi) {
           const int64_t q_row = (int64_t)pc.q_start + tok;
           const int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h;
@@ -200,7 +209,7 @@ __global__ void __launch_bounds__(288, 1)
       fetch_meta(i + 1);
       named_barrier(1 + wg, 128);   // buffer ph was last read two tiles ago, before the previous tile's barrier
       // every (key, query) pair of the tile visible?  then the position test is skipped
-      const int tok0 = r_lo + i * TOKQ, ta_min = pc.off + tok0, ta_max = ta_min + TOKQ - 1;
+      const int tok0 = r_lo + tile_of(i) * TOKQ, ta_min = pc.off + tok0, ta_max = ta_min + TOKQ - 1;
       bool full = kv_rows == BK && tok0 + TOKQ <= r_hi;
       if (MODE == MODE_CMP) full = full && ((k0 + BK - 1) * st + ks - 1 <= ta_min);
       else full = full && (k0 + BK - 1 <= ta_min) && (ta_max - k0 <= W);
