@@ -31,6 +31,26 @@ struct TopList {
       i[k] = 0x7fffffff;
     }
   }
+  // Candidate whose index is larger than every index in the list (a group meets its blocks in increasing order), so it
+  // loses every tie: it goes behind all entries with v >= cv.  Position by 13 independent compares, then one shift
+  // (no dependent chain, and the common "not good enough" case leaves after one compare).
+  __device__ __forceinline__ void insert_newer(float cv, int ci) {
+    if (!(cv > v[kList - 1])) return;
+    int pos = 0;
+#pragma unroll
+    for (int k = 0; k < kList; ++k) pos += (v[k] >= cv) ? 1 : 0;
+#pragma unroll
+    for (int k = kList - 1; k >= 0; --k) {
+      const bool here = (k == pos), shift = (k > pos);
+      if (k > 0) {
+        v[k] = here ? cv : (shift ? v[k - 1] : v[k]);
+        i[k] = here ? ci : (shift ? i[k - 1] : i[k]);
+      } else {
+        v[k] = here ? cv : v[k];
+        i[k] = here ? ci : i[k];
+      }
+    }
+  }
   __device__ __forceinline__ void insert(float cv, int ci) {
     if (!better(cv, ci, v[kList - 1], i[kList - 1])) return;
     v[kList - 1] = cv;
@@ -211,7 +231,7 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
           if (p.quant == 0) reinterpret_cast<float*>(p.probs)[a] = pv;
           else reinterpret_cast<__half*>(p.probs)[a] = __float2half_rn(pv);
         }
-        if (blk >= ni && blk <= nk - nl) lst.insert(pv, blk);
+        if (blk >= ni && blk <= nk - nl) lst.insert_newer(pv, blk);
       }
     }
     // ---- merge group 1's list into group 0's and write the row
