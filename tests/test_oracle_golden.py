@@ -116,3 +116,29 @@ def test_cp_metadata_matches_reference_rule():
     assert m["atomic_add_dkdv"] is True
     m1 = O.cp_metadata(cu, rank=0, world_size=2, cp_mode=1)
     assert m1["cp_cu_seqlens"] == [0, 10, 16] and m1["cp_offset"] == [0, 0]
+
+
+def test_row_subset_matches_full_oracle():
+    """nsa_forward_rows (the checker used on full-size inputs) against nsa_forward on a small varlen case: outputs,
+    selections and the gradients of a loss that only involves the sampled rows."""
+    import torch
+    from oracle import nsa_oracle as O
+    torch.manual_seed(5)
+    lens = [700, 130, 333]
+    cu = [0, 700, 830, 1163]
+    T, QH, KH, D = cu[-1], 8, 2, 64
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64)
+    q, k, v, w = mk(T, QH, D), mk(T, KH, D), mk(T, KH, D), mk(T, QH, 3)
+    rows = sorted({0, 30, 31, 32, 63, 64, 65, 511, 512, 513, 699, 700, 731, 829, 830, 900, 1162})
+    do = mk(len(rows), QH, D)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, w)]
+    o_full, parts_full = O.nsa_forward(*leaves, cu, return_parts=True)
+    (o_full[rows] * do).sum().backward()
+    g_full = [t.grad.clone() for t in leaves]
+    leaves2 = [t.clone().requires_grad_(True) for t in (q, k, v, w)]
+    o_rows, parts = O.nsa_forward_rows(*leaves2, cu, rows)
+    (o_rows * do).sum().backward()
+    assert torch.equal(parts["topk"], parts_full["topk"][:, rows])
+    assert torch.allclose(o_rows, o_full[rows], atol=1e-10, rtol=1e-10)
+    for a, b in zip(g_full, [t.grad for t in leaves2]):
+        assert torch.allclose(a, b, atol=1e-9, rtol=1e-9)
