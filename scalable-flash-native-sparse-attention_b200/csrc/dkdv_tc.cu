@@ -3,7 +3,7 @@
 // One CTA owns a 64-row K/V tile (compressed rows, a 64-key stretch of a sequence, or one selected block) and a slice
 // of the queries that see it.  Query rows come in tiles of 128 = (128/G tokens) x (G heads of the kv head), taken from
 // a contiguous token range (compressed, sliding window) or gathered through the key-block -> queries lists (selected).
-// Two warp groups of 128 threads each work on their own query tile (ping-pong), a ninth warp issues every MMA and three
+// Two warp groups of 128 threads each work on their own query tile (ping-pong), a ninth warp issues every MMA and six
 // more fetch the Q / dO tiles with TMA, one (64 d) x (G heads) x (1 token) box per lane, as soon as a group's buffers
 // are free:
 //     S    = Q K^T          M = query rows, N = keys      (A, B from shared memory, K-major)
@@ -32,7 +32,7 @@ __device__ __forceinline__ int find_le_tc(const int32_t* cu, int n, int x) {
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(480, 1)
     dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo) {
   using namespace tc;
   constexpr int BK = 64, BQ = 128;
@@ -171,10 +171,10 @@ __global__ void __launch_bounds__(384, 1)
     }
   } else if (warp >= 9) {
     // ================================================= TMA producer: tile `it` goes to the buffers of group it & 1
-    // three producer warps; box b belongs to lane b / 3 of warp 9 + b % 3, so that a small box count still spreads over
+    // six producer warps; box b belongs to lane b / 6 of warp 9 + b % 6, so that a small box count still spreads over
     // all of them (each thread's TMA instruction is issued on its own)
-    const int lane = (tid & 31) * 3 + (warp - 9);
-    constexpr int NP = 96;
+    const int lane = (tid & 31) * 6 + (warp - 9);
+    constexpr int NP = 192;
     constexpr int SLABS = D / 64;
     const int n_box = TOKQ * SLABS * 2;
     const uint32_t tx = (uint32_t)(TOKQ * G) * D * 2 * 2;
@@ -320,7 +320,7 @@ int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q/dout must be 16-byte aligned, n_q_rows set)", name);
     return NSA_ERR_CUDA;
   }
-  dkdv_tc_kernel<D, MODE><<<grid, 384, smem, st>>>(*p, L, tmq, tmo);
+  dkdv_tc_kernel<D, MODE><<<grid, 480, smem, st>>>(*p, L, tmq, tmo);
   return check_launch(name);
 }
 
