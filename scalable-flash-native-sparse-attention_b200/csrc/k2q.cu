@@ -41,12 +41,17 @@ __global__ void k2q_zero_kernel(NsaK2qParams p) {
   if (i < n_cur) p.cursor[i] = 0;
 }
 
+// Threads are slot-major (thread i = slot i / Tq of token i % Tq), so a warp holds one slot of 32 consecutive tokens: the
+// forced slots (initial block, local blocks) then name the same block row in every lane, and one atomic per distinct
+// row per warp (match + leader) replaces up to 32 atomics on one address.
 __global__ void k2q_count_kernel(NsaK2qParams p) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int kh = blockIdx.y;
-  if (i >= p.Tq * p.hp.top_n) return;
-  int row = entry_row(p, kh, i / p.hp.top_n, (int)(i % p.hp.top_n));
-  if (row >= 0) atomicAdd(p.offsets + (int64_t)kh * (p.n_blocks_total + 1) + row + 1, 1);
+  const int lane = threadIdx.x & 31;
+  int row = -1;
+  if (i < p.Tq * p.hp.top_n) row = entry_row(p, kh, i % p.Tq, (int)(i / p.Tq));
+  const unsigned grp = __match_any_sync(0xffffffffu, row);
+  if (row >= 0 && lane == __ffs(grp) - 1) atomicAdd(p.offsets + (int64_t)kh * (p.n_blocks_total + 1) + row + 1, __popc(grp));
 }
 
 // in-place inclusive scan of offsets[kh][1..n] (offsets[kh][0] stays 0): one CTA of 1024 threads per kv head
@@ -89,11 +94,20 @@ __global__ void k2q_scan_kernel(NsaK2qParams p) {
 __global__ void k2q_fill_kernel(NsaK2qParams p) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int kh = blockIdx.y;
-  if (i >= p.Tq * p.hp.top_n) return;
-  int64_t q_row = i / p.hp.top_n;
-  int row = entry_row(p, kh, q_row, (int)(i % p.hp.top_n));
+  const int lane = threadIdx.x & 31;
+  int row = -1;
+  int64_t q_row = 0;
+  if (i < p.Tq * p.hp.top_n) {
+    q_row = i % p.Tq;
+    row = entry_row(p, kh, q_row, (int)(i / p.Tq));
+  }
+  const unsigned grp = __match_any_sync(0xffffffffu, row);
+  const int leader = __ffs(grp) - 1;
+  int base = 0;
+  if (row >= 0 && lane == leader) base = atomicAdd(p.cursor + (int64_t)kh * p.n_blocks_total + row, __popc(grp));
+  base = __shfl_sync(0xffffffffu, base, leader);
   if (row < 0) return;
-  int pos = p.offsets[(int64_t)kh * (p.n_blocks_total + 1) + row] + atomicAdd(p.cursor + (int64_t)kh * p.n_blocks_total + row, 1);
+  const int pos = p.offsets[(int64_t)kh * (p.n_blocks_total + 1) + row] + base + __popc(grp & ((1u << lane) - 1));
   p.tokens[(int64_t)kh * (p.Tq * p.hp.top_n) + pos] = (int)q_row;
 }
 
