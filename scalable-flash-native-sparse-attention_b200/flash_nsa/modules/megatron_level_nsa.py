@@ -124,9 +124,11 @@ class NSAFunction(torch.autograd.Function):
         dq = torch.empty_like(q)
         dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
         dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
-        # sliding window writes dq, the other branches add into it; every branch adds into the fp32 dk/dv
-        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2])
-        slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1])
+        # the selected branch writes dq (its per-token warps would pay most for a read-modify-write), the dense branches
+        # add into it in their row-per-thread epilogues; every branch adds into the fp32 dk/dv
+        slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1],
+                     accumulate_dq=False)
+        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=True)
         _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
                                          delta=deltas[0])
         _, dwk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper)
@@ -134,8 +136,8 @@ class NSAFunction(torch.autograd.Function):
         return dq, dk, dv, dcombine_weight, dwk, dwv, None
 
 
-def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper, delta=None):
-    """Sliding-window backward that OVERWRITES dq (bf16) and adds into dk/dv (fp32)."""
+def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper, delta=None, accumulate_dq=False):
+    """Sliding-window backward that writes (or adds into) dq (bf16) and adds into dk/dv (fp32)."""
     from ..ops._common import attn_params, call
     if not (dout.stride(-1) == 1 and dout.stride(1) == dout.size(-1)):
         dout = dout.contiguous()
@@ -143,7 +145,7 @@ def _swa_bwd_into(q, k, v, o, lse, dout, dq, dk, dv, sm_scale, helper, delta=Non
     if not have_delta:
         delta = torch.empty_like(lse)
     p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=dout, delta=delta, dq=dq, dk=dk, dv=dv)
-    p.accumulate_dq = 0
+    p.accumulate_dq = int(accumulate_dq)
     if have_delta:
         p.phases = 6
     if q.size(0) > 0:
@@ -255,8 +257,9 @@ class CPNSAFunction(torch.autograd.Function):
                                                      dw=dcombine_weight[:, h0 * G:(h0 + stride) * G],
                                                      deltas=[deltas[0].t(), deltas[1], deltas[2]])
             dk, dv = comm.grad_buffers()  # zero-filled fp32 [t*W, stride, d]
-            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2])
-            slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1])
+            slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1],
+                         accumulate_dq=False)
+            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=True)
             _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
                                              delta=deltas[0])
             _, fk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper, async_dw=True)

@@ -20,7 +20,8 @@ def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
 
 
 def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=None, fuse_dqdkdv=False,
-                 dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None):
+                 dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None,
+                 accumulate_dq=None):
     """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
     otherwise dq is new and dk/dv come back in k's dtype.  Deterministic: one CTA owns a key block."""
     T, QH, D = q.shape
@@ -28,7 +29,7 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
         sm_scale = D ** -0.5
     if not (do.stride(-1) == 1 and do.stride(1) == do.size(-1)):
         do = do.contiguous()
-    acc_dq = dq is not None
+    acc_dq = (dq is not None) if accumulate_dq is None else bool(accumulate_dq)   # False with a given dq: overwrite it
     if dq is None:
         dq = torch.empty_like(q)
     own = dk is None
