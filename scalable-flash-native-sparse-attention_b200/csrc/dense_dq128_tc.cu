@@ -225,12 +225,16 @@ __global__ void __launch_bounds__(320, 1)
       fence_before_sync();
       mbar_arrive(ds_ready);
     }
-    if (!mbar_wait(done, 0, &budget)) timed_out = true;
-    fence_after_sync();
-
-    // ---- epilogue: my half of my row of dQ
+    // ---- epilogue: my half of my row of dQ; when adding into an existing dq its old values are fetched before the
+    // wait for the last MMA, so that their latency is hidden
     const float sc = p.sm_scale;
     __nv_bfloat16* dq_row = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)(kh * G + g) * D + h * (D / 2);
+    uint4 old[D / 16];
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c)
+      old[c] = (p.accumulate_dq && row_ok) ? *reinterpret_cast<const uint4*>(dq_row + c * 8) : make_uint4(0, 0, 0, 0);
+    if (!mbar_wait(done, 0, &budget)) timed_out = true;
+    fence_after_sync();
     const uint32_t acc = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TM_DQ + h * (D / 2);
 #pragma unroll
     for (int c = 0; c < D / 64; ++c) {
@@ -240,18 +244,15 @@ __global__ void __launch_bounds__(320, 1)
       if (row_ok) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
+          const uint4 od = old[c * 4 + q4];
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[q4 * 8 + e]) * sc;
-          uint4* dst = reinterpret_cast<uint4*>(dq_row + c * 32 + q4 * 8);
-          if (p.accumulate_dq) {
-            const uint4 old = *dst;
-            f[0] += bf16_lo(old.x); f[1] += bf16_hi(old.x); f[2] += bf16_lo(old.y); f[3] += bf16_hi(old.y);
-            f[4] += bf16_lo(old.z); f[5] += bf16_hi(old.z); f[6] += bf16_lo(old.w); f[7] += bf16_hi(old.w);
-          }
+          f[0] += bf16_lo(od.x); f[1] += bf16_hi(od.x); f[2] += bf16_lo(od.y); f[3] += bf16_hi(od.y);
+          f[4] += bf16_lo(od.z); f[5] += bf16_hi(od.z); f[6] += bf16_lo(od.w); f[7] += bf16_hi(od.w);
           uint4 wv;
           wv.x = pack_bf16(f[0], f[1]); wv.y = pack_bf16(f[2], f[3]); wv.z = pack_bf16(f[4], f[5]); wv.w = pack_bf16(f[6], f[7]);
-          *dst = wv;
+          *reinterpret_cast<uint4*>(dq_row + c * 32 + q4 * 8) = wv;
         }
       }
     }
