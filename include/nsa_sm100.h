@@ -288,6 +288,21 @@ typedef struct NsaReorderParams {
 /* replaces reorder, flash_nsa/ops/reorder.py:43-93 (out of place) */
 int nsa_reorder(const NsaReorderParams* p, void* stream);
 
+/* ---- rotary position embedding (demo layers) ---------------------------------------------------------- */
+typedef struct NsaRopeParams {
+  const void *q, *k;     /* [B,N,QH,D], [B,N,KH,D] bf16; backward: the gradients of qe, ke                          */
+  void *qe, *ke;         /* outputs, same shapes; may alias q, k (in place)                                          */
+  const void *cos, *sin; /* [B,N,D] bf16 (a broadcast batch has stride 0)                                            */
+  int64_t q_stride_b, q_stride_n, q_stride_h, k_stride_b, k_stride_n, k_stride_h;
+  int64_t qe_stride_b, qe_stride_n, qe_stride_h, ke_stride_b, ke_stride_n, ke_stride_h;
+  int64_t cos_stride_b, cos_stride_n; /* shared by cos and sin                                                       */
+  int32_t B, N, QH, KH, D;            /* D % 16 == 0; the last dimension of every tensor is contiguous               */
+  int32_t backward;                   /* 0: e1 = x1 cos1 - x2 sin1, e2 = x2 cos2 + x1 sin2 (x1, x2 the halves of a head);
+                                         1: the transposed rotation applied to the incoming gradients               */
+} NsaRopeParams;
+/* replaces fused_apply_rope (forward and backward), flash_nsa/ops/rope.py:5-232 */
+int nsa_rope(const NsaRopeParams* p, void* stream);
+
 /* ---- misc -------------------------------------------------------------------------------------------- */
 const char* nsa_last_error(void);
 int nsa_version(void);

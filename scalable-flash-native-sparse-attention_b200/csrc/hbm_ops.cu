@@ -263,6 +263,47 @@ __global__ void combine_bwd_kernel(NsaCombineParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------ rotary embedding
+// One thread = 8 elements of the first half of a head and the matching 8 of the second half, for q heads then k heads of
+// one (batch, position) row; cos / sin are read once per thread (16 B each half).  In place is safe: a thread reads
+// both halves before it writes either.
+__global__ void rope_kernel(NsaRopeParams p) {
+  const int HC = p.D / 16;                       // 16-byte chunks per half head
+  const int per_row = (p.QH + p.KH) * HC;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = idx / per_row;
+  if (row >= (int64_t)p.B * p.N) return;
+  const int r = (int)(idx - row * per_row);
+  const int hh = r / HC, c = r - hh * HC;
+  const int64_t b = row / p.N, n = row - b * p.N;
+  const bool is_k = hh >= p.QH;
+  const int h = is_k ? hh - p.QH : hh;
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(is_k ? p.k : p.q) +
+                           (is_k ? b * p.k_stride_b + n * p.k_stride_n + h * p.k_stride_h : b * p.q_stride_b + n * p.q_stride_n + h * p.q_stride_h);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(is_k ? p.ke : p.qe) +
+                     (is_k ? b * p.ke_stride_b + n * p.ke_stride_n + h * p.ke_stride_h : b * p.qe_stride_b + n * p.qe_stride_n + h * p.qe_stride_h);
+  const int64_t co = b * p.cos_stride_b + n * p.cos_stride_n;
+  const __nv_bfloat16* cs = reinterpret_cast<const __nv_bfloat16*>(p.cos) + co;
+  const __nv_bfloat16* sn = reinterpret_cast<const __nv_bfloat16*>(p.sin) + co;
+  const int half = p.D / 2, o1 = c * 8, o2 = half + c * 8;
+  const F8 x1 = unpack8(ldg16(x + o1)), x2 = unpack8(ldg16(x + o2));
+  const F8 c1 = unpack8(ldg16(cs + o1)), c2 = unpack8(ldg16(cs + o2));
+  const F8 s1 = unpack8(ldg16(sn + o1)), s2 = unpack8(ldg16(sn + o2));
+  F8 e1, e2;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    if (!p.backward) {
+      e1.v[e] = x1.v[e] * c1.v[e] - x2.v[e] * s1.v[e];
+      e2.v[e] = x2.v[e] * c2.v[e] + x1.v[e] * s2.v[e];
+    } else {   // x1, x2 are the gradients of e1, e2
+      e1.v[e] = x1.v[e] * c1.v[e] + x2.v[e] * s2.v[e];
+      e2.v[e] = x2.v[e] * c2.v[e] - x1.v[e] * s1.v[e];
+    }
+  }
+  *reinterpret_cast<uint4*>(y + o1) = pack8(e1);
+  *reinterpret_cast<uint4*>(y + o2) = pack8(e2);
+}
+
 // ------------------------------------------------------------------------------------------------ chunk reorder
 // "shuffle": sequential chunk m < W goes to slot 2m, chunk m+W goes to slot 2(W-m)-1 ... i.e. slot 2i holds
 // chunk i and slot 2i+1 holds chunk 2W-1-i.  "unshuffle" is the inverse.
@@ -431,6 +472,20 @@ extern "C" int nsa_combine_bwd(const NsaCombineParams* p, void* stream) {
   if (n == 0) return NSA_OK;
   combine_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
   return check_launch("combine_bwd");
+}
+
+extern "C" int nsa_rope(const NsaRopeParams* p, void* stream) {
+  NSA_REQUIRE(p && p->q && p->k && p->qe && p->ke && p->cos && p->sin, NSA_ERR_BAD_ARG, "rope: null pointer");
+  NSA_REQUIRE(p->D > 0 && p->D % 16 == 0, NSA_ERR_UNSUPPORTED_SHAPE, "rope: D=%d must be a multiple of 16", p->D);
+  NSA_REQUIRE((p->q_stride_h | p->q_stride_n | p->q_stride_b | p->k_stride_h | p->k_stride_n | p->k_stride_b | p->qe_stride_h |
+               p->qe_stride_n | p->qe_stride_b | p->ke_stride_h | p->ke_stride_n | p->ke_stride_b | p->cos_stride_b | p->cos_stride_n) % 8 == 0,
+              NSA_ERR_BAD_ARG, "rope: strides must be multiples of 8 elements (16-byte vectors)");
+  NSA_REQUIRE(((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->qe | (uintptr_t)p->ke | (uintptr_t)p->cos | (uintptr_t)p->sin) % 16 == 0,
+              NSA_ERR_BAD_ARG, "rope: pointers must be 16-byte aligned");
+  const int64_t n = (int64_t)p->B * p->N * (p->QH + p->KH) * (p->D / 16);
+  if (n <= 0) return NSA_OK;
+  rope_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("rope");
 }
 
 extern "C" int nsa_reorder(const NsaReorderParams* p, void* stream) {

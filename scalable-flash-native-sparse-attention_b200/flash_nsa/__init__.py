@@ -14,4 +14,7 @@ from .ops.combine import fused_sigmoid_combine
 
 from .modules.megatron_level_nsa import NSACore, flash_nsa_varlen_func, cp_flash_nsa_varlen_func
 
+from .layers.megatron_level_nsa import NSA
+from .layers.hf_level_nsa import HFNSA
+
 from .inference import nsa_prefill, nsa_decode

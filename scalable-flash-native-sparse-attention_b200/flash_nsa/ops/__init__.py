@@ -7,3 +7,4 @@ from .topk import get_bind_from_find, slc_topk_indices
 from .select_attn import select_attn, slc_attn_bwd, slc_attn_fwd
 from .sliding_window_attention import (swa_bwd, swa_fwd, swa_varlen_func, two_stage_swa_bwd, two_stage_swa_fwd)
 from .reorder import reorder
+from .rope import fused_apply_rope
