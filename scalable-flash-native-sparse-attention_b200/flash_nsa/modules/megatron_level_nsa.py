@@ -24,7 +24,15 @@ def weight_grad(input, grad_output, weight):
     grad_output = grad_output.reshape(-1, grad_output.size(-1))
     main_grad = getattr(weight, "main_grad", None)
     if main_grad is not None:
-        main_grad.addmm_(grad_output.t().to(main_grad.dtype), input.to(main_grad.dtype))
+        # the trainer's fp32 accumulation buffer: one library GEMM on the bf16 operands with an fp32 result, added in place
+        # (flash_nsa/modules/megatron_level_nsa.py:20-44 uses apex's wgrad_gemm_accum_fp32 or its Triton GEMM for this)
+        if main_grad.dtype == torch.float32 and input.dtype != torch.float32:
+            try:
+                main_grad.add_(torch.mm(grad_output.t(), input, out_dtype=torch.float32))
+            except (TypeError, RuntimeError):
+                main_grad.addmm_(grad_output.t().to(main_grad.dtype), input.to(main_grad.dtype))
+        else:
+            main_grad.addmm_(grad_output.t().to(main_grad.dtype), input.to(main_grad.dtype))
         if hasattr(weight, "grad_added_to_main_grad"):
             weight.grad_added_to_main_grad = True
             return torch.empty(main_grad.shape, dtype=input.dtype, device=input.device, requires_grad=False)

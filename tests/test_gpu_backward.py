@@ -256,3 +256,35 @@ def test_against_reference_golden_grads(name):
     _check("slc dq", qd.grad[::step], g["slc_dq"])
     _check("slc dk", kd.grad, g["slc_dk"])
     _check("slc dv", vd.grad, g["slc_dv"])
+
+
+def test_compress_weight_grads_accumulate_into_main_grad():
+    """With a trainer-provided fp32 `main_grad` on the compression weights (Megatron's gradient-accumulation fusion) the
+    weight gradients are added into it and autograd gets a placeholder; the sums equal the plain .grad of a second run."""
+    lens = [600, 333]
+    QH, KH, D = 8, 2, 64
+    q, k, v, w, do, cu = _mk(lens, QH, KH, D, seed=31)
+    fn = _setup(cu)
+    cfg = fn.NSAConfig(head_dim=D, num_heads=QH, num_kv_heads=KH, cmp_k_method="linear", cmp_v_method="swiglu")
+    cu_d = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    g = torch.Generator().manual_seed(4)
+    res = {}
+    for mode in ("plain", "main_grad"):
+        core = fn.NSACore(cfg)
+        g.manual_seed(4)
+        for prm in (core.cmp_k_weight, core.cmp_v_weight):
+            prm.data = (torch.randn(prm.shape, generator=g) * 0.02).bfloat16().cuda()
+            if mode == "main_grad":
+                prm.main_grad = torch.full(prm.shape, 0.5, dtype=torch.float32, device="cuda")
+                prm.grad_added_to_main_grad = False
+        qd, kd, vd, wd = [t.cuda().clone().requires_grad_(True) for t in (q, k, v, w)]
+        o = core(qd, kd, vd, wd, cu_d)
+        o.backward(do.cuda())
+        if mode == "plain":
+            res[mode] = [core.cmp_k_weight.grad.float(), core.cmp_v_weight.grad.float()]
+        else:
+            assert core.cmp_k_weight.grad_added_to_main_grad and core.cmp_v_weight.grad_added_to_main_grad
+            res[mode] = [core.cmp_k_weight.main_grad - 0.5, core.cmp_v_weight.main_grad - 0.5]
+    for a, b in zip(res["plain"], res["main_grad"]):
+        scale = max(1.0, a.abs().max().item())
+        assert (a - b).abs().max().item() <= 1e-2 * scale
