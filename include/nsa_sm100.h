@@ -288,6 +288,17 @@ typedef struct NsaReorderParams {
 /* replaces reorder, flash_nsa/ops/reorder.py:43-93 (out of place) */
 int nsa_reorder(const NsaReorderParams* p, void* stream);
 
+/* ---- writing new K/V rows into the paged cache (inference caller) -------------------------------------- */
+typedef struct NsaStoreKvParams {
+  const void *key, *value;     /* [N, H*D] bf16 rows (row strides below), the new tokens of a step                  */
+  void *k_cache, *v_cache;     /* [slots, H*D] bf16, rows contiguous                                                 */
+  const int32_t* slot_mapping; /* [N] flat cache row of every new token, -1 = skip (padding of a captured graph)     */
+  int64_t key_stride, value_stride;
+  int32_t N, row_elems;        /* row_elems = H*D, a multiple of 8                                                   */
+} NsaStoreKvParams;
+/* replaces store_kvcache, nano-vllm/nanovllm/layers/attention.py:123-154 */
+int nsa_store_kvcache(const NsaStoreKvParams* p, void* stream);
+
 /* ---- rotary position embedding (demo layers) ---------------------------------------------------------- */
 typedef struct NsaRopeParams {
   const void *q, *k;     /* [B,N,QH,D], [B,N,KH,D] bf16; backward: the gradients of qe, ke                          */

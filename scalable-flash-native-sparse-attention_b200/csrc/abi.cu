@@ -87,6 +87,7 @@ extern "C" int nsa_struct_size(const char* name) {
   NSA_SZ(NsaCombineParams);
   NSA_SZ(NsaReorderParams);
   NSA_SZ(NsaRopeParams);
+  NSA_SZ(NsaStoreKvParams);
   NSA_SZ(NsaPagedPoolParams);
   NSA_SZ(NsaDecodeParams);
 #undef NSA_SZ

@@ -263,6 +263,22 @@ __global__ void combine_bwd_kernel(NsaCombineParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------ cache store
+__global__ void store_kvcache_kernel(NsaStoreKvParams p) {
+  const int CH = p.row_elems / 8;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t n = idx / CH;
+  if (n >= p.N) return;
+  const int c = (int)(idx - n * CH);
+  const int slot = __ldg(p.slot_mapping + n);
+  if (slot < 0) return;
+  const __nv_bfloat16* ks = reinterpret_cast<const __nv_bfloat16*>(p.key) + n * p.key_stride + c * 8;
+  const __nv_bfloat16* vs = reinterpret_cast<const __nv_bfloat16*>(p.value) + n * p.value_stride + c * 8;
+  const int64_t off = (int64_t)slot * p.row_elems + c * 8;
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.k_cache) + off) = ldg16(ks);
+  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.v_cache) + off) = ldg16(vs);
+}
+
 // ------------------------------------------------------------------------------------------------ rotary embedding
 // One thread = 8 elements of the first half of a head and the matching 8 of the second half, for q heads then k heads of
 // one (batch, position) row; cos / sin are read once per thread (16 B each half).  In place is safe: a thread reads
@@ -472,6 +488,16 @@ extern "C" int nsa_combine_bwd(const NsaCombineParams* p, void* stream) {
   if (n == 0) return NSA_OK;
   combine_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
   return check_launch("combine_bwd");
+}
+
+extern "C" int nsa_store_kvcache(const NsaStoreKvParams* p, void* stream) {
+  NSA_REQUIRE(p && p->key && p->value && p->k_cache && p->v_cache && p->slot_mapping, NSA_ERR_BAD_ARG, "store_kvcache: null pointer");
+  NSA_REQUIRE(p->row_elems > 0 && p->row_elems % 8 == 0 && p->key_stride % 8 == 0 && p->value_stride % 8 == 0, NSA_ERR_BAD_ARG,
+              "store_kvcache: rows must be multiples of 8 elements");
+  const int64_t n = (int64_t)p->N * (p->row_elems / 8);
+  if (n <= 0) return NSA_OK;
+  store_kvcache_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("store_kvcache");
 }
 
 extern "C" int nsa_rope(const NsaRopeParams* p, void* stream) {

@@ -13,6 +13,23 @@ from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_dec
                   combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported)
 
 
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping):
+    """Write the new tokens' K/V rows into the paged cache: key/value [n, kh, d], caches [pages, page_size, kh, d],
+    slot_mapping int32 [n] = flat cache row per token (-1 = skip).  The caller-side op of the serving engine
+    (nano-vllm/nanovllm/layers/attention.py:147-154)."""
+    from ..ops._common import S, call, ptr
+    N, H, D = key.shape
+    row = H * D
+    assert key.stride(-1) == 1 and value.stride(-1) == 1 and key.stride(1) == D and value.stride(1) == D
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.size(-1) * k_cache.size(-2) == row
+    assert slot_mapping.numel() == N and slot_mapping.dtype.is_signed and slot_mapping.element_size() == 4
+    p = S["NsaStoreKvParams"]()
+    p.key, p.value, p.k_cache, p.v_cache, p.slot_mapping = ptr(key), ptr(value), ptr(k_cache), ptr(v_cache), ptr(slot_mapping)
+    p.key_stride, p.value_stride, p.N, p.row_elems = key.stride(0), value.stride(0), N, row
+    if N > 0:
+        call("nsa_store_kvcache", p, key)
+
+
 def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, context_lens, block_tables, cmp_slot_mapping,
                 cmp_block_tables, fixed_y_maxlen=8192, fixed_num_slc_blocks=2048, kernel_size=32, stride=16, block_size=64,
                 top_n=16, num_init_blocks=1, num_local_blocks=2, window_size=512, sm_scale=None):

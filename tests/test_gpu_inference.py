@@ -179,3 +179,64 @@ def test_decode_writes_the_new_compressed_row():
     got_k = cache.k.view(-1, KH, D)[slot].float().cpu()
     got_v = cache.v.view(-1, KH, D)[slot].float().cpu()
     assert (got_k - ref_k).abs().max().item() <= 8e-3 and (got_v - ref_v).abs().max().item() <= 8e-3
+
+
+def test_generation_loop_prefill_then_many_decode_steps():
+    """A serving loop: prefill a prompt, then 70 decode steps (crossing 16-token pooling boundaries, 64-token selection
+    blocks and a page boundary).  Every step stores the new K/V rows with store_kvcache, passes the slot of the compressed
+    row that the step completes, and is compared with the oracle run on the whole un-paged prefix; at the end the
+    compressed rows held by the cache equal the pooled rows of the whole sequence."""
+    from flash_nsa import nsa_prefill, nsa_decode
+    from flash_nsa.inference import store_kvcache
+    QH, KH, D = 16, 4, 128
+    prompt, steps = [200, 77], 70
+    lens = [p + steps for p in prompt]
+    seqs = _seqs(lens, QH, KH, D, seed=9)
+    cache = Cache(lens, KH, D, seed=4).cuda()
+    B = len(lens)
+
+    def tok_slot(b, pos):
+        return int(cache.block_tables[b, pos // PAGE]) * PAGE + pos % PAGE
+
+    # ---- prefill of the prompts (K/V rows go in through store_kvcache)
+    k_new = torch.cat([seqs[b]["k"][:prompt[b]] for b in range(B)]).cuda()
+    v_new = torch.cat([seqs[b]["v"][:prompt[b]] for b in range(B)]).cuda()
+    slots = torch.tensor([tok_slot(b, p) for b in range(B) for p in range(prompt[b])], dtype=torch.int32, device="cuda")
+    store_kvcache(k_new, v_new, cache.k, cache.v, slots)
+    y_len = [max((p - 32) // 16 + 1, 0) for p in prompt]
+    x_cu = torch.tensor([0, prompt[0], prompt[0] + prompt[1]], dtype=torch.int32, device="cuda")
+    y_cu = torch.tensor([0, y_len[0], y_len[0] + y_len[1]], dtype=torch.int32, device="cuda")
+    cmp_slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    q = torch.cat([seqs[b]["q"][:prompt[b]] for b in range(B)]).cuda()
+    w = torch.cat([seqs[b]["w"][:prompt[b]] for b in range(B)]).cuda()
+    o = nsa_prefill(q, cache.k, cache.v, w, x_cu, y_cu, max(prompt), max(y_len), torch.tensor(prompt, dtype=torch.int32, device="cuda"),
+                    cache.block_tables, cmp_slots, cache.cmp_block_tables)
+    off = 0
+    for b in range(B):
+        assert _bulk_ok(o[off:off + prompt[b]], _oracle(seqs[b], prompt[b])), f"prefill seq {b}"
+        off += prompt[b]
+
+    # ---- decode steps
+    refs = [_oracle(seqs[b], lens[b]) for b in range(B)]      # causal: row t only depends on the first t+1 tokens
+    worst = 0.0
+    for s in range(steps):
+        ctx = [prompt[b] + s + 1 for b in range(B)]           # tokens in the cache after this step's store
+        pos = [c - 1 for c in ctx]
+        k1 = torch.stack([seqs[b]["k"][pos[b]] for b in range(B)]).cuda()
+        v1 = torch.stack([seqs[b]["v"][pos[b]] for b in range(B)]).cuda()
+        store_kvcache(k1, v1, cache.k, cache.v, torch.tensor([tok_slot(b, pos[b]) for b in range(B)], dtype=torch.int32, device="cuda"))
+        slot = [cache.cmp_slot(b, (c - 32) // 16) if (c % 16 == 0 and c >= 32) else -1 for b, c in enumerate(ctx)]
+        q1 = torch.stack([seqs[b]["q"][pos[b]] for b in range(B)]).cuda()
+        w1 = torch.stack([seqs[b]["w"][pos[b]] for b in range(B)]).cuda()
+        o1 = nsa_decode(q1, cache.k, cache.v, w1, torch.tensor(ctx, dtype=torch.int32, device="cuda"), cache.block_tables,
+                        torch.tensor(slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+        for b in range(B):
+            err = (o1[b].float().cpu() - refs[b][pos[b]]).abs().max().item()
+            worst = max(worst, err)
+            assert err <= TOL, f"decode step {s} seq {b}: {err}"
+    # ---- the cache's compressed rows are the pooled rows of the whole sequences
+    for b in range(B):
+        Y = (lens[b] - 32) // 16 + 1
+        ref_k = O.mean_pool(seqs[b]["k"].float(), [0, lens[b]])
+        got = torch.stack([cache.k.view(-1, KH, D)[cache.cmp_slot(b, j)] for j in range(Y)]).float().cpu()
+        assert (got - ref_k).abs().max().item() <= 8e-3
