@@ -1,22 +1,26 @@
 // One decode step of NSA for a batch of sequences over a paged KV cache, fused into a single kernel.
 // CTA = (sequence, kv head), 8 warps.  The query heads of the kv head are the 16 rows of the warp-level MMA tile and
-// every K/V row is read straight from the cache pages (see warp_tile.cuh); the KV range of each branch is split over the
-// warps and their partial softmax states are merged through shared memory:
+// every 64-row K/V tile is copied from the cache pages into the warp's private shared-memory buffer with all its
+// cp.async copies in flight at once (see warp_tile_smem.cuh); the KV range of each branch is split over the warps and
+// their partial softmax states are merged through shared memory:
 //   0. the window of 32 tokens ending at the new token is pooled into the new compressed K/V row (when it completes one)
 //   1. compressed attention: 64-row tiles of compressed K/V round-robin over the 8 warps  -> cmp_o, lse
 //   2. block scores: the same K tiles again, P[j] = sum_heads exp2(s - lse), pooled 4 -> 1 (+ the row before)
-//   3. top-n: forced blocks + (top_n - forced) rounds of CTA-wide arg-max (ties: lowest block index)
-//   4. selected blocks on warps 0-3, sliding-window tiles on warps 4-7
+//   3. top-n on warp 0: forced blocks + (top_n - forced) rounds of warp-wide arg-max (ties: lowest block index)
+//   4. selected blocks on warps 0-4 (the forced ones start before the selection is known), sliding-window tiles on
+//      warps 5-7, concurrently with 3
 //   5. o = sigmoid(w0) cmp_o + sigmoid(w1) slc_o + sigmoid(w2) swa_o
 // Bytes read per (sequence, kv head): compressed K twice and V once, 16 selected blocks and <= 9 window tiles of K and V.
-#include "warp_tile.cuh"
+#include "warp_tile_smem.cuh"
 
 namespace nsa {
 
 template <int D>
 __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p) {
   constexpr int CH = D / 8, STATE = 32 + 16 * D;
-  extern __shared__ __align__(16) float sm[];
+  constexpr uint32_t TILE_BYTES = 64 * D * 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  float* sm = reinterpret_cast<float*>(smem_raw + 8 * TILE_BYTES);   // the first 8 x TILE_BYTES: one K/V tile buffer per warp
   float* state = sm;                        // 8 x STATE floats; reused for the score arrays between phases 1 and 4
   float* cmp_o_s = sm + 8 * STATE;          // [16][D]
   float* lse_s = cmp_o_s + 16 * D;          // [16]
@@ -76,8 +80,9 @@ __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p)
     __syncthreads();  // the row is read below by other threads of this CTA (plain loads, no read-only path)
   }
 
-  uint4 qa[D / 32], qb[D / 32];
-  wt::load_q<D>(qa, qb, reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)b * p.q_stride_t + (int64_t)kh * G * D, G, lane);
+  uint32_t qf[D / 16][4];
+  wts::load_q<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)b * p.q_stride_t + (int64_t)kh * G * D, G, lane);
+  const uint32_t buf = smem_u32(smem_raw) + warp * TILE_BYTES;
   const float c2 = p.sm_scale * 1.4426950408889634f;
   const int n_ct = (Y + 63) >> 6;
 
@@ -102,13 +107,13 @@ __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p)
 
   // ---- 1. compressed attention
   {
-    wt::Acc<D> acc;
+    wts::Acc<D> acc;
     acc.init();
     for (int tile = warp; tile < n_ct; tile += 8) {
       const int j0 = tile << 6;
-      wt::attend64<D>(acc, qa, qb, kc, vc, cs, cs, [&](int i) { return cmprow(min(j0 + i, Y - 1)); }, [&](int i) { return j0 + i < Y; }, c2, lane);
+      wts::attend64<D>(acc, qf, buf, kc, vc, cs, cs, [&](int i) { return cmprow(min(j0 + i, Y - 1)); }, [&](int i) { return j0 + i < Y; }, c2, lane);
     }
-    wt::store_state<D>(acc, state + warp * STATE, lane);
+    wts::store_state<D>(acc, state + warp * STATE, lane);
   }
   __syncthreads();
   for (int idx = tid; idx < 16 * D; idx += 256) {
@@ -127,7 +132,10 @@ __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p)
     for (int tile = warp; tile < n_ct; tile += 8) {
       const int j0 = tile << 6;
       float s[8][4];
-      wt::scores64<D>(s, qa, qb, kc, cs, [&](int i) { return cmprow(min(j0 + i, Y - 1)); }, lane);
+      wts::fill_async<D>(buf, kc, cs, [&](int i) { return cmprow(min(j0 + i, Y - 1)); }, lane);
+      wts::fill_wait();
+      wts::scores64<D>(s, qf, buf, lane);
+      __syncwarp();
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int col = j0 + nt * 8 + 2 * c_;
@@ -149,86 +157,90 @@ __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p)
     }
   }
   __syncthreads();
-  // ---- 3. pooled block scores and the selection
+  // ---- 3 + 4. selection on warp 0, selected blocks on warps 0-4, sliding window on warps 5-7.
+  // The window tiles and the forced blocks do not depend on the selection, so warps 5-7 and 1-3 start on them at once and
+  // the memory system stays busy while warp 0 picks the free blocks (pooling 4 -> 1, then rounds of warp-wide arg-max;
+  // ties: lowest block index).
   const int n_blk = nk + 1;
-  for (int blk = tid; blk < n_blk; blk += 256) {
-    auto at = [&](int j) { return (j >= 0 && j < Y) ? pcm[1 + j] : 0.f; };
-    const int j = 4 * blk;
-    float pv = at(j - 1) + ((2.f * at(j) + 2.f * at(j + 1)) + (2.f * at(j + 2) + at(j + 3)));
-    psl[blk] = (blk >= ni && blk <= nk - nl) ? pv : -1.f;   // forced blocks are not candidates
-  }
-  if (tid < 32) sel[tid] = -1;
-  __syncthreads();
-  const int n_free = max(0, min(top_n, nk + 1) - ni - nl);
-  for (int r = 0; r < n_free; ++r) {
-    float bv = -1.f;
-    int bi = 0x7fffffff;
-    for (int blk = tid; blk < n_blk; blk += 256) {
-      float v = psl[blk];
-      if (v > bv) {  // ascending scan keeps the lowest index among equals
-        bv = v;
-        bi = blk;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) {
-      red_v[warp] = bv;
-      red_i[warp] = bi;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      for (int w = 1; w < 8; ++w)
-        if (red_v[w] > bv || (red_v[w] == bv && red_i[w] < bi)) {
-          bv = red_v[w];
-          bi = red_i[w];
-        }
-      if (bv >= 0.f) {
-        sel[ni + nl + r] = bi;
-        psl[bi] = -1.f;
-      }
-    }
-    __syncthreads();
-  }
-  if (tid < ni) sel[tid] = (tid <= nk) ? tid : -1;
-  else if (tid < ni + nl) sel[tid] = (tid <= nk) ? nk - (tid - ni) : -1;
-  __syncthreads();
-  if (p.topk_out && tid < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + tid] = sel[tid];
   const int n_valid = min(top_n, nk + 1);
-  __syncthreads();  // every read of the score arrays is done: the states may be written again
-
-  // ---- 4. selected blocks (warps 0-3) and sliding window (warps 4-7)
+  const int n_free = max(0, n_valid - ni - nl);
   {
-    wt::Acc<D> acc;
+    wts::Acc<D> acc;
     acc.init();
-    if (warp < 4) {
-      for (int i = warp; i < n_valid; i += 4) {
-        const int blk = sel[i];
-        if (blk < 0 || blk > nk) continue;
-        const int k0 = blk << 6;
-        wt::attend64<D>(acc, qa, qb, kc, vc, cs, cs, [&](int x) { return tokrow(min(k0 + x, t)); }, [&](int x) { return k0 + x <= t; }, c2, lane);
-      }
-    } else {
+    auto block_tile = [&](int blk) {
+      const int k0 = blk << 6;
+      wts::attend64<D>(acc, qf, buf, kc, vc, cs, cs, [&](int x) { return tokrow(min(k0 + x, t)); }, [&](int x) { return k0 + x <= t; }, c2, lane);
+    };
+    if (warp >= 5) {
       const int lo = max(0, t - W);
-      for (int k0 = ((lo >> 6) << 6) + 64 * (warp - 4); k0 <= t; k0 += 256)
-        wt::attend64<D>(acc, qa, qb, kc, vc, cs, cs, [&](int x) { return tokrow(min(k0 + x, t)); },
-                        [&](int x) { return k0 + x >= lo && k0 + x <= t; }, c2, lane);
+      for (int k0 = ((lo >> 6) << 6) + 64 * (warp - 5); k0 <= t; k0 += 192)
+        wts::attend64<D>(acc, qf, buf, kc, vc, cs, cs, [&](int x) { return tokrow(min(k0 + x, t)); },
+                         [&](int x) { return k0 + x >= lo && k0 + x <= t; }, c2, lane);
+    } else {
+      if (warp == 0) {
+        for (int blk = lane; blk < n_blk; blk += 32) {
+          auto at = [&](int j) { return (j >= 0 && j < Y) ? pcm[1 + j] : 0.f; };
+          const int j = 4 * blk;
+          float pv = at(j - 1) + ((2.f * at(j) + 2.f * at(j + 1)) + (2.f * at(j + 2) + at(j + 3)));
+          psl[blk] = (blk >= ni && blk <= nk - nl) ? pv : -1.f;   // forced blocks are not candidates
+        }
+        sel[lane] = -1;
+        __syncwarp();
+        for (int r = 0; r < n_free; ++r) {
+          float bv = -1.f;
+          int bi = 0x7fffffff;
+          for (int blk = lane; blk < n_blk; blk += 32) {
+            const float v = psl[blk];
+            if (v > bv) {  // ascending scan keeps the lowest index among equals
+              bv = v;
+              bi = blk;
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+              bv = ov;
+              bi = oi;
+            }
+          }
+          if (lane == 0 && bv >= 0.f) {
+            sel[ni + nl + r] = bi;
+            psl[bi] = -1.f;
+          }
+          __syncwarp();
+        }
+        if (lane < ni) sel[lane] = (lane <= nk) ? lane : -1;
+        else if (lane < ni + nl) sel[lane] = (lane <= nk) ? nk - (lane - ni) : -1;
+        __syncwarp();
+        if (p.topk_out && lane < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + lane] = sel[lane];
+      } else if (warp - 1 < ni + nl && warp - 1 < n_valid) {
+        // forced slot warp-1: initial blocks 0.., then the local blocks nk, nk-1, ..
+        const int slot = warp - 1;
+        const int blk = slot < ni ? slot : nk - (slot - ni);
+        if (blk >= 0 && blk <= nk) block_tile(blk);
+      }
+      tc::named_barrier(1, 160);   // warps 0-4: the selection is in sel[]
+      // forced slots beyond the three head-start warps (other forced-block counts), then the free slots round-robin
+      for (int i = 0; i < n_valid; ++i) {
+        int owner;
+        if (i < ni + nl) owner = (i + 1 <= 3) ? -1 : (i % 5);          // slots 0..2 were taken by warps 1..3 above
+        else owner = ((i - ni - nl) + 4) % 5;
+        if (owner != warp) continue;
+        const int blk = sel[i];
+        if (blk >= 0 && blk <= nk) block_tile(blk);
+      }
     }
-    wt::store_state<D>(acc, state + warp * STATE, lane);
+    __syncthreads();  // every read of the score arrays is done: the states may be written again
+    wts::store_state<D>(acc, state + warp * STATE, lane);
   }
   __syncthreads();
   // ---- 5. merge + gated combine
   const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t)b * p.w_stride_t + (int64_t)kh * G * 3;
   for (int idx = tid; idx < G * D; idx += 256) {
     const int r = idx / D, c = idx - r * D;
-    const float slc = merged(0, 4, r, c, nullptr), swa = merged(4, 4, r, c, nullptr);
+    const float slc = merged(0, 5, r, c, nullptr), swa = merged(5, 3, r, c, nullptr);
     const float s0 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 0])));
     const float s1 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 1])));
     const float s2 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 2])));
@@ -258,7 +270,7 @@ extern "C" int nsa_decode_fused(const NsaDecodeParams* p, void* stream) {
   const size_t states = (size_t)8 * (32 + 16 * D) * 4, scores = ((size_t)p->y_cap + 8 + p->y_cap / 4 + 8) * 4;
   NSA_REQUIRE(scores <= states, NSA_ERR_UNSUPPORTED_SHAPE, "decode_fused: y_cap=%d too large for head dim %d (max %d)", p->y_cap, D,
               (int)((states / 4 - 16) * 4 / 5));
-  const size_t smem = states + (size_t)16 * D * 4 + 64 + 64 + 128;
+  const size_t smem = (size_t)8 * 64 * D * 2 + states + (size_t)16 * D * 4 + 64 + 64 + 128;
   cudaError_t e = (D == 128) ? cudaFuncSetAttribute(decode_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                              : cudaFuncSetAttribute(decode_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
