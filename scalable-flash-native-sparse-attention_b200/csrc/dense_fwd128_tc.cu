@@ -16,6 +16,7 @@
 // keeps the tensor core busy with one tile while the other tile's group does its softmax.
 // The running maximum of a row is only raised when the tile maximum exceeds it by more than 2^8 (the row's thread then
 // rescales its O row in tensor memory); l and the final normalisation use the same reference, so the result is exact.
+#include <algorithm>
 #include "tma.cuh"
 
 namespace nsa {
@@ -27,7 +28,7 @@ constexpr int MODE_SWA = 1;
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(576, 1)
-    dense_fwd128_tc_kernel(NsaAttnParams p, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
+    dense_fwd128_tc_kernel(NsaAttnParams p, int items, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                            const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
   constexpr int BM = 128, BN = 128, SLABS = D / 64;
@@ -42,45 +43,42 @@ __global__ void __launch_bounds__(576, 1)
   const uint32_t sV = sK + 2 * KV_BYTES;        // 2 stages
   const uint32_t bars = sV + 2 * KV_BYTES;
   const uint32_t q_full = bars, k_full = bars + 8, v_full = k_full + 16, k_free = v_full + 16, v_free = k_free + 16,
-                 s_full = v_free + 16, p_ready = s_full + 16, o_done = p_ready + 16, tm_slot = o_done + 16;
+                 s_full = v_free + 16, p_ready = s_full + 16, o_done = p_ready + 16, o_free = o_done + 16, q_free = o_free + 16, tm_slot = q_free + 8;
   float* sX = reinterpret_cast<float*>(smem_raw + 2 * Q_BYTES + 4 * KV_BYTES + 256);   // row maxima / sums crossing the two column halves
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
   const int TOK = BM / G;
-  const int pair = gridDim.x - 1 - blockIdx.x;
   const int kh = blockIdx.z;
   const Piece pc = load_piece(p.meta, blockIdx.y);
-  const int t0 = pair * 2 * TOK;
-  if (t0 >= pc.len) return;
-  const int ntok = min(2 * TOK, pc.len - t0);
-  const int tabs_min = pc.off + t0, tabs_max = tabs_min + ntok - 1;
   const int ks = p.hp.kernel_size, st = p.hp.stride, W = p.hp.window;
-
-  int kv_lo, kv_hi, kv_bos;
-  if (MODE == MODE_CMP) {
-    kv_lo = 0;
-    kv_hi = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
-    kv_bos = pc.y_bos;
-  } else {
-    kv_lo = (max(0, tabs_min - W) / BN) * BN;   // tiles on a fixed grid of key positions: a row's result does not
-    kv_hi = min(tabs_max + 1, pc.x_len);        // depend on which rows share its CTA (shards reproduce the full run)
-    kv_bos = pc.x_bos;
-  }
-  const int ntiles = (kv_hi > kv_lo) ? (kv_hi - kv_lo + BN - 1) / BN : 0;
-
-  if (ntiles == 0) {  // nothing visible for the whole pair: zeros
-    if (tid < 256) {
-      const int tok = (tid >> 7) * TOK + (tid & 127) / G, g = (tid & 127) % G;
-      if (tok < ntok) {
-        const int64_t q_row = pc.q_start + t0 + tok;
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D);
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) o[c] = make_uint4(0, 0, 0, 0);
-        if (p.lse) p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h] = 0.f;
-      }
+  const int kv_bos = (MODE == MODE_CMP) ? pc.y_bos : pc.x_bos;
+  // This CTA's query-tile pairs: `items` consecutive ones.  All roles walk them with the same two running counters: qi
+  // (pairs with work done so far) and gt (K/V tiles done so far), from which every barrier phase and ring stage is
+  // derived, so the loads and the first products of the next pair run under the epilogue of the current one.
+  const int pair0 = (gridDim.x - 1 - blockIdx.x) * items;
+  struct Item {
+    int t0, ntok, tabs_min, kv_lo, kv_hi, ntiles;
+  };
+  auto item_of = [&](int i, Item& it) -> bool {
+    it.t0 = (pair0 + i) * 2 * TOK;
+    if (it.t0 >= pc.len) return false;
+    it.ntok = min(2 * TOK, pc.len - it.t0);
+    it.tabs_min = pc.off + it.t0;
+    const int tabs_max = it.tabs_min + it.ntok - 1;
+    if (MODE == MODE_CMP) {
+      it.kv_lo = 0;
+      it.kv_hi = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
+    } else {
+      it.kv_lo = (max(0, it.tabs_min - W) / BN) * BN;   // tiles on a fixed grid of key positions: a row's result does not
+      it.kv_hi = min(tabs_max + 1, pc.x_len);           // depend on which rows share its CTA (shards reproduce the full run)
     }
-    return;
+    it.ntiles = (it.kv_hi > it.kv_lo) ? (it.kv_hi - it.kv_lo + BN - 1) / BN : 0;
+    return true;
+  };
+  {
+    Item first;
+    if (!item_of(0, first)) return;
   }
   if (base & 1023u) {
     if (tid == 0 && p.status) atomicOr(p.status, 8);
@@ -88,6 +86,7 @@ __global__ void __launch_bounds__(576, 1)
   }
   if (tid == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + 8 * s, 1);
       mbar_init(v_full + 8 * s, 1);
@@ -96,6 +95,7 @@ __global__ void __launch_bounds__(576, 1)
       mbar_init(s_full + 8 * s, 1);
       mbar_init(p_ready + 8 * s, 256);
       mbar_init(o_done + 8 * s, 1);
+      mbar_init(o_free + 8 * s, 256);
     }
     fence_mbar_init();
   }
@@ -107,33 +107,42 @@ __global__ void __launch_bounds__(576, 1)
   asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
   int budget = kWaitBudget;
   bool timed_out = false;
+  int gt = 0, qi = 0;
 
   if (warp == 17) {
     if ((tid & 31) == 0) {
       // ============================================ TMA producer
-      tma::expect_tx(q_full, 2 * Q_BYTES);
+      for (int i = 0; i < items; ++i) {
+        Item im;
+        if (!item_of(i, im)) break;
+        if (im.ntiles == 0) continue;
+        if (qi > 0 && !mbar_wait(q_free, (qi - 1) & 1, &budget)) timed_out = true;   // every S of the previous pair is done
+        tma::expect_tx(q_full, 2 * Q_BYTES);
 #pragma unroll
-      for (int w = 0; w < 2; ++w)
+        for (int w = 0; w < 2; ++w)
 #pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl)
-          tma::load_3d(sQ + w * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, pc.q_start + t0 + w * TOK, q_full);
-      for (int it = 0; it < ntiles; ++it) {
-        const int s = it & 1, row = kv_bos + kv_lo + it * BN;
-        if (it >= 2 && !mbar_wait(k_free + 8 * s, ((it >> 1) - 1) & 1, &budget)) timed_out = true;
-        tma::expect_tx(k_full + 8 * s, KV_BYTES);
+          for (int sl = 0; sl < SLABS; ++sl)
+            tma::load_3d(sQ + w * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, pc.q_start + im.t0 + w * TOK, q_full);
+        for (int it = 0; it < im.ntiles; ++it) {
+          const int g = gt + it, s = g & 1, row = kv_bos + im.kv_lo + it * BN;
+          if (g >= 2 && !mbar_wait(k_free + 8 * s, ((g >> 1) - 1) & 1, &budget)) timed_out = true;
+          tma::expect_tx(k_full + 8 * s, KV_BYTES);
 #pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sK + s * KV_BYTES + sl * K_SLAB, &tmk, sl * 64, kh, row, k_full + 8 * s);
-        if (it >= 2 && !mbar_wait(v_free + 8 * s, ((it >> 1) - 1) & 1, &budget)) timed_out = true;
-        tma::expect_tx(v_full + 8 * s, KV_BYTES);
+          for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sK + s * KV_BYTES + sl * K_SLAB, &tmk, sl * 64, kh, row, k_full + 8 * s);
+          if (g >= 2 && !mbar_wait(v_free + 8 * s, ((g >> 1) - 1) & 1, &budget)) timed_out = true;
+          tma::expect_tx(v_full + 8 * s, KV_BYTES);
 #pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sV + s * KV_BYTES + sl * K_SLAB, &tmv, sl * 64, kh, row, v_full + 8 * s);
+          for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sV + s * KV_BYTES + sl * K_SLAB, &tmv, sl * 64, kh, row, v_full + 8 * s);
+        }
+        gt += im.ntiles;
+        ++qi;
       }
     }
   } else if (warp == 16) {
     if ((tid & 31) == 0) {
       // ============================================ MMA issue
-      auto issue_s = [&](int w, int it) {   // S_w = Q_w K(it)^T
-        const uint32_t tK = sK + (it & 1) * KV_BYTES;
+      auto issue_s = [&](int w, int g) {   // S_w = Q_w K(g)^T
+        const uint32_t tK = sK + (g & 1) * KV_BYTES;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t ao = (k >> 2) * Q_SLAB + (k & 3) * 32, bo = (k >> 2) * K_SLAB + (k & 3) * 32;
@@ -141,171 +150,202 @@ __global__ void __launch_bounds__(576, 1)
         }
         mma_commit(s_full + 8 * w);
       };
-      auto issue_pv = [&](int w, int it) {  // O_w += P_w V(it); k-step u = keys 16u..16u+15; P of keys 64h.. starts at column 64h
-        const uint32_t tV = sV + (it & 1) * KV_BYTES;
-        if (!mbar_wait(p_ready + 8 * w, it & 1, &budget)) timed_out = true;
+      auto issue_pv = [&](int w, int g, bool first) {  // O_w += P_w V(g); k-step u = keys 16u..16u+15; P of keys 64h.. starts at column 64h
+        const uint32_t tV = sV + (g & 1) * KV_BYTES;
+        if (!mbar_wait(p_ready + 8 * w, g & 1, &budget)) timed_out = true;
+        // the first product of a pair overwrites O_w: the previous pair's epilogue must have read it
+        if (first && qi > 0 && !mbar_wait(o_free + 8 * w, (qi - 1) & 1, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
         for (int u = 0; u < BN / 16; ++u)
-          mma_ts(tmem + TM_O + 128 * w, tmem + TM_S + 128 * w + 64 * (u >> 2) + 8 * (u & 3), desc_mnmajor(tV + u * 2048, K_SLAB), IDESC_O, (it > 0 || u > 0));
+          mma_ts(tmem + TM_O + 128 * w, tmem + TM_S + 128 * w + 64 * (u >> 2) + 8 * (u & 3), desc_mnmajor(tV + u * 2048, K_SLAB), IDESC_O,
+                 (!first || u > 0));
         mma_commit(o_done + 8 * w);
       };
-      if (!mbar_wait(q_full, 0, &budget)) timed_out = true;
-      if (!mbar_wait(k_full, 0, &budget)) timed_out = true;
-      fence_after_sync();
-      issue_s(0, 0);
-      issue_s(1, 0);
-      mma_commit(k_free);
-      for (int it = 0; it < ntiles; ++it) {
-        const int s = it & 1;
-        const bool more = it + 1 < ntiles;
-        if (!mbar_wait(v_full + 8 * s, (it >> 1) & 1, &budget)) timed_out = true;
-        issue_pv(0, it);
-        if (more) {
-          if (!mbar_wait(k_full + 8 * (s ^ 1), ((it + 1) >> 1) & 1, &budget)) timed_out = true;
-          fence_after_sync();
-          issue_s(0, it + 1);
+      for (int i = 0; i < items; ++i) {
+        Item im;
+        if (!item_of(i, im)) break;
+        if (im.ntiles == 0) continue;
+        if (!mbar_wait(q_full, qi & 1, &budget)) timed_out = true;
+        if (!mbar_wait(k_full + 8 * (gt & 1), (gt >> 1) & 1, &budget)) timed_out = true;
+        fence_after_sync();
+        issue_s(0, gt);
+        issue_s(1, gt);
+        mma_commit(k_free + 8 * (gt & 1));
+        if (im.ntiles == 1) mma_commit(q_free);
+        for (int it = 0; it < im.ntiles; ++it) {
+          const int g = gt + it, s = g & 1;
+          const bool more = it + 1 < im.ntiles;
+          if (!mbar_wait(v_full + 8 * s, (g >> 1) & 1, &budget)) timed_out = true;
+          issue_pv(0, g, it == 0);
+          if (more) {
+            if (!mbar_wait(k_full + 8 * (s ^ 1), ((g + 1) >> 1) & 1, &budget)) timed_out = true;
+            fence_after_sync();
+            issue_s(0, g + 1);
+          }
+          issue_pv(1, g, it == 0);
+          mma_commit(v_free + 8 * s);
+          if (more) {
+            issue_s(1, g + 1);
+            mma_commit(k_free + 8 * (s ^ 1));
+            if (it + 2 == im.ntiles) mma_commit(q_free);   // the pair's last S products are issued: Q may be replaced
+          }
         }
-        issue_pv(1, it);
-        mma_commit(v_free + 8 * s);
-        if (more) {
-          issue_s(1, it + 1);
-          mma_commit(k_free + 8 * (s ^ 1));
-        }
+        gt += im.ntiles;
+        ++qi;
       }
     }
   } else {
     // ============================================ softmax: tile w = a / b, column half h; thread = query row
     const int w = warp >> 3, h = (warp >> 2) & 1, row = tid & 127;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 128 * w;
-    const int tok = w * TOK + row / G, g = row % G;
-    const bool row_ok = tok < ntok;
-    const int t_abs = tabs_min + tok;
-    const int64_t q_row = pc.q_start + t0 + tok;
-    // keys vis_lo..vis_hi (positions in the sequence's K/V rows) are visible to my row
-    int vis_lo = 0, vis_hi = -1;
-    if (row_ok) {
-      if (MODE == MODE_CMP) vis_hi = (t_abs - ks + 1 >= 0) ? (t_abs - ks + 1) / st : -1;
-      else { vis_hi = t_abs; vis_lo = t_abs - W; }
-      vis_hi = min(vis_hi, kv_hi - 1);
-    }
     const float c2 = p.sm_scale * 1.4426950408889634f;
-    float m_ref = -INFINITY, l_run = 0.f;   // l_run: my half of the columns only
-    float* xmax = sX + (w * 2) * 256;       // [2 buffers][2 halves][128 rows] of this tile
+    float* xmax = sX + (w * 3) * 256;       // [2 maximum buffers + 1 sum buffer][2 halves][128 rows] of this tile
     constexpr int HN = BN / 2;
+    for (int i = 0; i < items; ++i) {
+      Item im;
+      if (!item_of(i, im)) break;
+      const int tok = w * TOK + row / G, g_ = row % G;
+      const bool row_ok = tok < im.ntok;
+      const int t_abs = im.tabs_min + tok;
+      const int64_t q_row = pc.q_start + im.t0 + tok;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g_) * D + h * (D / 2);
+      if (im.ntiles == 0) {  // nothing visible for the whole pair: zeros
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0, 0, 0, 0);
+          if (p.lse && h == 0) p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_) * p.lse_stride_h] = 0.f;
+        }
+        continue;
+      }
+      // keys vis_lo..vis_hi (positions in the sequence's K/V rows) are visible to my row
+      int vis_lo = 0, vis_hi = -1;
+      if (row_ok) {
+        if (MODE == MODE_CMP) vis_hi = (t_abs - ks + 1 >= 0) ? (t_abs - ks + 1) / st : -1;
+        else { vis_hi = t_abs; vis_lo = t_abs - W; }
+        vis_hi = min(vis_hi, im.kv_hi - 1);
+      }
+      float m_ref = -INFINITY, l_run = 0.f;   // l_run: my half of the columns only
 
-    for (int it = 0; it < ntiles; ++it) {
-      const int kv0 = kv_lo + it * BN + h * HN;
-      const int lo = vis_lo - kv0, hi = vis_hi - kv0;   // visible columns of my half of this tile
-      const bool full = lo <= 0 && hi >= HN - 1;
-      if (!mbar_wait(s_full + 8 * w, it & 1, &budget)) timed_out = true;
-      fence_after_sync();
-      // ---- pass 1: row maximum over my 64 columns, then over both halves through shared memory
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+      for (int it = 0; it < im.ntiles; ++it) {
+        const int g = gt + it;
+        const int kv0 = im.kv_lo + it * BN + h * HN;
+        const int lo = vis_lo - kv0, hi = vis_hi - kv0;   // visible columns of my half of this tile
+        const bool full = lo <= 0 && hi >= HN - 1;
+        if (!mbar_wait(s_full + 8 * w, g & 1, &budget)) timed_out = true;
+        fence_after_sync();
+        // ---- pass 1: row maximum over my 64 columns, then over both halves through shared memory
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
 #pragma unroll
-      for (int c = 0; c < HN / 32; ++c) {
-        uint32_t sv[32];
-        tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
-        wait_ld();
-        if (full) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i >= lo && c * 32 + i <= hi) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-        }
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      float* xb = xmax + (it & 1) * 256;   // this buffer was last read two tiles ago, before the previous tile's barrier
-      xb[h * 128 + row] = mx;
-      named_barrier(1 + w, 256);
-      mx = fmaxf(mx, xb[(h ^ 1) * 128 + row]) * c2;
-      // ---- reference maximum: raise it only when the row maximum ran away by more than 2^8
-      float alpha = 1.f;
-      bool need = false;
-      if (m_ref == -INFINITY) {
-        m_ref = mx;  // nothing accumulated yet for this row (its O row is still exactly zero or unwritten)
-      } else if (mx > m_ref + 8.f) {
-        alpha = fast_exp2(m_ref - mx);
-        m_ref = mx;
-        need = true;
-      }
-      const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      // ---- pass 2: P = exp2(S c - m) -> bf16, written over the first 32 of MY 64 S columns (already consumed)
-      float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < HN / 32; ++c) {
-        uint32_t sv[32], pk[16];
-        tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
-        wait_ld();
-        if (full) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)), e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu));
-            rs0 += e0;
-            rs1 += e1;
-            pk[i >> 1] = pack_bf16(e0, e1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int col = c * 32 + i;
-            const float e0 = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i]), c2, nmu)) : 0.f;
-            const float e1 = (col + 1 >= lo && col + 1 <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), c2, nmu)) : 0.f;
-            rs0 += e0;
-            rs1 += e1;
-            pk[i >> 1] = pack_bf16(e0, e1);
-          }
-        }
-        tmem_st16(lane_base + TM_S + h * HN + c * 16, pk);
-      }
-      l_run = l_run * alpha + (rs0 + rs1);
-      if (it > 0 && __any_sync(0xffffffffu, need)) {  // rescale my half of my O row (warp-uniform branch, per-lane
-#pragma unroll                                        // factor); the previous P.V of this tile retired before this S
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t o[32];
-          tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, o);
+        for (int c = 0; c < HN / 32; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
           wait_ld();
+          if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(lane_base + TM_O + h * (D / 2) + c * 32, o);
+            for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (c * 32 + e >= lo && c * 32 + e <= hi) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+          }
         }
-      }
-      wait_st();
-      fence_before_sync();
-      mbar_arrive(p_ready + 8 * w);
-    }
-    // the row's l: both halves
-    float* xl = xmax + (ntiles & 1) * 256;
-    xl[h * 128 + row] = l_run;
-    named_barrier(1 + w, 256);
-    l_run += xl[(h ^ 1) * 128 + row];
-    if (!mbar_wait(o_done + 8 * w, (ntiles - 1) & 1, &budget)) timed_out = true;
-    fence_after_sync();
-
-    // ---- epilogue: my half of my row of O
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)(kh * G + g) * D + h * (D / 2);
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float* xb = xmax + (g & 1) * 256;   // this buffer was last read two tiles ago, before the previous tile's barrier
+        xb[h * 128 + row] = mx;
+        named_barrier(1 + w, 256);
+        mx = fmaxf(mx, xb[(h ^ 1) * 128 + row]) * c2;
+        // ---- reference maximum: raise it only when the row maximum ran away by more than 2^8
+        float alpha = 1.f;
+        bool need = false;
+        if (m_ref == -INFINITY) {
+          m_ref = mx;  // nothing accumulated yet for this row (its O row is still exactly zero or unwritten)
+        } else if (mx > m_ref + 8.f) {
+          alpha = fast_exp2(m_ref - mx);
+          m_ref = mx;
+          need = true;
+        }
+        const float nmu = (m_ref == -INFINITY) ? 0.f : -m_ref;
+        // ---- pass 2: P = exp2(S c - m) -> bf16, written over the first 32 of MY 64 S columns (already consumed)
+        float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-    for (int c = 0; c < D / 64; ++c) {
-      uint32_t o[32];
-      tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, o);
+        for (int c = 0; c < HN / 32; ++c) {
+          uint32_t sv[32], pk[16];
+          tmem_ld32(lane_base + TM_S + h * HN + c * 32, sv);
+          wait_ld();
+          if (full) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float e0 = fast_exp2(fmaf(__uint_as_float(sv[e]), c2, nmu)), e1 = fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, nmu));
+              rs0 += e0;
+              rs1 += e1;
+              pk[e >> 1] = pack_bf16(e0, e1);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const int col = c * 32 + e;
+              const float e0 = (col >= lo && col <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[e]), c2, nmu)) : 0.f;
+              const float e1 = (col + 1 >= lo && col + 1 <= hi) ? fast_exp2(fmaf(__uint_as_float(sv[e + 1]), c2, nmu)) : 0.f;
+              rs0 += e0;
+              rs1 += e1;
+              pk[e >> 1] = pack_bf16(e0, e1);
+            }
+          }
+          tmem_st16(lane_base + TM_S + h * HN + c * 16, pk);
+        }
+        l_run = l_run * alpha + (rs0 + rs1);
+        if (it > 0 && __any_sync(0xffffffffu, need)) {  // rescale my half of my O row (warp-uniform branch, per-lane
+#pragma unroll                                          // factor); the previous P.V of this tile retired before this S
+          for (int c = 0; c < D / 64; ++c) {
+            uint32_t o[32];
+            tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, o);
+            wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(lane_base + TM_O + h * (D / 2) + c * 32, o);
+          }
+        }
+        wait_st();
+        fence_before_sync();
+        mbar_arrive(p_ready + 8 * w);
+      }
+      // the row's l: both halves (a buffer of its own: the maximum buffers belong to the tiles around this point)
+      float* xl = xmax + 2 * 256;
+      xl[h * 128 + row] = l_run;
+      named_barrier(1 + w, 256);
+      l_run += xl[(h ^ 1) * 128 + row];
+      if (!mbar_wait(o_done + 8 * w, (gt + im.ntiles - 1) & 1, &budget)) timed_out = true;
+      fence_after_sync();
+      // ---- epilogue: my half of my row of O
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint32_t o[D / 2];
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t t32[32];
+        tmem_ld32(lane_base + TM_O + h * (D / 2) + c * 32, t32);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = t32[e];
+      }
       wait_ld();
+      fence_before_sync();
+      mbar_arrive(o_free + 8 * w);   // O_w (and the sum buffer) may be overwritten by the next pair
       if (row_ok) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q8 = 0; q8 < D / 16; ++q8) {
           uint4 x;
-          x.x = pack_bf16(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
-          x.y = pack_bf16(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
-          x.z = pack_bf16(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
-          x.w = pack_bf16(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = x;
+          x.x = pack_bf16(__uint_as_float(o[q8 * 8 + 0]) * inv, __uint_as_float(o[q8 * 8 + 1]) * inv);
+          x.y = pack_bf16(__uint_as_float(o[q8 * 8 + 2]) * inv, __uint_as_float(o[q8 * 8 + 3]) * inv);
+          x.z = pack_bf16(__uint_as_float(o[q8 * 8 + 4]) * inv, __uint_as_float(o[q8 * 8 + 5]) * inv);
+          x.w = pack_bf16(__uint_as_float(o[q8 * 8 + 6]) * inv, __uint_as_float(o[q8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + q8 * 8) = x;
         }
+        if (p.lse && h == 0)
+          p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_) * p.lse_stride_h] = l_run > 0.f ? m_ref + log2f(l_run) : 0.f;
       }
+      gt += im.ntiles;
+      ++qi;
     }
-    if (row_ok && p.lse && h == 0)
-      p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g) * p.lse_stride_h] = l_run > 0.f ? m_ref + log2f(l_run) : 0.f;
   }
   if (timed_out && p.status) atomicOr(p.status, 1);
   fence_before_sync();
@@ -329,14 +369,19 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name) 
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable", name);
     return NSA_ERR_CUDA;
   }
-  const size_t smem = (size_t)6 * 128 * D * 2 + 256 + 4 * 256 * 4;
+  const size_t smem = (size_t)6 * 128 * D * 2 + 256 + 6 * 256 * 4;
   cudaError_t e = cudaFuncSetAttribute(dense_fwd128_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
-  dim3 grid((p->meta.max_piece_len + 2 * TOK - 1) / (2 * TOK), p->meta.n_pieces, p->KH);
-  dense_fwd128_tc_kernel<D, MODE><<<grid, 576, smem, st>>>(*p, tmq, tmk, tmv);
+  // consecutive query-tile pairs per CTA (up to 8): the CTA's set-up, and the epilogue of one pair under the loads of the
+  // next, are shared; fewer when the launch would not fill the GPU a few times over
+  const int n_pairs = (p->meta.max_piece_len + 2 * TOK - 1) / (2 * TOK);
+  const int64_t total = (int64_t)n_pairs * p->meta.n_pieces * p->KH;
+  const int items = (int)std::max<int64_t>(1, std::min<int64_t>(8, total / (148 * 4)));
+  dim3 grid((n_pairs + items - 1) / items, p->meta.n_pieces, p->KH);
+  dense_fwd128_tc_kernel<D, MODE><<<grid, 576, smem, st>>>(*p, items, tmq, tmk, tmv);
   return check_launch(name);
 }
 
