@@ -132,20 +132,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     }
     __syncwarp();
     if (lane == 0 && nxt >= 0) fetch<D>(wp.bufK, wp.barK, &tmk, kh, pc.x_bos + nxt * BS);  // K buffer is free again
-    if (cur == nk) {
+    if (cur == nk) {   // the token's own block: keys after it do not take part
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int key = key0 + nt * 8 + 2 * c_;
         const bool v0 = key <= t_abs, v1 = key + 1 <= t_abs;
-        s[nt][0] = v0 ? s[nt][0] * c2 : -INFINITY;
-        s[nt][1] = v1 ? s[nt][1] * c2 : -INFINITY;
-        s[nt][2] = v0 ? s[nt][2] * c2 : -INFINITY;
-        s[nt][3] = v1 ? s[nt][3] * c2 : -INFINITY;
-      }
-    } else {
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] *= c2; s[nt][1] *= c2; s[nt][2] *= c2; s[nt][3] *= c2;
+        s[nt][0] = v0 ? s[nt][0] : -INFINITY;
+        s[nt][1] = v1 ? s[nt][1] : -INFINITY;
+        s[nt][2] = v0 ? s[nt][2] : -INFINITY;
+        s[nt][3] = v1 ? s[nt][3] : -INFINITY;
       }
     }
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
@@ -154,28 +149,33 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
       mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
       mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
     }
-    mx_lo = warp_max4(mx_lo);
-    mx_hi = warp_max4(mx_hi);
-    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-    const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
-    const float al_lo = fast_exp2(m_lo - mu_lo), al_hi = fast_exp2(m_hi - mu_hi);
+    mx_lo = warp_max4(mx_lo) * c2;   // c2 > 0: the maximum of the scaled scores
+    mx_hi = warp_max4(mx_hi) * c2;
+    // Reference maximum: raised only when the block maximum exceeds it by more than 2^8 (then o and l are rescaled); l and
+    // the final normalisation use the same reference, so the result is exact, and most blocks skip the rescale.
+    float al_lo = 1.f, al_hi = 1.f;
+    if (m_lo == -INFINITY) m_lo = mx_lo;
+    else if (mx_lo > m_lo + 8.f) { al_lo = fast_exp2(m_lo - mx_lo); m_lo = mx_lo; }
+    if (m_hi == -INFINITY) m_hi = mx_hi;
+    else if (mx_hi > m_hi + 8.f) { al_hi = fast_exp2(m_hi - mx_hi); m_hi = mx_hi; }
+    const float nmu_lo = (m_lo == -INFINITY) ? 0.f : -m_lo, nmu_hi = (m_hi == -INFINITY) ? 0.f : -m_hi;
     float rs_lo = 0.f, rs_hi = 0.f;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      s[nt][0] = fast_exp2(s[nt][0] - mu_lo);
-      s[nt][1] = fast_exp2(s[nt][1] - mu_lo);
-      s[nt][2] = fast_exp2(s[nt][2] - mu_hi);
-      s[nt][3] = fast_exp2(s[nt][3] - mu_hi);
+      s[nt][0] = fast_exp2(fmaf(s[nt][0], c2, nmu_lo));
+      s[nt][1] = fast_exp2(fmaf(s[nt][1], c2, nmu_lo));
+      s[nt][2] = fast_exp2(fmaf(s[nt][2], c2, nmu_hi));
+      s[nt][3] = fast_exp2(fmaf(s[nt][3], c2, nmu_hi));
       rs_lo += s[nt][0] + s[nt][1];
       rs_hi += s[nt][2] + s[nt][3];
     }
     l_lo = l_lo * al_lo + rs_lo;
     l_hi = l_hi * al_hi + rs_hi;
-    m_lo = mn_lo;
-    m_hi = mn_hi;
+    if (__any_sync(0xffffffffu, al_lo != 1.f || al_hi != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < NT; ++i) {
-      o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi;
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi;
+      }
     }
     if (!tc::mbar_wait(wp.barV, wp.nV & 1, &budget)) timed_out = true;
     ++wp.nV;
