@@ -28,8 +28,11 @@ __global__ void __launch_bounds__(128, 2) slc_dq_kernel(NsaAttnParams p) {
   constexpr int SS = D / 32, HH = D / 64, BS = 64;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g_ = lane >> 2, c_ = lane & 3;
-  const int G = p.QH / p.KH;
-  const int kh = blockIdx.z;
+  // blockIdx.z = (kv head, group of 16 of its query heads): more than 16 query heads per kv head run as several groups
+  const int Gall = p.QH / p.KH, HG = (Gall + 15) / 16;
+  const int kh = blockIdx.z / HG, hg = blockIdx.z % HG;
+  const int G = min(16, Gall - 16 * hg);
+  const int64_t hbase = (int64_t)kh * Gall + 16 * hg;   // first query head of my group
   const Piece pc = load_piece(p.meta, blockIdx.y);
   const int tl = (gridDim.x - 1 - blockIdx.x) * 4 + warp;
   if (tl >= pc.len) return;
@@ -40,8 +43,8 @@ __global__ void __launch_bounds__(128, 2) slc_dq_kernel(NsaAttnParams p) {
   const float c2 = p.sm_scale * 1.4426950408889634f;
 
   const int h_lo = min(g_, G - 1), h_hi = min(g_ + 8, G - 1);
-  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + (int64_t)kh * G * D + c_ * 8;
-  const __nv_bfloat16* dop = reinterpret_cast<const __nv_bfloat16*>(p.dout) + q_row * p.do_stride_t + (int64_t)kh * G * D + c_ * 8;
+  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + hbase * D + c_ * 8;
+  const __nv_bfloat16* dop = reinterpret_cast<const __nv_bfloat16*>(p.dout) + q_row * p.do_stride_t + hbase * D + c_ * 8;
   uint4 qa[SS], qb[SS], oa[SS], ob[SS];
 #pragma unroll
   for (int s = 0; s < SS; ++s) {
@@ -50,8 +53,8 @@ __global__ void __launch_bounds__(128, 2) slc_dq_kernel(NsaAttnParams p) {
     oa[s] = ldg_nc16b(dop + h_lo * D + 32 * s);
     ob[s] = ldg_nc16b(dop + h_hi * D + 32 * s);
   }
-  const int64_t la = q_row * p.lse_stride_t + (int64_t)(kh * G + h_lo) * p.lse_stride_h;
-  const int64_t lb = q_row * p.lse_stride_t + (int64_t)(kh * G + h_hi) * p.lse_stride_h;
+  const int64_t la = q_row * p.lse_stride_t + (hbase + h_lo) * p.lse_stride_h;
+  const int64_t lb = q_row * p.lse_stride_t + (hbase + h_hi) * p.lse_stride_h;
   const float lse_lo = p.lse[la], lse_hi = p.lse[lb], dl_lo = p.delta[la], dl_hi = p.delta[lb];
 
   const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(p.k) + (int64_t)pc.x_bos * p.k_stride_t + kh * D;
@@ -130,7 +133,7 @@ __global__ void __launch_bounds__(128, 2) slc_dq_kernel(NsaAttnParams p) {
     }
   }
 
-  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)kh * G * D + 16 * c_;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + hbase * D + 16 * c_;
   const float sc = p.sm_scale;
 #pragma unroll
   for (int h = 0; h < HH; ++h) {
@@ -173,7 +176,6 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   NSA_REQUIRE(p->topk && p->lse && p->dout && p->delta && p->dq && p->dk && p->dv, NSA_ERR_BAD_ARG,
               "slc_attn_bwd: topk, lse, dout, delta, dq, dk, dv are required");
   NSA_REQUIRE(p->k2q_offsets && p->k2q_tokens && p->k2q_blk_cu, NSA_ERR_BAD_ARG, "slc_attn_bwd: the k2q index is required");
-  NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_bwd: at most 16 query heads per kv head (got %d)", p->QH / p->KH);
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_bwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   NSA_REQUIRE(p->dk_stride_t % 2 == 0 && p->dv_stride_t % 2 == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: dk/dv row strides must be even");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;
@@ -191,7 +193,7 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   if (!(ph & 4)) return check_launch("slc_attn_bwd");
   rc = launch_slc_tma(p, st, true);
   if (rc != 1) return rc;
-  dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
+  dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH * ((p->QH / p->KH + 15) / 16));
   if (p->D == 128) slc_dq_kernel<128><<<grid, 128, 0, st>>>(*p);
   else slc_dq_kernel<64><<<grid, 128, 0, st>>>(*p);
   return check_launch("slc_attn_bwd(dq)");

@@ -24,8 +24,11 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   constexpr int SS = D / 32, HH = D / 64, BS = 64;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g_ = lane >> 2, c_ = lane & 3;
-  const int G = p.QH / p.KH;
-  const int kh = blockIdx.z;
+  // blockIdx.z = (kv head, group of 16 of its query heads): more than 16 query heads per kv head run as several groups
+  const int Gall = p.QH / p.KH, HG = (Gall + 15) / 16;
+  const int kh = blockIdx.z / HG, hg = blockIdx.z % HG;
+  const int G = min(16, Gall - 16 * hg);
+  const int64_t hbase = (int64_t)kh * Gall + 16 * hg;   // first query head of my group
   const Piece pc = load_piece(p.meta, blockIdx.y);
   const int tl = (gridDim.x - 1 - blockIdx.x) * 4 + warp;  // local row inside the piece
   if (tl >= pc.len) return;
@@ -36,7 +39,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   const float c2 = p.sm_scale * 1.4426950408889634f;
 
   const int h_lo = min(g_, G - 1), h_hi = min(g_ + 8, G - 1);
-  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + (int64_t)kh * G * D + c_ * 8;
+  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + hbase * D + c_ * 8;
   uint4 qa[SS], qb[SS];
 #pragma unroll
   for (int s = 0; s < SS; ++s) {
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   l_lo = warp_sum4(l_lo);
   l_hi = warp_sum4(l_hi);
   float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
-  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)kh * G * D + 16 * c_;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + hbase * D + 16 * c_;
 #pragma unroll
   for (int h = 0; h < HH; ++h) {
     if (g_ < G) {
@@ -173,9 +176,9 @@ __global__ void __launch_bounds__(128, 2) slc_fwd_kernel(NsaAttnParams p) {
   }
   if (c_ == 0 && p.lse) {
     if (g_ < G)
-      p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_) * p.lse_stride_h] = l_lo > 0.f ? m_lo + log2f(l_lo) : 0.f;
+      p.lse[q_row * p.lse_stride_t + (hbase + g_) * p.lse_stride_h] = l_lo > 0.f ? m_lo + log2f(l_lo) : 0.f;
     if (g_ + 8 < G)
-      p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_ + 8) * p.lse_stride_h] = l_hi > 0.f ? m_hi + log2f(l_hi) : 0.f;
+      p.lse[q_row * p.lse_stride_t + (hbase + g_ + 8) * p.lse_stride_h] = l_hi > 0.f ? m_hi + log2f(l_hi) : 0.f;
   }
 }
 
@@ -190,12 +193,11 @@ extern "C" int nsa_slc_attn_fwd(const NsaAttnParams* p, void* stream) {
   int rc = check_attn_common(p, "slc_attn_fwd", false);
   if (rc) return rc;
   NSA_REQUIRE(p->topk, NSA_ERR_BAD_ARG, "slc_attn_fwd: topk is required");
-  NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_fwd: at most 16 query heads per kv head (got %d)", p->QH / p->KH);
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_fwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
   rc = launch_slc_tma(p, (cudaStream_t)stream, false);   // contiguous K/V: TMA-staged tiles
   if (rc != 1) return rc;
-  dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH);
+  dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH * ((p->QH / p->KH + 15) / 16));
   const bool paged = p->meta.kv_table != nullptr;
   if (p->D == 128) {
     if (paged) slc_fwd_kernel<128, true><<<grid, 128, 0, (cudaStream_t)stream>>>(*p);

@@ -1,7 +1,7 @@
 // Selected-block attention over CONTIGUOUS (non-paged) K/V with TMA-staged tiles: forward and dQ.
 //
 // Every token has its own list of 64-key blocks, so the unit of work is still one warp per (token, kv head) with the
-// (<= 16) query heads as the 16 rows of the warp-level MMA.  What changes against slc_fwd.cu / slc_bwd.cu is how the
+// query heads (in groups of up to 16) as the 16 rows of the warp-level MMA.  What changes against slc_fwd.cu / slc_bwd.cu is how the
 // K/V rows reach the MMA: each warp owns a private 64-row K buffer and V buffer in shared memory, its lane 0 fetches a
 // selected block with one TMA box per 64-wide slab (128-byte swizzle), and fragments come from ldmatrix.  Fragment-
 // direct global loads deliver 64 bytes per L1 wavefront (4 lanes per key row) and saturate the L1 load pipe; the TMA
@@ -68,8 +68,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   WarpPipe wp{base + warp * 2 * TILE, base + warp * 2 * TILE + TILE, base + kWarps * 2 * TILE + warp * 16,
               base + kWarps * 2 * TILE + warp * 16 + 8, 0, 0};
   const int g_ = lane >> 2, c_ = lane & 3;
-  const int G = p.QH / p.KH;
-  const int kh = blockIdx.z;
+  // blockIdx.z = (kv head, group of 16 of its query heads): more than 16 query heads per kv head run as several groups
+  const int Gall = p.QH / p.KH, HG = (Gall + 15) / 16;
+  const int kh = blockIdx.z / HG, hg = blockIdx.z % HG;
+  const int G = min(16, Gall - 16 * hg);
+  const int64_t hbase = (int64_t)kh * Gall + 16 * hg;   // first query head of my group
   const Piece pc = load_piece(p.meta, blockIdx.y);
   const int tl = (gridDim.x - 1 - blockIdx.x) * kWarps + warp;
   if (tl >= pc.len) return;
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   bool timed_out = false;
 
   uint32_t qf[KS][4];
-  load_a_global<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + (int64_t)kh * G * D, G, lane);
+  load_a_global<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + hbase * D, G, lane);
   float o[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -199,16 +202,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   l_lo = warp_sum4(l_lo);
   l_hi = warp_sum4(l_hi);
   const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
-  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + (int64_t)kh * G * D + 2 * c_;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + q_row * p.o_stride_t + hbase * D + 2 * c_;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     if (g_ < G) *reinterpret_cast<uint32_t*>(op + g_ * D + nt * 8) = pack_bf16(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
     if (g_ + 8 < G) *reinterpret_cast<uint32_t*>(op + (g_ + 8) * D + nt * 8) = pack_bf16(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
   }
   if (c_ == 0 && p.lse) {
-    if (g_ < G) p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_) * p.lse_stride_h] = l_lo > 0.f ? m_lo + log2f(l_lo) : 0.f;
+    if (g_ < G) p.lse[q_row * p.lse_stride_t + (hbase + g_) * p.lse_stride_h] = l_lo > 0.f ? m_lo + log2f(l_lo) : 0.f;
     if (g_ + 8 < G)
-      p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_ + 8) * p.lse_stride_h] = l_hi > 0.f ? m_hi + log2f(l_hi) : 0.f;
+      p.lse[q_row * p.lse_stride_t + (hbase + g_ + 8) * p.lse_stride_h] = l_hi > 0.f ? m_hi + log2f(l_hi) : 0.f;
   }
   if (timed_out && lane == 0 && p.status) atomicOr(p.status, 128);
 }
@@ -225,8 +228,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   WarpPipe wp{base + warp * 2 * TILE, base + warp * 2 * TILE + TILE, base + kWarps * 2 * TILE + warp * 16,
               base + kWarps * 2 * TILE + warp * 16 + 8, 0, 0};
   const int g_ = lane >> 2, c_ = lane & 3;
-  const int G = p.QH / p.KH;
-  const int kh = blockIdx.z;
+  // blockIdx.z = (kv head, group of 16 of its query heads): more than 16 query heads per kv head run as several groups
+  const int Gall = p.QH / p.KH, HG = (Gall + 15) / 16;
+  const int kh = blockIdx.z / HG, hg = blockIdx.z % HG;
+  const int G = min(16, Gall - 16 * hg);
+  const int64_t hbase = (int64_t)kh * Gall + 16 * hg;   // first query head of my group
   const Piece pc = load_piece(p.meta, blockIdx.y);
   const int tl = (gridDim.x - 1 - blockIdx.x) * kWarps + warp;
   if (tl >= pc.len) return;
@@ -252,11 +258,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   bool timed_out = false;
 
   uint32_t qf[KS][4], of[KS][4];
-  load_a_global<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + (int64_t)kh * G * D, G, lane);
-  load_a_global<D>(of, reinterpret_cast<const __nv_bfloat16*>(p.dout) + q_row * p.do_stride_t + (int64_t)kh * G * D, G, lane);
+  load_a_global<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + q_row * p.q_stride_t + hbase * D, G, lane);
+  load_a_global<D>(of, reinterpret_cast<const __nv_bfloat16*>(p.dout) + q_row * p.do_stride_t + hbase * D, G, lane);
   const int h_lo = min(g_, G - 1), h_hi = min(g_ + 8, G - 1);
-  const int64_t la = q_row * p.lse_stride_t + (int64_t)(kh * G + h_lo) * p.lse_stride_h;
-  const int64_t lb = q_row * p.lse_stride_t + (int64_t)(kh * G + h_hi) * p.lse_stride_h;
+  const int64_t la = q_row * p.lse_stride_t + (hbase + h_lo) * p.lse_stride_h;
+  const int64_t lb = q_row * p.lse_stride_t + (hbase + h_hi) * p.lse_stride_h;
   const float lse_lo = p.lse[la], lse_hi = p.lse[lb], dl_lo = p.delta[la], dl_hi = p.delta[lb];
   float dq[NT][4];
 #pragma unroll
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     cur = nxt;
   }
 
-  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)kh * G * D + 2 * c_;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + hbase * D + 2 * c_;
   const float sc = p.sm_scale;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
@@ -374,7 +380,7 @@ int launch_slc_tma(const NsaAttnParams* p, cudaStream_t st, bool backward) {
     return NSA_ERR_CUDA;
   }
   const size_t smem = (size_t)kWarps * 2 * 64 * D * 2 + kWarps * 16;
-  dim3 grid((p->meta.max_piece_len + kWarps - 1) / kWarps, p->meta.n_pieces, p->KH);
+  dim3 grid((p->meta.max_piece_len + kWarps - 1) / kWarps, p->meta.n_pieces, p->KH * ((p->QH / p->KH + 15) / 16));
   cudaError_t e;
 #define NSA_LAUNCH(KERNEL)                                                                              \
   e = cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \

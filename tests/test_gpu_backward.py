@@ -56,6 +56,7 @@ CASES = [
     ([200, 333], 16, 1, 128),
     ([1100], 8, 2, 64),
     ([96, 130], 6, 2, 64),
+    ([300, 150], 32, 1, 64),   # G = 32: two groups of 16 query heads per kv head in the selected branch
 ]
 
 

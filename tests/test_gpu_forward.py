@@ -50,6 +50,8 @@ CASES = [
     ([1100], 8, 2, 64),
     ([64, 128, 65], 32, 2, 128),
     ([96], 6, 2, 64),          # G = 3: rows of a tile do not divide evenly
+    ([300, 150], 32, 1, 64),   # G = 32: two groups of 16 query heads per kv head in the selected branch
+    ([260], 40, 2, 128),       # G = 20: a full group and a group of 4
 ]
 
 
