@@ -11,7 +11,7 @@
 // N = 128 halves the shared-memory reads per query row of the two score products (the A tile is re-read by every MMA).
 // Tensor memory holds S^T, dP^T, dV, dK (4 x 128 columns), so the products of one tile are ordered
 //     S^T(i) | dK(i-1) | dP^T(i) | dV(i)     with exp2 of tile i running under dK(i-1) and dP^T(i), and dS^T under dV(i).
-// Warp 8 (one lane) issues all TMA loads and MMAs; warps 0-3 and 4-7 are two compute groups that take the query columns
+// Warp 8 (one lane) issues the MMAs, warp 9 (one lane) the TMA loads; warps 0-3 and 4-7 are two compute groups that take the query columns
 // 0-63 and 64-127 of every tile.  Q/dO tiles go through a 2-stage shared-memory ring.
 #include "tma.cuh"
 
@@ -21,7 +21,7 @@ constexpr int MODE_CMP = 0;
 constexpr int MODE_SWA = 1;
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(288, 1)
+__global__ void __launch_bounds__(320, 1)
     dkdv128_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
                       const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
@@ -101,17 +101,19 @@ __global__ void __launch_bounds__(288, 1)
   int budget = kWaitBudget;
   bool timed_out = false;
 
-  if (warp == 8) {
+  if (warp == 9) {
     if ((tid & 31) == 0) {
-      // ============================================ producer: TMA loads + MMA issue
+      // ============================================ TMA producer: K/V once, then the Q/dO tiles through the 2-stage ring
       tma::expect_tx(kv_full, 2 * KV_BYTES);
 #pragma unroll
       for (int sl = 0; sl < SLABS; ++sl) {
         tma::load_3d(sK + sl * K_SLAB, &tmk, sl * 64, kh, (int)(kv_bos + k0), kv_full);
         tma::load_3d(sV + sl * K_SLAB, &tmv, sl * 64, kh, (int)(kv_bos + k0), kv_full);
       }
-      auto load_q = [&](int i) {  // tile i into stage i % NS (the caller has made sure the stage is free)
+      for (int i = 0; i < n_it; ++i) {
         const int s = i % NS;
+        // the stage of tile i-2 is free once its dK product is done
+        if (i >= NS && !mbar_wait(kv_done, (i - NS) & 1, &budget)) timed_out = true;
         tma::expect_tx(q_full + 8 * s, 2 * Q_BYTES);
         const int row = pc.q_start + r_lo + tile_of(i) * TOKQ;
 #pragma unroll
@@ -119,9 +121,11 @@ __global__ void __launch_bounds__(288, 1)
           tma::load_3d(sQ + s * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, row, q_full + 8 * s);
           tma::load_3d(sO + s * Q_BYTES + sl * Q_SLAB, &tmo, sl * 64, kh * G, row, q_full + 8 * s);
         }
-      };
-      load_q(0);
-      if (n_it > 1) load_q(1);
+      }
+    }
+  } else if (warp == 8) {
+    if ((tid & 31) == 0) {
+      // ============================================ MMA issue
       if (!mbar_wait(kv_full, 0, &budget)) timed_out = true;
       auto issue_dk = [&](int i) {  // dK += dS^T Q of tile i; k-step u covers query rows 16u..16u+15, which group
         const int s = i % NS;       // w = u / 4 wrote at columns 64w + 32h + 8e of the dP^T region
@@ -152,10 +156,6 @@ __global__ void __launch_bounds__(288, 1)
           mma_ss(tmem + TM_DP, desc_kmajor(sV + ao), desc_kmajor(sO + s * Q_BYTES + bo), IDESC_SD, k > 0);
         }
         mma_commit(dp_full);
-        if (i > 0 && i + 1 < n_it) {  // the stage of tile i-1 is free once its dK is done
-          if (!mbar_wait(kv_done, (i - 1) & 1, &budget)) timed_out = true;
-          load_q(i + 1);
-        }
         if (!mbar_wait(p_ready, ph, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
@@ -327,7 +327,7 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, 
   dim3 grid;
   if (MODE == MODE_CMP) grid = dim3((p->meta.y_maxlen + 127) / 128, (p->meta.max_piece_len + q_chunk - 1) / q_chunk, p->meta.n_pieces * p->KH);
   else grid = dim3((p->meta.max_piece_len + p->hp.window + 127) / 128 + 1, 1, p->meta.n_pieces * p->KH);
-  dkdv128_tc_kernel<D, MODE><<<grid, 288, smem, st>>>(*p, L, tmq, tmo, tmk, tmv);
+  dkdv128_tc_kernel<D, MODE><<<grid, 320, smem, st>>>(*p, L, tmq, tmo, tmk, tmv);
   return check_launch(name);
 }
 
