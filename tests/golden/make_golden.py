@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the reference's own torch code.
 
-Run once, in a container that has the reference checkout (default /root/reference):
+Run once, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It loads flash_nsa/ops/torch_ref.py BY FILE PATH (the package itself needs a GPU to import),
 feeds it seeded inputs whose values are exactly representable in bfloat16, and stores inputs
@@ -96,7 +96,9 @@ def make_misc(ref):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    root = sys.argv[1]
     ref = load_ref(root)
     torch.set_num_threads(8)
     make_case(ref, "seq320_g4_d64", T=320, QH=4, KH=1, D=64, seed=11)
