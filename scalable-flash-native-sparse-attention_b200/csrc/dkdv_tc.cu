@@ -73,9 +73,9 @@ __global__ void __launch_bounds__(480, 1)
     kv_rows = min(BK, pc.x_len - k0);
     const int32_t* offs = p.k2q_offsets + (int64_t)kh * (p.n_blocks_total + 1);
     const int lo = offs[row], hi = offs[row + 1];
-    // at least 32 query tiles per CTA: short lists use fewer of the `splits` CTAs (the others leave at once), which
+    // at least 64 query tiles per CTA: short lists use fewer of the `splits` CTAs (the others leave at once), which
     // keeps the K/V load and the atomic write-back of a CTA small against its tile work
-    const int per = max((((hi - lo + L.splits - 1) / L.splits + TOKQ - 1) / TOKQ) * TOKQ, 32 * TOKQ);
+    const int per = max((((hi - lo + L.splits - 1) / L.splits + TOKQ - 1) / TOKQ) * TOKQ, 64 * TOKQ);
     r_lo = lo + blockIdx.y * per;
     r_hi = min(hi, r_lo + per);
     list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
