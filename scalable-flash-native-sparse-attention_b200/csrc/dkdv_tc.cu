@@ -33,7 +33,8 @@ __device__ __forceinline__ int find_le_tc(const int32_t* cu, int n, int x) {
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(480, 1)
-    dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo) {
+    dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
+                   const __grid_constant__ CUtensorMap tmdq) {
   using namespace tc;
   constexpr int BK = 64, BQ = 128;
   constexpr uint32_t KV_BYTES = BK * D * 2, Q_BYTES = BQ * D * 2, P_BYTES = BQ * BK * 2;
@@ -220,37 +221,51 @@ __global__ void __launch_bounds__(480, 1)
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = p.sm_scale * 1.4426950408889634f;
     const int my_n = t / G, my_g = t - my_n * G;
-    __nv_bfloat16* dq_prev = nullptr;   // dq row of my row in the previous tile (fused dQ)
-    // add my row of dS K (the tile's S / dP columns, complete once kv_done has fired) into dq
-    auto add_dq = [&](__nv_bfloat16* dst) {
+    // fused dQ: my row of dS K (the tile's S / dP columns, complete once kv_done has fired) goes, as bf16, into my P and dS
+    // buffers (free by then) in the layout of a q tile; one bulk tensor reduction per (token, 64-column slab) then adds
+    // the token's [G heads x 64] box into dq.  red_row = tensor row of token t % TOKQ of the tile (threads that own a box).
+    constexpr int SLABS = D / 64;
+    const int n_box = TOKQ * SLABS;
+    int red_row = -1;
+    auto add_dq = [&](int row) {
       fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(lane_base + 128 * wg + c * 32, v);
         wait_ld();
-        if (dst) {
+        const uint32_t sb = ((c >> 1) ? tS : tP) + t * 128;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
+        for (int i = 0; i < 4; ++i) {
+          uint32_t w[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              w[u] = pack_bf16(__uint_as_float(v[i + 2 * u]) * p.sm_scale, __uint_as_float(v[i + 2 * u + 1]) * p.sm_scale);
-            asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4};\n" ::"l"(dst + c * 32 + i), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                         "r"(w[3])
-                         : "memory");
-          }
+          for (int u = 0; u < 4; ++u)
+            w[u] = pack_bf16(__uint_as_float(v[8 * i + 2 * u]) * p.sm_scale, __uint_as_float(v[8 * i + 2 * u + 1]) * p.sm_scale);
+          const uint32_t ch = (c & 1) * 4 + i;
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(sb + ((ch ^ (t & 7)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
         }
       }
       fence_before_sync();
-      mbar_arrive(bar(4, wg));
+      mbar_arrive(bar(4, wg));            // the S / dP columns may take the next tile
+      fence_proxy_async();
+      named_barrier(2 + wg, 128);
+      if (t < n_box) {
+        if (row >= 0) {
+          for (int b = t; b < n_box; b += 128) {
+            const int n = b % TOKQ, sl = b / TOKQ;
+            tma::reduce_add_3d(&tmdq, sl * 64, kh * G, row, (sl ? tS : tP) + n * G * 128);
+          }
+        }
+        tma::bulk_commit();
+      }
     };
 
     for (int j = 0; j < n_round; ++j) {
       const int it = 2 * j + wg;
       const int tok0 = r_lo + it * TOKQ;  // first token (range position / list position) of my tile
       if (j > 0 && !mbar_wait(bar(3, wg), (j - 1) & 1, &budget)) timed_out = true;  // my buffers are free again
-      if (fuse && j > 0) add_dq(dq_prev);
+      if (fuse && j > 0) add_dq(red_row);
       // my own row: lse, delta, absolute position
       const bool row_ok = (my_n < TOKQ) && (tok0 + my_n < r_hi);
       float lse = 0.f, dl = 0.f;
@@ -261,9 +276,10 @@ __global__ void __launch_bounds__(480, 1)
         lse = p.lse[a];
         dl = p.delta[a];
         ta = pc.off + (int)(q_row - pc.q_start);
-        if (fuse) dq_prev = reinterpret_cast<__nv_bfloat16*>(p.dq) + q_row * p.dq_stride_t + (int64_t)(kh * G + my_g) * D;
-      } else {
-        dq_prev = nullptr;
+      }
+      if (fuse && t < n_box) {
+        const int tok = tok0 + t % TOKQ;
+        red_row = (tok < r_hi) ? __ldg(list + tok) : -1;
       }
       // keys kc_lo..kc_hi of the tile are visible to my row
       int kc_lo = 0, kc_hi = -1;
@@ -276,6 +292,10 @@ __global__ void __launch_bounds__(480, 1)
       const float nlse = -lse;
       if (!mbar_wait(bar(1, wg), j & 1, &budget)) timed_out = true;
       fence_after_sync();
+      if (fuse && j > 0) {   // the reductions of the previous tile have read my P / dS buffers
+        if (t < n_box) tma::bulk_wait_read();
+        named_barrier(2 + wg, 128);
+      }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t sv[32], dv[32];
@@ -318,7 +338,7 @@ __global__ void __launch_bounds__(480, 1)
     }
     // ---- all MMAs done (the tensor core retires them in issue order, group 1's last commit is the final one)
     if (!mbar_wait(bar(3, wg), (n_round - 1) & 1, &budget)) timed_out = true;
-    if (fuse) add_dq(dq_prev);
+    if (fuse) add_dq(red_row);
     if (!mbar_wait(bar(3, 1), (n_round - 1) & 1, &budget)) timed_out = true;
     fence_after_sync();
     // group 0 writes dV, group 1 writes dK: lane t = column t of the gradient
@@ -339,6 +359,7 @@ __global__ void __launch_bounds__(480, 1)
         }
       }
     }
+    if (fuse && t < n_box) tma::bulk_wait_all();
   }
   if (timed_out && p.status) atomicOr(p.status, 2);
   fence_before_sync();
@@ -355,13 +376,19 @@ int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 
     return NSA_ERR_CUDA;
   }
   const int G = p->QH / p->KH;
-  CUtensorMap tmq, tmo;
+  CUtensorMap tmq, tmo, tmdq;
   if (p->n_q_rows <= 0 || !tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, 1, G) ||
       !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, 1, G)) {
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q/dout must be 16-byte aligned, n_q_rows set)", name);
     return NSA_ERR_CUDA;
   }
-  dkdv_tc_kernel<D, MODE><<<grid, 480, smem, st>>>(*p, L, tmq, tmo);
+  if (!L.fuse_dq) {
+    tmdq = tmq;   // unused
+  } else if (!tma::make_map(&tmdq, p->dq, p->n_q_rows, p->QH, D, p->dq_stride_t, 1, G)) {
+    set_error("%s: cuTensorMapEncodeTiled failed for dq (must be 16-byte aligned with a row stride that is a multiple of 8)", name);
+    return NSA_ERR_CUDA;
+  }
+  dkdv_tc_kernel<D, MODE><<<grid, 480, smem, st>>>(*p, L, tmq, tmo, tmdq);
   return check_launch(name);
 }
 
