@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(480, 1)
   constexpr uint32_t A_LBO = (D == 128) ? Q_SLAB : 0;  // D = 64: the second half of M re-reads the only slab (rows 64.. of the result are unused)
   constexpr uint32_t IDESC_SD = make_idesc(BQ, BK, false, false), IDESC_KV = make_idesc(128, BK, true, true);
   constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, true, false);
-  constexpr uint32_t TM_DV = 256, TM_DK = 320, TM_COLS = 512;
+  constexpr uint32_t TM_DV = 256, TM_DK = 320, TM_DQ = 384, TM_COLS = 512;
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -135,8 +135,8 @@ __global__ void __launch_bounds__(480, 1)
   asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
   int budget = kWaitBudget;
   bool timed_out = false;
-  // selected branch with the dQ product fused in: after dV and dK of a tile, dS K goes into the tile's S / dP columns
-  // (both are consumed by then); the group adds it into dq before those columns take the next tile's S
+  // selected branch with the dQ product fused in: after dV and dK of a tile, dS K goes into columns of its own, shared by
+  // the two groups in turn; the tile's group adds it into dq
   const bool fuse = (MODE == MODE_SLC) && L.fuse_dq;
 
   if (warp == 8) {
@@ -145,7 +145,6 @@ __global__ void __launch_bounds__(480, 1)
       for (int j = 0; j < n_round; ++j) {
         for (int wg = 0; wg < 2; ++wg) {
           if (!mbar_wait(bar(0, wg), j & 1, &budget)) timed_out = true;
-          if (fuse && j > 0 && !mbar_wait(bar(4, wg), (j - 1) & 1, &budget)) timed_out = true;
           fence_after_sync();
           const uint32_t tQ = sQ0 + wg * Q_BYTES, tO = sO0 + wg * Q_BYTES;
 #pragma unroll
@@ -172,10 +171,13 @@ __global__ void __launch_bounds__(480, 1)
 #pragma unroll
           for (int u = 0; u < BQ / 16; ++u)
             mma_ss(tmem + TM_DK, desc_mnmajor(tQ + u * 2048, A_LBO), desc_mnmajor(tS + u * 2048, 0), IDESC_KV, (u > 0) ? 1u : first);
-          if (fuse) {
+          if (fuse) {   // dS K into its own columns, once the other group has read the previous tile's product out of them
+            const int m = 2 * j + wg;
+            if (m > 0 && !mbar_wait(bar(4, 0), (m - 1) & 1, &budget)) timed_out = true;
+            fence_after_sync();
 #pragma unroll
             for (int u = 0; u < BK / 16; ++u)
-              mma_ss(tmem + 128 * wg, desc_kmajor(tS + u * 32), desc_mnmajor(sK + u * 2048, K_SLAB), IDESC_DQ, u > 0);
+              mma_ss(tmem + TM_DQ, desc_kmajor(tS + u * 32), desc_mnmajor(sK + u * 2048, K_SLAB), IDESC_DQ, u > 0);
           }
           mma_commit(bar(3, wg));
         }
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(480, 1)
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = p.sm_scale * 1.4426950408889634f;
     const int my_n = t / G, my_g = t - my_n * G;
-    // fused dQ: my row of dS K (the tile's S / dP columns, complete once kv_done has fired) goes, as bf16, into my P and dS
+    // fused dQ: my row of dS K (complete once kv_done has fired) goes, as bf16, into my P and dS
     // buffers (free by then) in the layout of a q tile; one bulk tensor reduction per (token, 64-column slab) then adds
     // the token's [G heads x 64] box into dq.  red_row = tensor row of token t % TOKQ of the tile (threads that own a box).
     constexpr int SLABS = D / 64;
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(480, 1)
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(lane_base + 128 * wg + c * 32, v);
+        tmem_ld32(lane_base + TM_DQ + c * 32, v);
         wait_ld();
         const uint32_t sb = ((c >> 1) ? tS : tP) + t * 128;
 #pragma unroll
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(480, 1)
         }
       }
       fence_before_sync();
-      mbar_arrive(bar(4, wg));            // the S / dP columns may take the next tile
+      mbar_arrive(bar(4, 0));             // the dQ columns may take the next tile's product
       fence_proxy_async();
       named_barrier(2 + wg, 128);
       if (t < n_box) {
