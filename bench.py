@@ -300,7 +300,7 @@ def main():
         ach = fm[top] / (kernels[top] * 1e-3) / 1e12
         # DRAM bytes per launch of the kernels that can be the slowest one, from ncu captures at 32K tokens (profiles/),
         # scaled by tokens where the kernel's traffic is linear in tokens (the selected branch); None = not captured
-        ncu_traffic_32k = {"slc_dq": 1.7e6 + 511.0e6, "slc_fwd": 0.6e6 + 508.0e6, "slc_dkdv": 8.32e9 + 0.498e9}
+        ncu_traffic_32k = {"slc_bwd": 18.71e9 + 6.28e9, "slc_fwd": 0.6e6 + 508.0e6}
         traffic = ncu_traffic_32k[top] * (T_total / 32768) if top in ncu_traffic_32k else None
         roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
                     "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write at 32K tokens x tokens/32768" if traffic else None,

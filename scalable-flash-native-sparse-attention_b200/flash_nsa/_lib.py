@@ -95,6 +95,8 @@ def call(fn_name, params, stream):
     ph = getattr(params, "phases", 0) if fn_name.endswith("_bwd") else 0
     if ph:   # a backward entry point asked for a subset of {delta, dK/dV, dQ}
         n = bin(ph & 7).count("1")
+    if fn_name == "nsa_slc_attn_bwd" and (ph & 6) in (0, 6) and os.environ.get("NSA_SLC_BWD_UNFUSED", "0")[:1] != "1":
+        n -= 1   # dK/dV and dQ of the selected branch are one kernel when asked for together
     launch_count += n
     rc = getattr(L, fn_name)(ctypes.byref(params), ctypes.c_void_p(stream))
     if rc != 0:

@@ -23,7 +23,9 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
                  dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None,
                  accumulate_dq=None):
     """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
-    otherwise dq is new and dk/dv come back in k's dtype.  Deterministic: one CTA owns a key block."""
+    otherwise dq is new and dk/dv come back in k's dtype.  dK/dV and dQ come from ONE block-major kernel whatever
+    `fuse_dqdkdv` says (the reference's fuse_dqdkdv=True form, flash_nsa/ops/select_attn.py:148-335,646): per key block and
+    query tile it adds dS K into dq with bf16 reductions, so the last bits of dq depend on the order of those adds."""
     T, QH, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
