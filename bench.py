@@ -273,7 +273,7 @@ def main():
                 t.record_stream(s_out)
         s_main.wait_stream(s_out)
 
-    n_e2e = 0 if args.no_e2e else max(8, min(args.steps, 16))   # enough steps to amortise the un-hidden first copy-in / last copy-out
+    n_e2e = 0 if args.no_e2e else max(16, min(args.steps, 32))   # enough steps to amortise the un-hidden first copy-in / last copy-out
     if n_e2e:
         e2e_loop(2)
     sync_all()

@@ -156,7 +156,11 @@ int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream);
  * i.e. the flash-attn call with window_size=(window,-1), causal=True.                                     */
 int nsa_swa_fwd(const NsaAttnParams* p, void* stream);
 int nsa_swa_bwd(const NsaAttnParams* p, void* stream);
-/* selected-block attention: replaces slc_attn_fwd / slc_attn_bwd, flash_nsa/ops/select_attn.py:440-701    */
+/* selected-block attention: replaces slc_attn_fwd / slc_attn_bwd, flash_nsa/ops/select_attn.py:440-701.
+ * Backward: when dK/dV and dQ are both asked for (phases 0, 6 or 7) ONE block-major kernel produces them, adding its
+ * dQ tiles into dq with bf16 reductions (the reference's fuse_dqdkdv=True form, select_attn.py:148-335); with
+ * accumulate_dq = 0 dq is cleared first.  The last bits of dq then depend on the order of the adds; the environment
+ * variable NSA_SLC_BWD_UNFUSED=1 selects the token-major dQ kernel instead (fp32 accumulation, fixed order).        */
 int nsa_slc_attn_fwd(const NsaAttnParams* p, void* stream);
 int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream);
 
