@@ -4,9 +4,10 @@
 // one token for the whole kernel and everything after the MMA is thread-local:
 //   for each tile of 128 compressed rows, for each query head h of the kv head (in order h = 0..G-1):
 //       S_h = Q_h K^T                      tcgen05.mma, Q_h tile [128 tokens x d] and K tile [128 rows x d] loaded by TMA
-//       acc[c] += exp2(S_h[c]*c - lse_h)   the thread's 128 columns, fp32, heads accumulated in order
-//   mask the rows the token cannot see yet, pool 4 -> 1 (+ the row before) into 31 selection blocks and merge them
-//   into the thread's sorted list of the best free blocks (value descending, block index ascending).
+//       p[c] = exp2(S_h[c]*c - lse_h)      the thread's 128 columns, fp32; rows the token cannot see yet count as 0
+//       blk[i] += p[4i] + 2 (p[4i+1] + p[4i+2] + p[4i+3]) + p[4i+4]     31 selection blocks, heads in order
+//   merge the 31 block sums into the thread's sorted list of the best free blocks (value descending, block index
+//   ascending).
 // A tile starts one compressed row early and advances by 124 rows, so the "row before" of its first block is inside
 // the tile and tiles are independent.  Two warp groups take the even / odd tiles of the SAME tokens, so one TMA load of
 // Q_h feeds two MMAs; a ninth warp issues all TMA loads and MMAs.  At the end group 1's list is merged into group 0's.
@@ -189,12 +190,17 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
     const int64_t Tq = p.meta.piece_cu[p.meta.n_pieces];
     TopList lst;
     lst.init();
-    float acc[BN];
+    // Pooling is linear, so every head's probabilities go straight into the tile's 31 block sums (block i = columns
+    // 4i .. 4i+4 with weights 1 2 2 2 1): 32 accumulators per thread instead of 128, which leaves the compiler registers
+    // to keep a whole 32-column chunk of scale / exp2 / add chains in flight.
+    float blk[32];
 
     for (int jp = 0; jp < n_pairs; ++jp) {
       const int j = 2 * jp + wg;
+      const int row0 = STEP * j - 1;                       // column c is compressed row row0 + c
+      const bool full = (row0 >= 0) && (row0 + BN - 1 < nvis);   // no column of this tile is masked for my token
 #pragma unroll
-      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      for (int c = 0; c < 32; ++c) blk[c] = 0.f;
       float nlse = -__ldg(lse_p);
       for (int h = 0; h < G; ++h) {
         const int n = jp * G + h, b = n & 1;
@@ -207,31 +213,43 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
           uint32_t sv[32];
           tmem_ld32(lane_base + (2 * wg + b) * 128 + q4 * 32, sv);
           wait_ld();
+          if (q4 == 3) {   // every column of this S buffer has been read
+            fence_before_sync();
+            mbar_arrive(s_free + 8 * (2 * wg + b));
+          }
+          float e[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[q4 * 32 + i] += fast_exp2(fmaf(__uint_as_float(sv[i]), c2, cur));
+          for (int i = 0; i < 32; ++i) e[i] = fmaf(__uint_as_float(sv[i]), c2, cur);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) e[i] = fast_exp2(e[i]);
+          if (!full) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int r = row0 + q4 * 32 + i;
+              e[i] = (r >= 0 && r < nvis) ? e[i] : 0.f;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const int i = q4 * 8 + (c >> 2);
+            blk[i] += fmaf(2.f, (e[c + 1] + e[c + 2]) + e[c + 3], e[c]);
+            if (i > 0) blk[i - 1] += e[c];
+          }
         }
-        fence_before_sync();
-        mbar_arrive(s_free + 8 * (2 * wg + b));
       }
-      // ---- this tile's 31 blocks: column c is compressed row STEP*j - 1 + c
-      const int row0 = STEP * j - 1;
-#pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        const int r = row0 + c;
-        acc[c] = (r >= 0 && r < nvis) ? acc[c] : 0.f;
-      }
+      // ---- this tile's 31 blocks
 #pragma unroll
       for (int i = 0; i < 31; ++i) {
-        float pv = acc[4 * i] + ((2.f * acc[4 * i + 1] + 2.f * acc[4 * i + 2]) + (2.f * acc[4 * i + 3] + acc[4 * i + 4]));
+        float pv = blk[i];
         if (p.quant == 1) pv = __half2float(__float2half_rn(pv));
         else if (p.quant == 2) pv = __half2float(__float2half_rn(pv * pv * pv));
-        const int blk = 31 * j + i;
-        if (p.probs && tok_ok && blk < (int)p.probs_stride_t) {
-          const int64_t a = ((int64_t)kh * Tq + q_row) * p.probs_stride_t + blk;
+        const int bi = 31 * j + i;
+        if (p.probs && tok_ok && bi < (int)p.probs_stride_t) {
+          const int64_t a = ((int64_t)kh * Tq + q_row) * p.probs_stride_t + bi;
           if (p.quant == 0) reinterpret_cast<float*>(p.probs)[a] = pv;
           else reinterpret_cast<__half*>(p.probs)[a] = __float2half_rn(pv);
         }
-        if (blk >= ni && blk <= nk - nl) lst.insert_newer(pv, blk);
+        if (bi >= ni && bi <= nk - nl) lst.insert_newer(pv, bi);
       }
     }
     // ---- merge group 1's list into group 0's and write the row
