@@ -21,11 +21,13 @@ def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
 
 def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=None, fuse_dqdkdv=False,
                  dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None,
-                 accumulate_dq=None):
+                 accumulate_dq=None, two_kernel_dq=False):
     """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
     otherwise dq is new and dk/dv come back in k's dtype.  dK/dV and dQ come from ONE block-major kernel whatever
     `fuse_dqdkdv` says (the reference's fuse_dqdkdv=True form, flash_nsa/ops/select_attn.py:148-335,646): per key block and
-    query tile it adds dS K into dq with bf16 reductions, so the last bits of dq depend on the order of those adds."""
+    query tile it adds dS K into dq with bf16 reductions, so the last bits of dq depend on the order of those adds.
+    `two_kernel_dq=True` (not in the reference) runs the block-major dK/dV kernel and then the token-major dQ kernel, which
+    accumulates a token's dq in fp32 in a fixed order."""
     T, QH, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
@@ -49,7 +51,11 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
         p.n_blocks_total = offsets.size(1) - 1
         p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
         p.accumulate_dq = int(acc_dq)
-        if have_delta:
+        if two_kernel_dq:
+            p.phases = 2 if have_delta else 3
+            call("nsa_slc_attn_bwd", p, q)
+            p.phases = 4
+        elif have_delta:
             p.phases = 6
         call("nsa_slc_attn_bwd", p, q)
     if own:

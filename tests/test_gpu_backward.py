@@ -120,6 +120,37 @@ def test_branch_backward(lens, QH, KH, D):
     _check("comb dw", wd.grad, wr.grad)
 
 
+def test_selected_backward_one_kernel_equals_two_kernels():
+    """The block-major kernel that also adds dS K into dq (bf16 reductions) against the two-kernel form (token-major dQ,
+    fp32 accumulation per token): same dk / dv up to the order of their atomics, dq within bf16 rounding of 16 adds."""
+    for lens, QH, KH, D in (([1500, 700], 32, 2, 128), ([2100], 8, 2, 64), ([900], 40, 2, 128)):
+        q, k, v, w, do, cu = _mk(lens, QH, KH, D, seed=61)
+        _setup(cu)
+        from flash_nsa.ops import mean_pooling, compress_attn, slc_topk_indices
+        from flash_nsa.ops.select_attn import slc_attn_fwd, slc_attn_bwd
+        qd, kd, vd, dod = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+        ck = mean_pooling(kd)
+        _, lse_c = compress_attn(qd, ck, mean_pooling(vd))
+        res = slc_topk_indices(qd, ck, lse_c, maybe_efficient_version=True, scale_slc_p=True)
+        topk = res[0] if isinstance(res, (tuple, list)) else res
+        o, lse = slc_attn_fwd(qd, kd, vd, topk)
+        outs = []
+        for two in (False, True):
+            dq = torch.full_like(qd, 0.25)          # given dq: results are added into it
+            dk = torch.zeros(kd.shape, device="cuda", dtype=torch.float32)
+            dv = torch.zeros(vd.shape, device="cuda", dtype=torch.float32)
+            slc_attn_bwd(qd, kd, vd, topk, o, lse, dod, dq, dk, dv, two_kernel_dq=two)
+            outs.append((dq, dk, dv))
+        torch.cuda.synchronize()
+        for name, a, b in zip(("dq", "dk", "dv"), outs[0], outs[1]):
+            scale = max(1.0, b.float().abs().max().item())
+            tol = 2e-2 if name == "dq" else 1e-4
+            assert (a.float() - b.float()).abs().max().item() <= tol * scale, (name, lens, QH)
+        # a new dq (not given) starts from zero in both forms
+        dq0, _, _ = slc_attn_bwd(qd, kd, vd, topk, o, lse, dod)
+        assert (dq0.float() - (outs[1][0].float() - 0.25)).abs().max().item() <= 2e-2 * max(1.0, dq0.float().abs().max().item())
+
+
 def test_k2q_index_is_the_transpose():
     lens = [700, 130]
     q, k, v, w, do, cu = _mk(lens, 4, 2, 64, seed=5)
