@@ -9,8 +9,12 @@
 //   merge the 31 block sums into the thread's sorted list of the best free blocks (value descending, block index
 //   ascending).
 // A tile starts one compressed row early and advances by 124 rows, so the "row before" of its first block is inside
-// the tile and tiles are independent.  Two warp groups take the even / odd tiles of the SAME tokens, so one TMA load of
-// Q_h feeds two MMAs; a ninth warp issues all TMA loads and MMAs.  At the end group 1's list is merged into group 0's.
+// the tile and tiles are independent.  Three warp groups take three consecutive tiles of the SAME tokens, so one TMA
+// load of Q_h feeds three MMAs; each group has one S buffer in tensor memory (the next head's product is issued as soon
+// as the group has read the last column), and while one group waits for its product the other two keep the schedulers
+// busy: with two groups the kernel was bound by instruction latency at two warps per scheduler.  Warp 12 issues the
+// MMAs, warp 13 the TMA loads (14 warps are allocated as 16: 128 registers per thread).  At the end the lists of
+// groups 1 and 2 are merged into group 0's.
 // Nothing but the [kh, t, top_n] indices is written (optionally the block scores, for inspection).
 #include "tma.cuh"
 
@@ -72,10 +76,10 @@ struct TopList {
 }  // namespace
 
 template <int D>
-__global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, const __grid_constant__ CUtensorMap tmq,
+__global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, const __grid_constant__ CUtensorMap tmq,
                                                              const __grid_constant__ CUtensorMap tmk) {
   using namespace tc;
-  constexpr int BM = 128, BN = 128, STEP = 124, NQ = 4, SLABS = D / 64;
+  constexpr int BM = 128, BN = 128, STEP = 124, NQ = 4, NW = 3, SLABS = D / 64;
   constexpr uint32_t TILE_BYTES = BM * D * 2, SLAB_BYTES = 128 * 128;
   constexpr uint32_t IDESC = make_idesc(BM, BN, false);
 
@@ -83,9 +87,9 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
   const uint32_t base = smem_u32(smem_raw);
   const uint32_t sQ = base;                       // NQ stages
   const uint32_t sK = sQ + NQ * TILE_BYTES;       // one tile per warp group
-  const uint32_t bars = sK + 2 * TILE_BYTES;
-  const uint32_t q_full = bars, q_free = bars + 8 * NQ, k_full = bars + 16 * NQ, k_free = k_full + 16;
-  const uint32_t s_full = k_free + 16, s_free = s_full + 32, tm_slot = s_free + 32;   // s_*[wg][buf]
+  const uint32_t bars = sK + NW * TILE_BYTES;
+  const uint32_t q_full = bars, q_free = bars + 8 * NQ, k_full = bars + 16 * NQ, k_free = k_full + 8 * NW;
+  const uint32_t s_full = k_free + 8 * NW, s_free = s_full + 8 * NW, tm_slot = s_free + 8 * NW;   // s_*[wg]
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -104,21 +108,19 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
   const int tabs_max = pc.off + t0 + ntok - 1;
   const int nvis_max = (tabs_max >= ks - 1) ? min(pc.y_len, (tabs_max - (ks - 1)) / st + 1) : 0;
   const int n_tiles = max(nvis_max / STEP + 1, max(tabs_max, 0) / bs / 31 + 1);
-  const int n_pairs = (n_tiles + 1) / 2;
-  const int N = n_pairs * G;  // MMA steps per warp group
+  const int n_rounds = (n_tiles + NW - 1) / NW;   // each round: NW consecutive tiles, one per warp group
+  const int N = n_rounds * G;                      // MMA steps per warp group
 
   if (tid == 0) {
     for (int s = 0; s < NQ; ++s) {
       mbar_init(q_full + 8 * s, 1);
       mbar_init(q_free + 8 * s, 1);
     }
-    for (int w = 0; w < 2; ++w) {
+    for (int w = 0; w < NW; ++w) {
       mbar_init(k_full + 8 * w, 1);
       mbar_init(k_free + 8 * w, 1);
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(s_full + 8 * (2 * w + b), 1);
-        mbar_init(s_free + 8 * (2 * w + b), 128);
-      }
+      mbar_init(s_full + 8 * w, 1);
+      mbar_init(s_free + 8 * w, 128);
     }
     fence_mbar_init();
   }
@@ -131,53 +133,62 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
   int budget = kWaitBudget;
   bool timed_out = false;
 
-  if (warp == 8) {
+  if (warp == 4 * NW + 1) {
     if ((tid & 31) == 0) {
-      // ============================================ producer: TMA loads and MMA issue
+      // ============================================ TMA producer: the K tiles of each round, the Q_h tile of every step
       const int q_row0 = pc.q_start + t0;
-      int nl_ = 0;  // next step whose Q tile is to be loaded
-      auto top_up = [&](int upto) {
-        while (nl_ < N && nl_ < upto) {
-          const int s = nl_ % NQ;
-          if (nl_ >= NQ && !mbar_wait(q_free + 8 * s, ((nl_ / NQ) - 1) & 1, &budget)) timed_out = true;
-          tma::expect_tx(q_full + 8 * s, TILE_BYTES);
-          const int head = kh * G + (nl_ % G);
+      auto load_q = [&](int n) {
+        const int s = n % NQ;
+        if (n >= NQ && !mbar_wait(q_free + 8 * s, ((n / NQ) - 1) & 1, &budget)) timed_out = true;
+        tma::expect_tx(q_full + 8 * s, TILE_BYTES);
+        const int head = kh * G + (n % G);
 #pragma unroll
-          for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sQ + s * TILE_BYTES + sl * SLAB_BYTES, &tmq, sl * 64, head, q_row0, q_full + 8 * s);
-          ++nl_;
-        }
+        for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sQ + s * TILE_BYTES + sl * SLAB_BYTES, &tmq, sl * 64, head, q_row0, q_full + 8 * s);
       };
-      top_up(NQ - 1);
-      for (int jp = 0; jp < n_pairs; ++jp) {
-        for (int w = 0; w < 2; ++w) {
-          if (jp > 0 && !mbar_wait(k_free + 8 * w, (jp - 1) & 1, &budget)) timed_out = true;
+      auto load_k = [&](int jr) {
+        for (int w = 0; w < NW; ++w) {
+          if (jr > 0 && !mbar_wait(k_free + 8 * w, (jr - 1) & 1, &budget)) timed_out = true;
           tma::expect_tx(k_full + 8 * w, TILE_BYTES);
-          const int row = pc.y_bos + STEP * (2 * jp + w) - 1;
+          const int row = pc.y_bos + STEP * (NW * jr + w) - 1;
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) tma::load_3d(sK + w * TILE_BYTES + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, k_full + 8 * w);
         }
+      };
+      // the K tiles of round jr can only be fetched when the last MMA of round jr - 1 is done; by then the Q tiles of the
+      // first NQ - 2 steps of round jr are already on their way (their stages were freed earlier)
+      load_k(0);
+      for (int n = 0; n < N; ++n) {
+        load_q(n);
+        const int m = n + 2 - NQ;                    // step m - 1 can complete with what has been requested so far
+        if (m > 0 && m % G == 0) load_k(m / G);
+      }
+      for (int jr = max(1, (N + 1 - NQ) / G + 1); jr < n_rounds; ++jr) load_k(jr);
+    }
+  } else if (warp == 4 * NW) {
+    if ((tid & 31) == 0) {
+      // ============================================ MMA issue: one S buffer per warp group
+      for (int jr = 0; jr < n_rounds; ++jr) {
         for (int h = 0; h < G; ++h) {
-          const int n = jp * G + h, s = n % NQ, b = n & 1;
+          const int n = jr * G + h, s = n % NQ;
           if (!mbar_wait(q_full + 8 * s, (n / NQ) & 1, &budget)) timed_out = true;
-          for (int w = 0; w < 2; ++w) {
-            if (h == 0 && !mbar_wait(k_full + 8 * w, jp & 1, &budget)) timed_out = true;
-            if (n >= 2 && !mbar_wait(s_free + 8 * (2 * w + b), ((n >> 1) - 1) & 1, &budget)) timed_out = true;
+          for (int w = 0; w < NW; ++w) {
+            if (h == 0 && !mbar_wait(k_full + 8 * w, jr & 1, &budget)) timed_out = true;
+            if (n >= 1 && !mbar_wait(s_free + 8 * w, (n - 1) & 1, &budget)) timed_out = true;
             fence_after_sync();
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
               const uint32_t off = (k >> 2) * SLAB_BYTES + (k & 3) * 32;
-              mma_ss(tmem + (2 * w + b) * 128, desc_kmajor(sQ + s * TILE_BYTES + off), desc_kmajor(sK + w * TILE_BYTES + off), IDESC, k > 0);
+              mma_ss(tmem + w * 128, desc_kmajor(sQ + s * TILE_BYTES + off), desc_kmajor(sK + w * TILE_BYTES + off), IDESC, k > 0);
             }
-            mma_commit(s_full + 8 * (2 * w + b));
+            mma_commit(s_full + 8 * w);
             if (h == G - 1) mma_commit(k_free + 8 * w);
           }
           mma_commit(q_free + 8 * s);
-          top_up(n + NQ);
         }
       }
     }
   } else {
-    // ============================================ two warp groups: even / odd tiles of the same 128 tokens
+    // ============================================ NW warp groups: tiles NW*jr + wg of the same 128 tokens
     const int wg = warp >> 2, t = tid & 127;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const bool tok_ok = t < ntok;
@@ -191,47 +202,46 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
     TopList lst;
     lst.init();
     // Pooling is linear, so every head's probabilities go straight into the tile's 31 block sums (block i = columns
-    // 4i .. 4i+4 with weights 1 2 2 2 1): 32 accumulators per thread instead of 128, which leaves the compiler registers
-    // to keep a whole 32-column chunk of scale / exp2 / add chains in flight.
+    // 4i .. 4i+4 with weights 1 2 2 2 1): 32 accumulators per thread instead of 128.
     float blk[32];
 
-    for (int jp = 0; jp < n_pairs; ++jp) {
-      const int j = 2 * jp + wg;
+    for (int jr = 0; jr < n_rounds; ++jr) {
+      const int j = NW * jr + wg;
       const int row0 = STEP * j - 1;                       // column c is compressed row row0 + c
       const bool full = (row0 >= 0) && (row0 + BN - 1 < nvis);   // no column of this tile is masked for my token
 #pragma unroll
       for (int c = 0; c < 32; ++c) blk[c] = 0.f;
       float nlse = -__ldg(lse_p);
       for (int h = 0; h < G; ++h) {
-        const int n = jp * G + h, b = n & 1;
+        const int n = jr * G + h;
         const float cur = nlse;
         if (h + 1 < G) nlse = -__ldg(lse_p + (int64_t)(h + 1) * p.lse_stride_h);
-        if (!mbar_wait(s_full + 8 * (2 * wg + b), (n >> 1) & 1, &budget)) timed_out = true;
+        if (!mbar_wait(s_full + 8 * wg, n & 1, &budget)) timed_out = true;
         fence_after_sync();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t sv[32];
-          tmem_ld32(lane_base + (2 * wg + b) * 128 + q4 * 32, sv);
+        for (int q8 = 0; q8 < 8; ++q8) {
+          uint32_t sv[16];
+          tmem_ld16(lane_base + wg * 128 + q8 * 16, sv);
           wait_ld();
-          if (q4 == 3) {   // every column of this S buffer has been read
+          if (q8 == 7) {   // every column of my S buffer has been read: the next head's product may overwrite it
             fence_before_sync();
-            mbar_arrive(s_free + 8 * (2 * wg + b));
+            mbar_arrive(s_free + 8 * wg);
           }
-          float e[32];
+          float e[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) e[i] = fmaf(__uint_as_float(sv[i]), c2, cur);
+          for (int i = 0; i < 16; ++i) e[i] = fmaf(__uint_as_float(sv[i]), c2, cur);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) e[i] = fast_exp2(e[i]);
+          for (int i = 0; i < 16; ++i) e[i] = fast_exp2(e[i]);
           if (!full) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int r = row0 + q4 * 32 + i;
+            for (int i = 0; i < 16; ++i) {
+              const int r = row0 + q8 * 16 + i;
               e[i] = (r >= 0 && r < nvis) ? e[i] : 0.f;
             }
           }
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const int i = q4 * 8 + (c >> 2);
+          for (int c = 0; c < 16; c += 4) {
+            const int i = q8 * 4 + (c >> 2);
             blk[i] += fmaf(2.f, (e[c + 1] + e[c + 2]) + e[c + 3], e[c]);
             if (i > 0) blk[i - 1] += e[c];
           }
@@ -252,22 +262,25 @@ __global__ void __launch_bounds__(288, 1) slc_topk_tc_kernel(NsaTopkParams p, co
         if (bi >= ni && bi <= nk - nl) lst.insert_newer(pv, bi);
       }
     }
-    // ---- merge group 1's list into group 0's and write the row
+    // ---- merge the other groups' lists into group 0's and write the row
     __syncwarp();
     float* mv = reinterpret_cast<float*>(smem_raw);            // the Q stages are idle now (all MMAs have completed)
-    int* mi = reinterpret_cast<int*>(smem_raw + 128 * kList * 4);
-    named_barrier(1, 256);
-    if (wg == 1) {
+    int* mi = reinterpret_cast<int*>(smem_raw + (NW - 1) * 128 * kList * 4);
+    named_barrier(1, 128 * NW);
+    if (wg > 0) {
 #pragma unroll
       for (int k = 0; k < kList; ++k) {
-        mv[k * 128 + t] = lst.v[k];
-        mi[k * 128 + t] = lst.i[k];
+        mv[((wg - 1) * kList + k) * 128 + t] = lst.v[k];
+        mi[((wg - 1) * kList + k) * 128 + t] = lst.i[k];
       }
     }
-    named_barrier(1, 256);
+    named_barrier(1, 128 * NW);
     if (wg == 0) {
+#pragma unroll 1
+      for (int g = 0; g < NW - 1; ++g) {
 #pragma unroll
-      for (int k = 0; k < kList; ++k) lst.insert(mv[k * 128 + t], mi[k * 128 + t]);
+        for (int k = 0; k < kList; ++k) lst.insert(mv[(g * kList + k) * 128 + t], mi[(g * kList + k) * 128 + t]);
+      }
       if (tok_ok) {
         const int n_free = max(0, min(top_n, nk + 1) - ni - nl);
         int32_t* out = p.topk + ((int64_t)kh * Tq + q_row) * top_n;
@@ -298,7 +311,7 @@ int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, 
     return NSA_ERR_CUDA;
   }
   const int D = p->D;
-  size_t smem = (size_t)6 * 128 * D * 2 + 256;
+  size_t smem = (size_t)7 * 128 * D * 2 + 256;
   cudaError_t e = (D == 128) ? cudaFuncSetAttribute(slc_topk_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                              : cudaFuncSetAttribute(slc_topk_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -306,8 +319,8 @@ int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, 
     return NSA_ERR_CUDA;
   }
   dim3 grid((p->meta.max_piece_len + 127) / 128, p->meta.n_pieces, p->KH);
-  if (D == 128) slc_topk_tc_kernel<128><<<grid, 288, smem, st>>>(*p, tmq, tmk);
-  else slc_topk_tc_kernel<64><<<grid, 288, smem, st>>>(*p, tmq, tmk);
+  if (D == 128) slc_topk_tc_kernel<128><<<grid, 448, smem, st>>>(*p, tmq, tmk);
+  else slc_topk_tc_kernel<64><<<grid, 448, smem, st>>>(*p, tmq, tmk);
   return check_launch("slc_topk");
 }
 
