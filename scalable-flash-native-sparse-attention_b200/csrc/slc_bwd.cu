@@ -189,7 +189,9 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   // kernel and its second pass over K, V, q, dout are not needed.  NSA_SLC_BWD_UNFUSED=1 keeps the two-kernel form
   // (dq accumulated in fp32 per token, deterministic).
   static const bool unfused = [] { const char* e = getenv("NSA_SLC_BWD_UNFUSED"); return e && e[0] == '1'; }();
-  const bool fuse = (ph & 2) && (ph & 4) && !unfused && p->n_blocks_total > 0;
+  // the bulk tensor reductions need dq 16-byte aligned with a row stride that is a multiple of 16 bytes
+  const bool dq_tma_ok = (((uintptr_t)p->dq) & 15) == 0 && (p->dq_stride_t * 2) % 16 == 0;
+  const bool fuse = (ph & 2) && (ph & 4) && !unfused && dq_tma_ok && p->n_blocks_total > 0;
   if (fuse && !p->accumulate_dq) {
     cudaError_t e = cudaMemset2DAsync(p->dq, (size_t)p->dq_stride_t * 2, 0, (size_t)p->QH * p->D * 2, (size_t)p->n_q_rows, st);
     if (e != cudaSuccess) {

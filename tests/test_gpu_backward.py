@@ -146,6 +146,13 @@ def test_selected_backward_one_kernel_equals_two_kernels():
             scale = max(1.0, b.float().abs().max().item())
             tol = 2e-2 if name == "dq" else 1e-4
             assert (a.float() - b.float()).abs().max().item() <= tol * scale, (name, lens, QH)
+        # a dq that bulk tensor reductions cannot address (8-byte aligned only) takes the two-kernel form by itself
+        flat = torch.full((qd.numel() + 8,), 0.25, dtype=qd.dtype, device="cuda")
+        dq_u = flat[4:4 + qd.numel()].view_as(qd)
+        dk = torch.zeros(kd.shape, device="cuda", dtype=torch.float32)
+        dv = torch.zeros(vd.shape, device="cuda", dtype=torch.float32)
+        slc_attn_bwd(qd, kd, vd, topk, o, lse, dod, dq_u, dk, dv)
+        assert torch.equal(dq_u, outs[1][0])
         # a new dq (not given) starts from zero in both forms
         dq0, _, _ = slc_attn_bwd(qd, kd, vd, topk, o, lse, dod)
         assert (dq0.float() - (outs[1][0].float() - 0.25)).abs().max().item() <= 2e-2 * max(1.0, dq0.float().abs().max().item())
