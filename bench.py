@@ -305,6 +305,9 @@ def main():
         roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
                     "traffic": traffic, "traffic_source": "ncu dram__bytes_read+write at 32K tokens x tokens/32768" if traffic else None,
                     "peak_source": peak_src, "ms": kernels[top]}
+        if traffic:   # how close the same launch is to the HBM roof, from the measured DRAM traffic (not algorithmic bytes)
+            roofline["dram_gbs_from_traffic"] = traffic / (kernels[top] * 1e-3) / 1e9
+            roofline["dram_frac_from_traffic"] = roofline["dram_gbs_from_traffic"] / peak_gbs
 
     if rank != 0:
         if world > 1:
