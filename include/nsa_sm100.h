@@ -319,6 +319,12 @@ typedef struct NsaRopeParams {
 int nsa_rope(const NsaRopeParams* p, void* stream);
 
 /* ---- misc -------------------------------------------------------------------------------------------- */
+/* No counterpart in the reference (Triton kernels have no bounded waits).  Runs the give-up path of the bounded pipeline
+ * wait that every tcgen05 / TMA kernel here uses, on purpose and with nothing in flight: one warp polls a barrier that
+ * nobody arrives on at most `polls` times (1 .. 2^20), then ORs bit 512 into *status and returns.  *waits_failed
+ * (optional) receives 1000 * (number of waits that gave up) + the poll budget left for later waits.  The context stays
+ * usable; a test calls this to see that a time-out becomes a status bit and not a hang.                              */
+int nsa_selftest_wait_timeout(int32_t* status, int32_t polls, int32_t* waits_failed, void* stream);
 const char* nsa_last_error(void);
 int nsa_version(void);
 /* sizeof() of a parameter struct by name ("NsaAttnParams", ...), 0 if unknown: lets a binding verify its mirror */

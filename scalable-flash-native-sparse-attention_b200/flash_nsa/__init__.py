@@ -18,3 +18,4 @@ from .layers.megatron_level_nsa import NSA
 from .layers.hf_level_nsa import HFNSA
 
 from .inference import nsa_prefill, nsa_decode
+from .ops._common import check_status

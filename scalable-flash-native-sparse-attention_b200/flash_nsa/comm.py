@@ -1,11 +1,15 @@
 """Context-parallel exchange: all-gather of K/V shards into a full-sequence buffer and reduce-scatter of the
 fp32 dK/dV, over a torch.distributed process group (NCCL over NVLink on GPUs).
 
-Same role as the reference's `Comm` (flash_nsa/comm.py:15-68), different mechanics: the gather buffers are
-double-buffered so the gather of the next kv-head group is issued BEFORE the current group's kernels and
-overlaps them, and the cp_mode=2 zig-zag is undone by an out-of-place reorder kernel into the final buffer.
-With CPU tensors (gloo, used by the multi-process host-logic tests) the reorder is done with torch indexing
-and the reduce-scatter falls back to all-reduce + slice, since gloo has no reduce-scatter.
+Same role as the reference's `Comm` (flash_nsa/comm.py:15-68), different mechanics.  The full-sequence K/V
+buffers are double-buffered, so the caller issues the gather of kv-head group h+1 right after it has waited
+for group h, BEFORE group h's attention kernels are enqueued: a NCCL collective starts once the work that was
+on the compute stream at the time of the call has finished, so issued there it runs under those kernels.  For
+cp_mode=2 the gather lands rank-major in a staging buffer and an out-of-place reorder kernel un-zig-zags it
+into the final buffer on a side stream, also under the kernels; `wait()` only makes the compute stream wait
+for that stream's event.  With CPU tensors (gloo, used by the multi-process host-logic tests) the reorder is
+done with torch indexing and the reduce-scatter falls back to all-reduce + slice, since gloo has no
+reduce-scatter.
 """
 import torch
 import torch.distributed as dist
@@ -36,11 +40,16 @@ class Comm:
         self.t, self.heads = t_local, heads
         dims = {self.KEY: d, self.VALUE: vd}
         n = t_local * world_size
-        self.gather = {key: [torch.empty(n, heads, dd, dtype=dtype, device=device) for _ in range(2)] for key, dd in dims.items()}
+        # final (sequential token order) buffers, two per key; cp_mode 2 gathers into one staging buffer per key first
+        self.final = {key: [torch.empty(n, heads, dd, dtype=dtype, device=device) for _ in range(2)] for key, dd in dims.items()}
+        self.stage = ({key: torch.empty(n, heads, dd, dtype=dtype, device=device) for key, dd in dims.items()}
+                      if cp_mode == 2 else None)
         self.turn = {self.KEY: 0, self.VALUE: 0}
         self.pending = {}
         self.ready = {}
         self.grads = None
+        self.cuda = torch.device(device).type == "cuda"
+        self.side = torch.cuda.Stream(device=device) if (self.cuda and cp_mode == 2) else None
         if with_grads:
             self.grads = {self.GRAD_KEY: torch.empty(n, heads, d, dtype=torch.float32, device=device),
                           self.GRAD_VALUE: torch.empty(n, heads, vd, dtype=torch.float32, device=device)}
@@ -51,22 +60,42 @@ class Comm:
     # -------------------------------------------------------------- K / V
     @torch.no_grad()
     def all_gather(self, x, key):
-        """Start gathering the local shard `x` [t, heads, d]; rank-major order (un-shuffled in wait())."""
-        buf = self.gather[key][self.turn[key]]
+        """Start gathering the local shard `x` [t, heads, d] into the buffer that the PREVIOUS wait(key) did not return.
+        Safe to call while kernels that read the other buffer are still queued on the compute stream."""
+        out = self.final[key][self.turn[key]]
         self.turn[key] ^= 1
-        h = dist.all_gather_into_tensor(buf, x.contiguous(), group=self.pg, async_op=True)
-        self.pending[key] = (h, buf)
+        if self.cp_mode == 1:
+            h = dist.all_gather_into_tensor(out, x.contiguous(), group=self.pg, async_op=True)
+            self.pending[key] = (h, out, None)
+            return
+        stage = self.stage[key]
+        h = dist.all_gather_into_tensor(stage, x.contiguous(), group=self.pg, async_op=True)
+        if self.side is None:                       # CPU tensors
+            h.wait()
+            out.copy_(_reorder(stage, self.W, "unshuffle"))
+            self.pending[key] = (None, out, None)
+            return
+        # un-zig-zag on the side stream as soon as the gather is done; the staging buffer is free for the next gather by
+        # then because that gather is issued after wait(key), i.e. after the compute stream took this event
+        with torch.cuda.stream(self.side):
+            h.wait()
+            from .ops.reorder import reorder
+            reorder(stage, self.W, shuffle_mode="unshuffle", out=out)
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+        self.pending[key] = (None, out, ev)
 
     @torch.no_grad()
     def wait(self, key):
-        """Block the current stream until the pending operation on `key` is done; for K/V returns the full
-        sequence [t*W, heads, d] in sequential token order."""
+        """Make the current stream wait for the pending operation on `key`; for K/V returns the full sequence
+        [t*W, heads, d] in sequential token order."""
         if key not in self.pending:
             return self.ready.get(key)
-        h, buf = self.pending.pop(key)
-        h.wait()
-        if key in (self.KEY, self.VALUE) and self.cp_mode == 2:
-            buf = _reorder(buf, self.W, "unshuffle")
+        h, buf, ev = self.pending.pop(key)
+        if h is not None:
+            h.wait()
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
         self.ready[key] = buf
         return buf
 
@@ -81,7 +110,11 @@ class Comm:
 
     # -------------------------------------------------------------- dK / dV
     def grad_buffers(self):
-        """Zero-filled global fp32 dK, dV for one head group."""
+        """Zero-filled global fp32 dK, dV for one head group.  The zero fill is ordered behind the previous group's
+        reduce-scatter, which reads the same tensors (cp_mode 1) or their shuffled copies (cp_mode 2): callers wait for
+        GRAD_KEY / GRAD_VALUE of a group before asking for the next group's buffers, and this method checks it."""
+        assert self.GRAD_KEY not in self.pending and self.GRAD_VALUE not in self.pending, \
+            "wait(GRAD_KEY) / wait(GRAD_VALUE) of the previous head group must come before grad_buffers()"
         dk, dv = self.grads[self.GRAD_KEY], self.grads[self.GRAD_VALUE]
         dk.zero_()
         dv.zero_()
@@ -102,5 +135,5 @@ class Comm:
             out.copy_(full[r * self.t:(r + 1) * self.t])
             return out
         h = dist.reduce_scatter_tensor(out, full, group=self.pg, async_op=True)
-        self.pending[key] = (h, out)
+        self.pending[key] = (h, out, None)
         return out

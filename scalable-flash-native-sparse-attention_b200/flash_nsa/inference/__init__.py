@@ -8,6 +8,7 @@ forward kernels running on a piece table with the paged-row lookup switched on: 
 "piece" whose first row sits at position context_len - new_tokens of its sequence.  No host synchronisation happens in
 any of these calls, shapes depend only on the arguments, so a decode step can be captured in a CUDA graph.
 """
+from ..ops._common import poll_status, post_status
 from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
                   topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
                   combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported)
@@ -38,6 +39,7 @@ def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, cont
     assert k.size(1) % 128 == 0
     if sm_scale is None:
         sm_scale = q.size(-1) ** -0.5
+    poll_status(q.device)      # a pipeline time-out of an earlier call raises here, without synchronising
     hp = dict(kernel_size=kernel_size, stride=stride)
     mean_pooling_prefill(k, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
     mean_pooling_prefill(v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
@@ -50,7 +52,9 @@ def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, cont
                                 block_size=block_size, top_n=top_n, sm_scale=sm_scale)
     swa_o = swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
                         window_size=window_size, sm_scale=sm_scale)
-    return combine_prefill(cmp_o, slc_o, swa_o, w)
+    o = combine_prefill(cmp_o, slc_o, swa_o, w)
+    post_status(q.device)
+    return o
 
 
 def nsa_decode(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits=0, slc_num_splits=0,
@@ -63,12 +67,16 @@ def nsa_decode(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_blo
     assert k.size(1) % 128 == 0
     if sm_scale is None:
         sm_scale = q.size(-1) ** -0.5
+    poll_status(q.device)      # as in nsa_prefill; skipped while the step is being captured into a CUDA graph
     if decode_fused_supported(q, k, kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks):
-        return nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, fixed_y_maxlen,
-                                kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks, window_size, sm_scale)
-    return nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits,
-                              slc_num_splits, fixed_y_maxlen, fixed_num_slc_blocks, kernel_size, stride, block_size, top_n,
-                              num_init_blocks, num_local_blocks, window_size, sm_scale)
+        o = nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, fixed_y_maxlen,
+                             kernel_size, stride, block_size, top_n, num_init_blocks, num_local_blocks, window_size, sm_scale)
+    else:
+        o = nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits,
+                               slc_num_splits, fixed_y_maxlen, fixed_num_slc_blocks, kernel_size, stride, block_size, top_n,
+                               num_init_blocks, num_local_blocks, window_size, sm_scale)
+    post_status(q.device)
+    return o
 
 
 def nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, cmp_num_splits=0,

@@ -8,6 +8,7 @@ import torch
 
 from ..comm import Comm
 from ..config import NSAConfig
+from ..ops._common import poll_status, post_status
 from ..ops.act import sigmoid_mul_bwd, sigmoid_mul_fwd, swiglu_bwd, swiglu_fwd
 from ..ops.combine import combine_bwd, combine_fwd
 from ..ops.compress_attn import cmp_attn_bwd, cmp_attn_fwd
@@ -185,28 +186,28 @@ class CPNSAFunction(torch.autograd.Function):
             q = chunk_q[:, h0 * G:(h0 + stride) * G]
             w_i = combine_weight[:, h0 * G:(h0 + stride) * G]
             k = comm.wait(Comm.KEY)
-            block_k, hidden_k, cmp_k = compress_kv_fwd(k, cmp_k_weight, H.cmp_k_method)
             v = comm.wait(Comm.VALUE)
+            if h0 + stride < kh:
+                # the next group's gather goes out NOW, before this group's kernels are enqueued: the collective starts
+                # when the work queued so far is done, so it runs under the kernels below (it fills the other buffer pair)
+                comm.all_gather(chunk_k[:, h0 + stride:h0 + 2 * stride], Comm.KEY)
+                comm.all_gather(chunk_v[:, h0 + stride:h0 + 2 * stride], Comm.VALUE)
+            block_k, hidden_k, cmp_k = compress_kv_fwd(k, cmp_k_weight, H.cmp_k_method)
             block_v, hidden_v, cmp_v = compress_kv_fwd(v, cmp_v_weight, H.cmp_v_method)
             cmp_o, cmp_lse = cmp_attn_fwd(q, cmp_k, cmp_v, sm_scale=sm_scale)
             topk, _ = slc_topk_indices(q, cmp_k, cmp_lse, sm_scale=sm_scale, maybe_efficient_version=True, scale_slc_p=True)
             slc_o, slc_lse = slc_attn_fwd(q, k, v, topk, sm_scale=sm_scale)
             swa_o, swa_lse = swa_fwd(q, k, v, sm_scale=sm_scale)
             comm.release()  # the gathered K/V of this head group are no longer read by later launches
-            if h0 + stride < kh:
-                comm.all_gather(chunk_k[:, h0 + stride:h0 + 2 * stride], Comm.KEY)
-                comm.all_gather(chunk_v[:, h0 + stride:h0 + 2 * stride], Comm.VALUE)
             combine_fwd(cmp_o, slc_o, swa_o, w_i, out=combine_o[:, h0 * G:(h0 + stride) * G])
-            cmp_tensors = [block_k, hidden_k, cmp_k, block_v, hidden_v, cmp_v]
-            if H.recompute_cmp_kv or True:
-                # compressed tensors cover the GLOBAL sequence; they are always rebuilt in backward
-                cmp_tensors = [None] * 6
+            # the compressed tensors cover the GLOBAL sequence: they are never kept, backward rebuilds them
             if H.recompute_cmp_o:
                 cmp_o, cmp_lse = None, None
             if H.recompute_slc_o:
                 slc_o, slc_lse = None, None
             if H.recompute_swa_o:
                 swa_o, swa_lse = None, None
+            del block_k, hidden_k, cmp_k, block_v, hidden_v, cmp_v
             saved.append([cmp_o, cmp_lse, slc_o, slc_lse, swa_o, swa_lse, topk])
         flat, layout = [], []
         for group in saved:
@@ -251,8 +252,11 @@ class CPNSAFunction(torch.autograd.Function):
             w_i = combine_weight[:, h0 * G:(h0 + stride) * G]
             dq = chunk_dq[:, h0 * G:(h0 + stride) * G]
             k = comm.wait(Comm.KEY)
-            block_k, hidden_k, cmp_k = compress_kv_fwd(k, cmp_k_weight, km, helper)
             v = comm.wait(Comm.VALUE)
+            if h0 + stride < kh:   # next group's K/V: issued before this group's kernels, runs under them
+                comm.all_gather(chunk_k[:, h0 + stride:h0 + 2 * stride], Comm.KEY)
+                comm.all_gather(chunk_v[:, h0 + stride:h0 + 2 * stride], Comm.VALUE)
+            block_k, hidden_k, cmp_k = compress_kv_fwd(k, cmp_k_weight, km, helper)
             block_v, hidden_v, cmp_v = compress_kv_fwd(v, cmp_v_weight, vm, helper)
             if cmp_o is None:
                 cmp_o, cmp_lse = cmp_attn_fwd(q, cmp_k, cmp_v, sm_scale=sm_scale, helper=helper)
@@ -275,9 +279,6 @@ class CPNSAFunction(torch.autograd.Function):
             _, fv = compress_kv_bwd(v, cmp_v_weight, block_v, hidden_v, dcmp_v, dv, version=vm, helper=helper, async_dw=True)
             dv_local = comm.reduce_scatter(Comm.GRAD_VALUE)
             comm.release()
-            if h0 + stride < kh:
-                comm.all_gather(chunk_k[:, h0 + stride:h0 + 2 * stride], Comm.KEY)
-                comm.all_gather(chunk_v[:, h0 + stride:h0 + 2 * stride], Comm.VALUE)
             if isinstance(fk, Callable):
                 g = fk()
                 if dwk is not None and g is not None:
@@ -355,6 +356,12 @@ class NSACore(torch.nn.Module):
         assert cu_seqlens is not None
         cp_mode = cp_mode if cp_mode is not None else self.cp_mode
         NSAHelper.init_cu_seqlens(cu_seqlens, x_cu_seqlens_np=cu_seqlens_np, cp_mode=cp_mode)
+        # a pipeline time-out reported by the kernels of an EARLIER call raises here (no synchronisation: the status word is
+        # copied to pinned host memory behind each forward and looked at when the next one starts)
+        poll_status(q.device)
         if NSAHelper.world_size <= 1:
-            return flash_nsa_varlen_func(q, k, v, combine_weight, self.cmp_k_weight, self.cmp_v_weight, self.sm_scale)
-        return cp_flash_nsa_varlen_func(q, k, v, combine_weight, self.cmp_k_weight, self.cmp_v_weight, self.sm_scale)
+            o = flash_nsa_varlen_func(q, k, v, combine_weight, self.cmp_k_weight, self.cmp_v_weight, self.sm_scale)
+        else:
+            o = cp_flash_nsa_varlen_func(q, k, v, combine_weight, self.cmp_k_weight, self.cmp_v_weight, self.sm_scale)
+        post_status(q.device)
+        return o

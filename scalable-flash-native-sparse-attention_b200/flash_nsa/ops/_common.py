@@ -59,24 +59,77 @@ def check_bf16_3d(name, t, last_contig=True):
 
 
 _status = {}
+_mirror = {}   # device index -> [pinned host copy of the word, event of the last copy or None]
+
+STATUS_BITS = {1: "dense forward", 2: "selected-branch dK/dV", 4: "dense dQ", 8: "misaligned shared memory", 16: "scores + top-n",
+               32: "decode: compressed rows exceed y_cap", 64: "dense dK/dV (128-row tiles)", 128: "selected forward",
+               256: "selected dQ", 512: "wait self-test"}
 
 
 def status_word(device):
     """One int32 per device that kernels OR error bits into (bounded waits that gave up)."""
     key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]
 
 
+def _raise_status(v):
+    names = ", ".join(n for b, n in STATUS_BITS.items() if v & b) or "unknown"
+    raise _lib.NsaError(f"a kernel gave up waiting on its pipeline (status bits {v:#x}: {names}); the results of the calls since "
+                        "the last check are not valid")
+
+
 def check_status(device="cuda"):
-    """Synchronises and raises if any kernel reported a pipeline time-out since the last check."""
-    dev = torch.device(device, torch.cuda.current_device()) if torch.device(device).index is None else torch.device(device)
+    """Synchronises with the device and raises NsaError if any kernel reported a pipeline time-out since the last check
+    (the word is cleared, so the next check starts fresh).  A kernel whose bounded wait ran out still returns, with rc 0
+    and garbage results: this is how a caller finds out."""
+    d = torch.device(device)
+    dev = torch.device("cuda", torch.cuda.current_device()) if d.index is None else d
     w = status_word(dev)
     v = int(w.item())
+    m = _mirror.get(dev.index)
+    if m is not None:
+        m[1] = None
     if v:
         w.zero_()
-        raise _lib.NsaError(f"a kernel gave up waiting on its tensor-core pipeline (status bits {v:#x})")
+        _raise_status(v)
+
+
+def poll_status(device):
+    """Non-blocking form used by NSACore.forward / nsa_prefill / nsa_decode: raises if the status word copied to the host at
+    the end of an EARLIER call (post_status) has arrived and is non-zero.  Never synchronises; does nothing while the
+    current stream is being captured into a CUDA graph."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    idx = torch.device(device).index
+    m = _mirror.get(torch.cuda.current_device() if idx is None else idx)
+    if m is None or m[1] is None or not m[1].query():
+        return
+    m[1] = None
+    v = int(m[0][0])
+    if v:
+        status_word(device).zero_()
+        _raise_status(v)
+
+
+def post_status(device):
+    """Enqueue a copy of the status word into pinned host memory behind the work queued so far (no synchronisation)."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    idx = torch.device(device).index
+    idx = torch.cuda.current_device() if idx is None else idx
+    m = _mirror.get(idx)
+    if m is None:
+        m = _mirror[idx] = [torch.zeros(1, dtype=torch.int32).pin_memory(), None]
+    if m[1] is not None and not m[1].query():
+        return          # the previous copy is still in flight: keep it (its host word must not be overwritten under it)
+    m[0].copy_(status_word(torch.device("cuda", idx)), non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    m[1] = ev
 
 
 def call(fn, params, ref_tensor):

@@ -44,12 +44,9 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
     if not have_delta:
         delta = torch.empty_like(lse)
     if T > 0:
-        offsets, tokens = get_bind_from_find(topk, helper=helper)
+        index = get_bind_from_find(topk, helper=helper)
         p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=do, delta=delta, dq=dq, dk=dk, dv=dv, topk=topk)
-        p.k2q_offsets, p.k2q_tokens = ptr(offsets), ptr(tokens)
-        p.k2q_stride_h = tokens.stride(0)
-        p.n_blocks_total = offsets.size(1) - 1
-        p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
+        attach_k2q(p, index, helper)
         p.accumulate_dq = int(acc_dq)
         if two_kernel_dq:
             p.phases = 2 if have_delta else 3
@@ -63,6 +60,16 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
     if async_dq:
         return dq, dk, dv, (lambda: None)
     return dq, dk, dv
+
+
+def attach_k2q(p, index, helper=NSAHelper):
+    """Point an NsaAttnParams at a key-block -> queries index built by get_bind_from_find (the tensors must stay alive
+    until the launch has been enqueued)."""
+    offsets, tokens = index[0], index[1]
+    p.k2q_offsets, p.k2q_tokens = ptr(offsets), ptr(tokens)
+    p.k2q_stride_h = tokens.stride(0)
+    p.n_blocks_total = offsets.size(1) - 1
+    p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
 
 
 class _SlcAttention(torch.autograd.Function):

@@ -22,7 +22,6 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     T, QH, D = q.shape
     KH = k.size(1)
     assert QH % KH == 0
-    assert NSAHelper.num_init_blocks >= 1 or True
     if sm_scale is None:
         sm_scale = D ** -0.5
     helper = NSAHelper

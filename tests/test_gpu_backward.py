@@ -206,21 +206,37 @@ def test_nsa_core_forward_backward(methods):
         core.cmp_v_weight.data = wv.cuda()
     qd, kd, vd, wd = [t.cuda().clone().requires_grad_(True) for t in (q, k, v, w)]
     o = core(qd, kd, vd, wd, torch.tensor(cu, dtype=torch.int32, device="cuda"))
+    topk_gpu = o.grad_fn.saved_tensors[-1].cpu()          # the selection the CUDA path made, [KH,T,16]
     (o.float() * do.cuda().float()).sum().backward()
 
     qr, kr, vr, wr = _leaf(q, k, v, w)
     wkr = wk.float().requires_grad_(True) if wk is not None else None
     wvr = wv.float().requires_grad_(True) if wv is not None else None
-    o_ref = O.nsa_forward(qr, kr, vr, wr, cu, cmp_k_method=methods[0], cmp_v_method=methods[1], cmp_k_weight=wkr,
-                          cmp_v_weight=wvr, quant="fp16_cubed")
+    # the oracle's selected branch runs on the CUDA path's own selection, so that a near-tie resolved the other way
+    # cannot move a row: every tensor is then held to a strict maximum.  The selection itself is compared below.
+    o_ref, parts = O.nsa_forward(qr, kr, vr, wr, cu, cmp_k_method=methods[0], cmp_v_method=methods[1], cmp_k_weight=wkr,
+                                 cmp_v_weight=wvr, quant="fp16_cubed", topk=topk_gpu, return_parts=True)
     (o_ref * do.float()).sum().backward()
+    T = cu[-1]
+    differing = 0
+    for b in range(len(lens)):
+        for t in range(lens[b]):
+            nv = min(16, t // 64 + 1)
+            for kh in range(KH):
+                a = set(topk_gpu[kh, cu[b] + t, :nv].tolist())
+                differing += int(a != set(parts["topk"][kh, cu[b] + t, :nv].tolist()))
+                assert len(a) == nv and all(0 <= x <= t // 64 for x in a)
+    assert differing <= max(2, KH * T // 50), differing     # learned compression rounds its rows to bf16: a few near-ties flip
 
-    def bulk(name, got, ref, frac=0.999):
-        # a flipped near-tie in the selection changes single rows; judge the bulk, bound everything
+    def bulk(name, got, ref, frac=None):
         err = (got.float().cpu() - ref.float()).abs().flatten()
         scale = max(1.0, ref.abs().max().item())
-        assert err.kthvalue(max(1, int(frac * err.numel()))).values.item() <= TOL * scale, name
         assert torch.isfinite(got).all(), name
+        if frac is None:
+            assert err.max().item() <= TOL * scale, f"{name}: max err {err.max().item():.4g} > {TOL * scale:.4g}"
+        else:   # weight gradients (sums over every compressed row of bf16-rounded terms): bulk at TOL, tail capped at 5x
+            assert err.kthvalue(max(1, int(frac * err.numel()))).values.item() <= TOL * scale, name
+            assert err.max().item() <= 5 * TOL * scale, f"{name}: max err {err.max().item():.4g}"
 
     bulk("o", o, o_ref)
     bulk("dq", qd.grad, qr.grad)

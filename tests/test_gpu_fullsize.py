@@ -8,8 +8,9 @@ the complete dq / dk / dv / dw of that step, and every gradient tensor of the CU
 Also here: size-independent properties at full size (softmax rows sum to one: with V = 1 every branch returns 1 where a
 row sees any key; rows outside the sample get exactly zero gradient).
 
-Tolerance as in test_gpu_backward.py: max abs error <= 2e-2 * max(1, max|reference|), judged on 99.9 % of the elements
-for tensors that depend on the block selection (a flipped near-tie changes single rows).
+Tolerance as in test_gpu_backward.py: max abs error <= 2e-2 * max(1, max|reference|) over EVERY element.  The oracle's
+selected branch runs on the selection the CUDA path made (read from the autograd node), so a near-tie that the two
+resolve differently cannot move a row; the selections themselves are compared as sets in test_config1_64k_sampled_rows.
 """
 import random
 
@@ -56,14 +57,22 @@ def _setup(cu, methods=("mean", "mean")):
     return flash_nsa
 
 
-def _bulk(name, got, ref, frac=0.999):
+def _bulk(name, got, ref, frac=None):
+    """frac None: strict maximum.  Otherwise (weight gradients of the learned compression, sums of bf16-rounded terms over
+    every compressed row): that quantile within the bound and the maximum within five times the bound."""
     got, ref = got.float().cpu(), ref.float()
     assert got.shape == ref.shape, (name, got.shape, ref.shape)
     assert torch.isfinite(got).all(), name
     err = (got - ref).abs().flatten()
     scale = max(1.0, ref.abs().max().item())
+    worst = err.max().item()
+    print(f"[fullsize] {name}: max err {worst:.4g}, bound {TOL * scale:.4g}")
+    if frac is None:
+        assert worst <= TOL * scale, f"{name}: max err {worst:.4g} > {TOL * scale:.4g}"
+        return
     k = max(1, int(frac * err.numel()))
     assert err.kthvalue(k).values.item() <= TOL * scale, f"{name}: {err.kthvalue(k).values.item():.4g} > {TOL * scale:.4g}"
+    assert worst <= 5 * TOL * scale, f"{name}: max err {worst:.4g} > {5 * TOL * scale:.4g}"
 
 
 def _core_case(lens, methods, seed, n_random):
@@ -88,6 +97,7 @@ def _core_case(lens, methods, seed, n_random):
     ridx = torch.tensor(rows, device="cuda")
     do[ridx] = do_rows.cuda()
     o = core(qd, kd, vd, wd, torch.tensor(cu, dtype=torch.int32, device="cuda"))
+    topk_gpu = o.grad_fn.saved_tensors[-1][:, ridx].cpu()       # the CUDA path's selection for the sampled rows
     o.backward(do)
     torch.cuda.synchronize()
 
@@ -95,13 +105,13 @@ def _core_case(lens, methods, seed, n_random):
     wkr = wk.float().requires_grad_(True) if wk is not None else None
     wvr = wv.float().requires_grad_(True) if wv is not None else None
     o_ref, parts = O.nsa_forward_rows(*leaves, cu, rows, cmp_k_method=methods[0], cmp_v_method=methods[1],
-                                      cmp_k_weight=wkr, cmp_v_weight=wvr, quant="fp16_cubed")
+                                      cmp_k_weight=wkr, cmp_v_weight=wvr, quant="fp16_cubed", topk=topk_gpu)
     (o_ref * do_rows.float()).sum().backward()
     qr, kr, vr, wr = leaves
 
-    _bulk("o[rows]", o[ridx], o_ref.detach(), frac=0.995)
-    _bulk("dq[rows]", qd.grad[ridx], qr.grad[rows], frac=0.995)
-    _bulk("dw[rows]", wd.grad[ridx], wr.grad[rows], frac=0.995)
+    _bulk("o[rows]", o[ridx], o_ref.detach())
+    _bulk("dq[rows]", qd.grad[ridx], qr.grad[rows])
+    _bulk("dw[rows]", wd.grad[ridx], wr.grad[rows])
     _bulk("dk", kd.grad, kr.grad)
     _bulk("dv", vd.grad, vr.grad)
     if wkr is not None:

@@ -72,8 +72,10 @@ def _oracle(s, L):
 
 def _bulk_ok(got, ref):
     err = (got.float().cpu() - ref).abs().flatten()
-    # a flipped near-tie of the selection moves single rows; judge the bulk and require finiteness
-    return err.kthvalue(max(1, int(0.998 * err.numel()))).values.item() <= TOL and bool(torch.isfinite(got).all())
+    # a flipped near-tie of the selection moves single rows by one low-score block: the bulk is held to TOL, every element
+    # to ten times TOL (the config-4 test below feeds the CUDA selection to the oracle and holds every element to TOL)
+    return (err.kthvalue(max(1, int(0.998 * err.numel()))).values.item() <= TOL and err.max().item() <= 10 * TOL
+            and bool(torch.isfinite(got).all()))
 
 
 @pytest.mark.parametrize("QH,KH,D", [(8, 2, 64), (16, 4, 128)])
@@ -240,3 +242,23 @@ def test_generation_loop_prefill_then_many_decode_steps():
         ref_k = O.mean_pool(seqs[b]["k"].float(), [0, lens[b]])
         got = torch.stack([cache.k.view(-1, KH, D)[cache.cmp_slot(b, j)] for j in range(Y)]).float().cpu()
         assert (got - ref_k).abs().max().item() <= 8e-3
+
+
+def test_baseline_config4_paged_decode_and_chunked_prefill():
+    """BASELINE config 4 at its full shape, exactly as the benchmark builds it (32 q heads / 8 kv heads / d = 128, page
+    256, randomly permuted page table, 64 decode sequences with contexts U[4096, 8192], and a 2048-token chunk on a
+    6144-token prefix): for EVERY decode sequence the output row, the selected blocks (as sets, near-ties by the oracle's
+    scores) and the compressed row the step writes, and for 64 sampled rows of the chunk the prefill output, the
+    selection and the pooled rows it writes, against the oracle evaluated on the un-paged sequences.  Paged = un-paged
+    and chunked = one-shot are the identities the reference checks in inference.ipynb (cells 34, 43, 50)."""
+    from bench import Config4
+    c4 = Config4(torch.device("cuda", torch.cuda.current_device()))
+    o, tk = c4.decode(return_topk=True)
+    res = c4.check_decode(o, tk)                  # all 64 sequences
+    assert res["max_err"] <= TOL
+    assert res["near_tie_rows"] <= 8, res         # of 64 x 8 rows
+    assert torch.equal(o, c4.decode())            # public entry point, same result when the step is repeated
+    res = c4.check_prefill(c4.prefill(), n_rows=64)
+    assert res["max_err"] <= TOL and res["rows"] >= 64
+    # the paged entry points reach contexts where all 16 slots are used and most blocks are NOT selected
+    assert min(c4.ctx) >= 4096 and all((L - 1) // 64 + 1 >= 64 for L in c4.ctx)

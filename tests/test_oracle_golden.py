@@ -142,3 +142,16 @@ def test_row_subset_matches_full_oracle():
     assert torch.allclose(o_rows, o_full[rows], atol=1e-10, rtol=1e-10)
     for a, b in zip(g_full, [t.grad for t in leaves2]):
         assert torch.allclose(a, b, atol=1e-9, rtol=1e-9)
+    # a selection passed in replaces the oracle's own: its own selection (unused slots as -1) reproduces the output, a
+    # different one moves only the selected branch; block scores come back per sequence
+    tk = parts["topk"].clone()
+    tk[tk == O.cdiv(700, 64)] = -1
+    o_same, p2 = O.nsa_forward_rows(q, k, v, w, cu, rows, topk=tk)
+    assert torch.equal(o_same, o_rows.detach())
+    assert [tuple(s.shape) for s in p2["scores"]] == [(KH, 11, 11), (KH, 3, 3), (KH, 3, 6)]
+    tk2 = tk.clone()
+    r699 = rows.index(699)
+    tk2[:, r699, 5] = tk2[:, r699, 4]                      # one block fewer for the row of token 699
+    o_less, _ = O.nsa_forward_rows(q, k, v, w, cu, rows, topk=tk2)
+    changed = (o_less != o_same).flatten(1).any(1)
+    assert changed.nonzero().flatten().tolist() == [r699]
