@@ -939,7 +939,9 @@ def kernel_breakdown(q, k, v, w, do, lens):
         topk, _ = slc_topk_indices(qd, ck, cmp_lse, maybe_efficient_version=True)
         slc_o, slc_lse = slc_attn_fwd(qd, kd, vd, topk)
         swa_o, swa_lse = swa_fwd(qd, kd, vd)
-        index = get_bind_from_find(topk)
+        from flash_nsa.ops.topk import backward_index_sizes
+        rr, ir = backward_index_sizes(qd.size(1) // kd.size(1), qd.size(2), qd.size(0))
+        index = get_bind_from_find(topk, range_rows=rr, item_rows=ir)
         dq = torch.empty_like(qd)
         dkf, dvf = torch.zeros(kd.shape, device=kd.device), torch.zeros(vd.shape, device=vd.device)
         dck, dcv = torch.zeros(ck.shape, device=kd.device), torch.zeros(cv.shape, device=kd.device)
@@ -966,7 +968,7 @@ def kernel_breakdown(q, k, v, w, do, lens):
             "swa_fwd": lambda: swa_fwd(qd, kd, vd),
             "combine_fwd": lambda: combine_fwd(cmp_o, slc_o, swa_o, wd),
             "combine_bwd": lambda: combine_bwd(cmp_o, slc_o, swa_o, wd, do, deltas=deltas),
-            "k2q_index": lambda: get_bind_from_find(topk),
+            "k2q_index": lambda: get_bind_from_find(topk, range_rows=rr, item_rows=ir),
             "cmp_dkdv": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 2),
             "cmp_dq": bwd_call("nsa_cmp_attn_bwd", ck, cv, cmp_o, cmp_lse, True, dck, dcv, 4),
             # dK/dV and dQ asked for together run as ONE block-major kernel (dS K added into dq by global reductions)

@@ -128,9 +128,12 @@ typedef struct NsaAttnParams {
   float* dk;         /* bwd: fp32, same rows as k; results are ADDED (atomics): zero-fill for a fresh result */
   float* dv;         /* bwd: fp32, same rows as v; idem                                                   */
   const int32_t* topk; /* selected branch: [KH,Tq,top_n] int32                                            */
-  const int32_t* k2q_offsets; /* selected bwd: [KH, n_blocks_total+1] CSR offsets from nsa_k2q_index      */
-  const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows of each block's list         */
+  const int32_t* k2q_offsets; /* selected bwd: CSR offsets from nsa_k2q_index (not read by the kernels: the items carry
+                                 their entry ranges; callers that inspect the index use them)                  */
+  const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows, cell after cell               */
   const int32_t* k2q_blk_cu;  /* selected bwd: [n_pieces+1] first table row of each piece (as in NsaK2qParams) */
+  const int32_t* k2q_items;   /* selected bwd: [KH, k2q_items_cap, 4] work items from nsa_k2q_index (item_rows > 0) */
+  const int32_t* k2q_n_items; /* selected bwd: [KH] number of items per kv head                               */
   int32_t* status;   /* optional device word: kernels OR a bit into it when a bounded wait on the tensor-core
                         pipeline gives up (NSA_ERR_TIMEOUT condition); never written on success; may be NULL     */
   int64_t q_stride_t, k_stride_t, v_stride_t, o_stride_t, do_stride_t, dq_stride_t, dk_stride_t, dv_stride_t;
@@ -142,7 +145,7 @@ typedef struct NsaAttnParams {
   int32_t accumulate_dq;   /* bwd: 1 = dq += result, 0 = dq = result                                      */
   int32_t n_q_rows;        /* bwd: total number of local query rows (= piece_cu[n_pieces])                */
   int32_t n_k_rows;        /* bwd: rows of the k / v tensors (bounds of the bulk tensor loads)            */
-  int32_t reserved1;
+  int32_t k2q_items_cap;   /* selected bwd: items per kv head that k2q_items can hold (its kv-head stride)   */
   int32_t n_blocks_total;  /* selected bwd: rows of the k2q table per kv head                             */
   int32_t phases;          /* bwd: 0 = run every kernel of the call; otherwise a mask, bit 0 = delta, bit 1 = dK/dV,
                               bit 2 = dQ (lets a profiler time the kernels of one call separately)         */
@@ -157,7 +160,9 @@ int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream);
 int nsa_swa_fwd(const NsaAttnParams* p, void* stream);
 int nsa_swa_bwd(const NsaAttnParams* p, void* stream);
 /* selected-block attention: replaces slc_attn_fwd / slc_attn_bwd, flash_nsa/ops/select_attn.py:440-701.
- * Backward: when dK/dV and dQ are both asked for (phases 0, 6 or 7) ONE block-major kernel produces them, adding its
+ * Backward: needs the key-block -> queries index WITH work items (nsa_k2q_index, item_rows > 0; range buckets are
+ * optional and only change the order of the work).  dK/dV come from one persistent block-major kernel (one CTA per SM
+ * walking the items in order); when dK/dV and dQ are both asked for (phases 0, 6 or 7) the same kernel also adds its
  * dQ tiles into dq with bf16 reductions (the reference's fuse_dqdkdv=True form, select_attn.py:148-335); with
  * accumulate_dq = 0 dq is cleared first.  The last bits of dq then depend on the order of the adds; the environment
  * variable NSA_SLC_BWD_UNFUSED=1 selects the token-major dQ kernel instead (fp32 accumulation, fixed order).        */
@@ -193,22 +198,33 @@ typedef struct NsaK2qParams {
   NsaSeqMeta meta;
   NsaHyper hp;
   const int32_t* topk; /* [KH,Tq,top_n]                                                                   */
-  int32_t* offsets;    /* out [KH, n_blocks_total+1]; also used as the histogram while building           */
+  int32_t* offsets;    /* out [KH, n_cells+1]; also used as the histogram while building                  */
   int32_t* tokens;     /* out [KH, Tq*top_n]                                                              */
-  int32_t* cursor;     /* scratch [KH, n_blocks_total] (any contents)                                     */
+  int32_t* cursor;     /* scratch [KH, n_cells] (any contents)                                            */
   const int32_t* blk_cu; /* [n_pieces+1] offsets of each piece's block rows (cdiv(len+off, block_size))    */
+  int32_t* items;      /* optional out [KH, items_cap, 4]: work items (block row, first entry, end entry, range), 16-byte
+                          aligned; written when item_rows > 0                                             */
+  int32_t* n_items;    /* optional out [KH]: items written per kv head                                    */
   int64_t Tq;
   int32_t KH;
   int32_t n_blocks_total;
+  int32_t range_rows;  /* 0: one list per (kv head, block row), n_cells = n_blocks_total.  > 0: lists are split by the
+                          range q_row / range_rows of the query row; cell = range * n_blocks_total + block row,
+                          n_cells = cdiv(Tq, range_rows) * n_blocks_total                                  */
+  int32_t item_rows;   /* > 0: also cut every cell into items of at most item_rows entries, in cell order   */
+  int32_t items_cap;   /* capacity of `items` per kv head; Tq*top_n/item_rows + min(n_cells, Tq*top_n) + 1 always suffices */
+  int32_t reserved0;
 } NsaK2qParams;
 /* replaces get_bind_from_find, flash_nsa/ops/topk.py:889-945: for every (kv head, key block) the list of local
- * query rows that selected it, as CSR (counts -> exclusive scan -> stable fill) instead of a dense table.  */
+ * query rows that selected it, as CSR (counts -> exclusive scan -> fill) instead of a dense table.  Range buckets and
+ * work items (no counterpart in the reference) order the backward's work so that concurrently running CTAs touch the
+ * q / dO / dq rows of one range, which then stay in L2.                                                    */
 int nsa_k2q_index(const NsaK2qParams* p, void* stream);
 /* No counterpart in the reference.  Same result as nsa_k2q_index, but the fill cursors live in a 1 MiB array inside
  * the library image instead of `cursor` (which is ignored), so the call needs no scratch allocation at all.
  * For hosts that cannot allocate at the point of the call: an inference server that gave all free device memory to its
  * KV-cache pool at start-up, or code between a framework's caching allocator and a region where cudaMalloc is not
- * allowed.  Limit: KH * n_blocks_total <= 262144 (e.g. 4 kv heads and 4 M tokens), larger sizes are refused with
+ * allowed.  Limit: KH * n_cells <= 262144 (without range buckets e.g. 4 kv heads and 4 M tokens), larger sizes are refused with
  * NSA_ERR_UNSUPPORTED_SHAPE.  The first call on each device looks up the array's device address (make that call
  * outside any stream capture).  All calls on a device share the array: the cursors are cleared at the start of every
  * call, and two calls whose kernels overlap on the GPU (different streams) corrupt each other.                  */

@@ -398,7 +398,5 @@ template int launch_dkdv<128, MODE_CMP>(const NsaAttnParams*, cudaStream_t, cons
 template int launch_dkdv<64, MODE_CMP>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
 template int launch_dkdv<128, MODE_SWA>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
 template int launch_dkdv<64, MODE_SWA>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
-template int launch_dkdv<128, MODE_SLC>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
-template int launch_dkdv<64, MODE_SLC>(const NsaAttnParams*, cudaStream_t, const char*, dim3, DkdvLaunch);
 
 }  // namespace nsa

@@ -1,16 +1,14 @@
-// Selected-block attention, backward.
-//   dK/dV: dkdv_kernel<D, MODE_SLC> (dense_bwd.cu) over the key-block -> queries lists.
-//   dQ:    one warp per (query token, kv head), like the forward: recompute S and P for each selected block,
-//          dP = dO V^T, dS = P*(dP - delta), dQ += dS K.  Operands come straight from global memory into MMA
-//          fragments (see slc_fwd.cu for the two fragment layouts).
+// Selected-block attention, backward: the entry point and the token-major dQ kernel for paged / unaligned callers.
+//   dK/dV (+ dQ): slc_bwd_tc_kernel (slc_bwd_tc.cu), persistent, over the work items of the key-block -> queries index.
+//   dQ alone:     slc_tma.cu when its conditions hold, otherwise the kernel below: one warp per (query token, kv head),
+//                 like the forward: recompute S and P for each selected block, dP = dO V^T, dS = P*(dP - delta),
+//                 dQ += dS K.  Operands come straight from global memory into MMA fragments (see slc_fwd.cu).
 #include <cstdlib>
 #include "nsa_common.cuh"
 
 namespace nsa {
 
-constexpr int MODE_SLC = 2;
-template <int D, int MODE>
-int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 grid, DkdvLaunch L);
+int launch_slc_bwd_tc(const NsaAttnParams* p, cudaStream_t st, const char* name, int fuse);   // slc_bwd_tc.cu
 int launch_slc_tma(const NsaAttnParams* p, cudaStream_t st, bool backward);   // slc_tma.cu
 void launch_delta(const void* o, const void* dout, float* delta, int64_t T, int H, int D, int64_t o_stride_t,
                   int64_t do_stride_t, int64_t lse_stride_t, int64_t lse_stride_h, cudaStream_t st);
@@ -176,7 +174,12 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   if (rc) return rc;
   NSA_REQUIRE(p->topk && p->lse && p->dout && p->delta && p->dq && p->dk && p->dv, NSA_ERR_BAD_ARG,
               "slc_attn_bwd: topk, lse, dout, delta, dq, dk, dv are required");
-  NSA_REQUIRE(p->k2q_offsets && p->k2q_tokens && p->k2q_blk_cu, NSA_ERR_BAD_ARG, "slc_attn_bwd: the k2q index is required");
+  NSA_REQUIRE(p->k2q_tokens && p->k2q_blk_cu, NSA_ERR_BAD_ARG, "slc_attn_bwd: the k2q index is required");
+  NSA_REQUIRE(!((p->phases ? p->phases : 7) & 2) || (p->k2q_items && p->k2q_n_items && p->k2q_items_cap > 0), NSA_ERR_BAD_ARG,
+              "slc_attn_bwd: the k2q index must carry work items (build it with item_rows > 0)");
+  NSA_REQUIRE((((uintptr_t)p->k2q_items) & 15) == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: k2q_items must be 16-byte aligned");
+  NSA_REQUIRE((((uintptr_t)p->q | (uintptr_t)p->dout) & 15) == 0 && (p->q_stride_t * 2) % 16 == 0 && (p->do_stride_t * 2) % 16 == 0,
+              NSA_ERR_BAD_ARG, "slc_attn_bwd: q and dout must be 16-byte aligned with 16-byte-multiple row strides (bulk tensor loads)");
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_bwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   NSA_REQUIRE(p->dk_stride_t % 2 == 0 && p->dv_stride_t % 2 == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: dk/dv row strides must be even");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;
@@ -200,10 +203,7 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
     }
   }
   if ((ph & 2) && p->n_blocks_total > 0) {
-    DkdvLaunch L{0, 8, p->k2q_blk_cu, fuse ? 1 : 0};
-    dim3 grid(p->n_blocks_total, L.splits, p->KH);
-    rc = (p->D == 128) ? launch_dkdv<128, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L)
-                       : launch_dkdv<64, MODE_SLC>(p, st, "slc_attn_bwd(dkdv)", grid, L);
+    rc = launch_slc_bwd_tc(p, st, "slc_attn_bwd(dkdv)", fuse ? 1 : 0);
     if (rc) return rc;
   }
   if (!(ph & 4) || fuse) return check_launch("slc_attn_bwd");

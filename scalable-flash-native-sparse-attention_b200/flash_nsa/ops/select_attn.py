@@ -3,7 +3,7 @@ import torch
 
 from ..utils import NSAHelper
 from ._common import attn_params, call, is_cp, ptr
-from .topk import get_bind_from_find
+from .topk import backward_index_sizes, get_bind_from_find
 
 
 def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
@@ -21,13 +21,14 @@ def slc_attn_fwd(q, k, v, topk, sm_scale=None, o=None, helper=NSAHelper):
 
 def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=None, fuse_dqdkdv=False,
                  dkdv_dtype=torch.float, dkdv_repeat=True, async_dq=False, helper=NSAHelper, delta=None,
-                 accumulate_dq=None, two_kernel_dq=False):
+                 accumulate_dq=None, two_kernel_dq=False, range_rows=None, item_rows=None):
     """-> (dq, dk, dv).  Given `dq` (bf16) / `dk`,`dv` (fp32 [tokens,kh,d]) the results are added into them;
     otherwise dq is new and dk/dv come back in k's dtype.  dK/dV and dQ come from ONE block-major kernel whatever
     `fuse_dqdkdv` says (the reference's fuse_dqdkdv=True form, flash_nsa/ops/select_attn.py:148-335,646): per key block and
     query tile it adds dS K into dq with bf16 reductions, so the last bits of dq depend on the order of those adds.
     `two_kernel_dq=True` (not in the reference) runs the block-major dK/dV kernel and then the token-major dQ kernel, which
-    accumulates a token's dq in fp32 in a fixed order."""
+    accumulates a token's dq in fp32 in a fixed order.  `range_rows` / `item_rows` override the sizes of the key-block ->
+    queries index (default: backward_index_sizes); they change the order of the work, not the result."""
     T, QH, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
@@ -44,7 +45,10 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
     if not have_delta:
         delta = torch.empty_like(lse)
     if T > 0:
-        index = get_bind_from_find(topk, helper=helper)
+        auto_r, auto_i = backward_index_sizes(QH // k.size(1), D, T)
+        range_rows = auto_r if range_rows is None else range_rows
+        item_rows = auto_i if item_rows is None else item_rows
+        index = get_bind_from_find(topk, helper=helper, range_rows=range_rows, item_rows=item_rows)
         p = attn_params(q, k, v, helper, sm_scale, o=o, lse=lse, dout=do, delta=delta, dq=dq, dk=dk, dv=dv, topk=topk)
         attach_k2q(p, index, helper)
         p.accumulate_dq = int(acc_dq)
@@ -66,10 +70,12 @@ def attach_k2q(p, index, helper=NSAHelper):
     """Point an NsaAttnParams at a key-block -> queries index built by get_bind_from_find (the tensors must stay alive
     until the launch has been enqueued)."""
     offsets, tokens = index[0], index[1]
+    assert getattr(index, "items", None) is not None, "the backward needs an index built with item_rows > 0"
     p.k2q_offsets, p.k2q_tokens = ptr(offsets), ptr(tokens)
     p.k2q_stride_h = tokens.stride(0)
-    p.n_blocks_total = offsets.size(1) - 1
+    p.n_blocks_total = helper.cp_k_len if is_cp(helper) else helper.k_len
     p.k2q_blk_cu = ptr(helper.cp_k_cu_seqlens if is_cp(helper) else helper.k_cu_seqlens)
+    p.k2q_items, p.k2q_n_items, p.k2q_items_cap = ptr(index.items), ptr(index.n_items), index.items.size(1)
 
 
 class _SlcAttention(torch.autograd.Function):

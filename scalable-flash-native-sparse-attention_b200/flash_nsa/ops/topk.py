@@ -57,26 +57,58 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     return topk, probs
 
 
+class K2qIndex(tuple):
+    """(offsets, tokens) of the key-block -> queries index, plus what the backward kernel needs: `items` [kh, cap, 4] =
+    (block row, first entry, end entry, range) and `n_items` [kh] when work items were asked for, `range_rows` and
+    `n_ranges`.  Unpacks as `offsets, tokens = index` like the plain form."""
+
+    def __new__(cls, offsets, tokens, items=None, n_items=None, range_rows=0, n_ranges=1, cursor=None):
+        self = super().__new__(cls, (offsets, tokens))
+        self.offsets, self.tokens, self.items, self.n_items = offsets, tokens, items, n_items
+        self.range_rows, self.n_ranges = range_rows, n_ranges
+        self._cursor = cursor      # scratch of the build: kept until the index goes away (the build is asynchronous)
+        return self
+
+
+def backward_index_sizes(G, D, rows):
+    """(range_rows, item_rows) that slc_attn_bwd asks for: a range holds about 16 MiB of q (so q + dO + dq of the rows that
+    the running CTAs touch stay in L2), an item holds at most 32 query tiles of 128 / G tokens."""
+    per_row = G * D * 2
+    range_rows = 1 << max(10, ((16 << 20) // per_row).bit_length() - 1)
+    return (range_rows if rows > range_rows else 0), 32 * max(128 // G, 1)
+
+
 @torch.no_grad()
-def get_bind_from_find(topk, helper=NSAHelper):
-    """topk [kh,t,top_n] -> (offsets [kh, blocks+1], tokens [kh, t*top_n]): for every (kv head, key block) the
-    ascending list of local query rows that selected it, `tokens[h, offsets[h,b]:offsets[h,b+1]]`.
-    Block rows are laid out per piece (sequence, or shard piece under context parallelism) with
-    k_cu_seqlens / cp_k_cu_seqlens."""
+def get_bind_from_find(topk, helper=NSAHelper, range_rows=0, item_rows=0):
+    """topk [kh,t,top_n] -> K2qIndex (offsets [kh, cells+1], tokens [kh, t*top_n]): for every (kv head, key block) the
+    list of local query rows that selected it, `tokens[h, offsets[h,b]:offsets[h,b+1]]` (order inside a list not fixed).
+    Block rows are laid out per piece (sequence, or shard piece under context parallelism) with k_cu_seqlens /
+    cp_k_cu_seqlens.  `range_rows` > 0 splits every list by the range `row // range_rows` of the query row (cell =
+    range * blocks + block row, range-major); `item_rows` > 0 also returns the work items of the backward kernel."""
     KH, T, top_n = topk.shape
     cp = is_cp(helper)
     blk_cu = helper.cp_k_cu_seqlens if cp else helper.k_cu_seqlens
     n_blocks = helper.cp_k_len if cp else helper.k_len
-    offsets = torch.empty(KH, n_blocks + 1, dtype=torch.int32, device=topk.device)
-    tokens = torch.empty(KH, max(T * top_n, 1), dtype=torch.int32, device=topk.device)
-    cursor = torch.empty(KH, max(n_blocks, 1), dtype=torch.int32, device=topk.device)
+    n_ranges = cdiv(T, range_rows) if range_rows > 0 else 1
+    n_cells = n_ranges * n_blocks
+    dev = topk.device
+    offsets = torch.empty(KH, n_cells + 1, dtype=torch.int32, device=dev)
+    tokens = torch.empty(KH, max(T * top_n, 1), dtype=torch.int32, device=dev)
+    cursor = torch.empty(KH, max(n_cells, 1), dtype=torch.int32, device=dev)
     p = S["NsaK2qParams"]()
     p.meta, p.hp = seq_meta(helper), hyper()
     p.hp.top_n = top_n
     p.topk, p.offsets, p.tokens, p.cursor, p.blk_cu = ptr(topk), ptr(offsets), ptr(tokens), ptr(cursor), ptr(blk_cu)
     p.Tq, p.KH, p.n_blocks_total = T, KH, n_blocks
+    p.range_rows, p.item_rows = range_rows, item_rows
+    items = n_items = None
+    if item_rows > 0:
+        cap = T * top_n // item_rows + min(n_cells, T * top_n) + 1
+        items = torch.empty(KH, cap, 4, dtype=torch.int32, device=dev)
+        n_items = torch.zeros(KH, dtype=torch.int32, device=dev)
+        p.items, p.n_items, p.items_cap = ptr(items), ptr(n_items), cap
     call("nsa_k2q_index", p, topk)
-    return offsets, tokens
+    return K2qIndex(offsets, tokens, items, n_items, range_rows, n_ranges, cursor)
 
 
 @torch.no_grad()

@@ -158,6 +158,32 @@ def test_selected_backward_one_kernel_equals_two_kernels():
         assert (dq0.float() - (outs[1][0].float() - 0.25)).abs().max().item() <= 2e-2 * max(1.0, dq0.float().abs().max().item())
 
 
+@pytest.mark.parametrize("range_rows,item_rows", [(128, 24), (512, 8), (0, 1000), (64, 3)])
+def test_selected_backward_does_not_depend_on_how_the_work_is_cut(range_rows, item_rows):
+    """The persistent backward kernel walks work items (key block x slice of its query list) range by range; however the
+    lists are cut into ranges and items (many small items, items that end inside a query tile, a single range), dk / dv
+    agree up to the order of their atomics and dq within the bf16 rounding of its adds, and all match the oracle."""
+    lens, QH, KH, D = [900, 333, 70], 32, 2, 128
+    q, k, v, w, do, cu = _mk(lens, QH, KH, D, seed=67)
+    _setup(cu)
+    from flash_nsa.ops.select_attn import slc_attn_fwd, slc_attn_bwd
+    ckf = O.mean_pool(k.float(), cu)
+    _, l0 = O.cmp_attn(q.float(), ckf, O.mean_pool(v.float(), cu), cu)
+    topk = O.topk_select(O.slc_scores(q.float(), ckf, l0, cu), cu)
+    qr, kr, vr = _leaf(q, k, v)
+    o_ref, _ = O.slc_attn(qr, kr, vr, topk, cu)
+    (o_ref * do.float()).sum().backward()
+    qd, kd, vd, dod, tk = q.cuda(), k.cuda(), v.cuda(), do.cuda(), topk.cuda()
+    o, lse = slc_attn_fwd(qd, kd, vd, tk)
+    dq, dk, dv = slc_attn_bwd(qd, kd, vd, tk, o, lse, dod, range_rows=range_rows, item_rows=item_rows)
+    _check("dq", dq, qr.grad)
+    _check("dk", dk, kr.grad)
+    _check("dv", dv, vr.grad)
+    dq2, dk2, dv2 = slc_attn_bwd(qd, kd, vd, tk, o, lse, dod)
+    assert (dk.float() - dk2.float()).abs().max().item() <= 2e-2 * max(1.0, dk2.float().abs().max().item())
+    assert (dq.float() - dq2.float()).abs().max().item() <= 2e-2 * max(1.0, dq2.float().abs().max().item())
+
+
 def test_k2q_index_is_the_transpose():
     lens = [700, 130]
     q, k, v, w, do, cu = _mk(lens, 4, 2, 64, seed=5)
@@ -185,6 +211,50 @@ def test_k2q_index_is_the_transpose():
                 want = {k_cu[b] + int(x) for x in topk[kh, cu[b] + t, :nv].tolist()}
                 assert rebuilt.get(cu[b] + t, set()) == want
         assert int(offsets[kh, -1]) == sum(min(16, t // 64 + 1) for L in lens for t in range(L))
+
+
+def test_k2q_index_with_range_buckets_and_work_items():
+    """The form of the index the backward kernel walks: lists split by the range of the query row (cell = range * blocks +
+    block row, range-major) and cut into work items of bounded size.  Checked: every cell holds exactly the rows of its
+    range that selected its block; the items tile every non-empty cell exactly once, in cell order, none longer than
+    item_rows; the plain index is the union over ranges."""
+    lens = [700, 130, 333]
+    q, k, v, w, do, cu = _mk(lens, 4, 2, 64, seed=6)
+    _setup(cu)
+    from flash_nsa import NSAHelper
+    from flash_nsa.ops import get_bind_from_find
+    ckf = O.mean_pool(k.float(), cu)
+    _, l0 = O.cmp_attn(q.float(), ckf, O.mean_pool(v.float(), cu), cu)
+    topk = O.topk_select(O.slc_scores(q.float(), ckf, l0, cu), cu)
+    R, P = 256, 40
+    plain = get_bind_from_find(topk.cuda())
+    idx = get_bind_from_find(topk.cuda(), range_rows=R, item_rows=P)
+    torch.cuda.synchronize()
+    T, KH = cu[-1], 2
+    n_blocks = NSAHelper.k_len
+    assert idx.n_ranges == -(-T // R) and idx.offsets.shape == (KH, idx.n_ranges * n_blocks + 1)
+    off, tok, items, n_items = idx.offsets.cpu(), idx.tokens.cpu(), idx.items.cpu(), idx.n_items.cpu()
+    p_off, p_tok = plain.offsets.cpu(), plain.tokens.cpu()
+    for kh in range(KH):
+        union = [[] for _ in range(n_blocks)]
+        for cell in range(idx.n_ranges * n_blocks):
+            r, row = divmod(cell, n_blocks)
+            rows = tok[kh, off[kh, cell]:off[kh, cell + 1]].tolist()
+            assert all(r * R <= x < (r + 1) * R for x in rows), (kh, cell)
+            union[row] += rows
+        for row in range(n_blocks):
+            assert sorted(union[row]) == sorted(p_tok[kh, p_off[kh, row]:p_off[kh, row + 1]].tolist()), (kh, row)
+        # the items: consecutive slices that cover [0, total) exactly, cell after cell
+        pos, cell = 0, 0
+        for i in range(int(n_items[kh])):
+            row, lo, hi, r = items[kh, i].tolist()
+            assert lo == pos and lo < hi <= lo + P
+            c = r * n_blocks + row
+            assert c >= cell and off[kh, c] <= lo and hi <= off[kh, c + 1]
+            cell, pos = c, hi
+        assert pos == int(off[kh, -1]) == int(p_off[kh, -1])
+        n_expected = sum(-(-int(off[kh, c + 1] - off[kh, c]) // P) for c in range(idx.n_ranges * n_blocks))
+        assert int(n_items[kh]) == n_expected
 
 
 @pytest.mark.parametrize("methods", [("mean", "mean"), ("linear", "sigmoid-mul"), ("swiglu", "mean")])
