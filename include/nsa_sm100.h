@@ -133,7 +133,9 @@ typedef struct NsaAttnParams {
   const int32_t* k2q_tokens;  /* selected bwd: [KH, Tq*top_n] local query rows, cell after cell               */
   const int32_t* k2q_blk_cu;  /* selected bwd: [n_pieces+1] first table row of each piece (as in NsaK2qParams) */
   const int32_t* k2q_items;   /* selected bwd: [KH, k2q_items_cap, 4] work items from nsa_k2q_index (item_rows > 0) */
-  const int32_t* k2q_n_items; /* selected bwd: [KH] number of items per kv head                               */
+  int32_t* k2q_n_items;       /* selected bwd: [KH + 2]: items per kv head, then two ticket counters of the backward
+                                 kernel (zero between launches: nsa_k2q_index clears them, the kernel restores them),
+                                 so two backward launches on one index must not overlap on the GPU              */
   int32_t* status;   /* optional device word: kernels OR a bit into it when a bounded wait on the tensor-core
                         pipeline gives up (NSA_ERR_TIMEOUT condition); never written on success; may be NULL     */
   int64_t q_stride_t, k_stride_t, v_stride_t, o_stride_t, do_stride_t, dq_stride_t, dk_stride_t, dv_stride_t;
@@ -204,7 +206,8 @@ typedef struct NsaK2qParams {
   const int32_t* blk_cu; /* [n_pieces+1] offsets of each piece's block rows (cdiv(len+off, block_size))    */
   int32_t* items;      /* optional out [KH, items_cap, 4]: work items (block row, first entry, end entry, range), 16-byte
                           aligned; written when item_rows > 0                                             */
-  int32_t* n_items;    /* optional out [KH]: items written per kv head                                    */
+  int32_t* n_items;    /* optional out [KH + 2]: items written per kv head; the two extra words are cleared (they are
+                          the ticket counters of nsa_slc_attn_bwd)                                       */
   int64_t Tq;
   int32_t KH;
   int32_t n_blocks_total;

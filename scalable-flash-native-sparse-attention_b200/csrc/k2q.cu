@@ -54,6 +54,7 @@ __global__ void k2q_zero_kernel(NsaK2qParams p) {
   int64_t n_off = (int64_t)p.KH * (nc + 1), n_cur = (int64_t)p.KH * nc;
   if (i < n_off) p.offsets[i] = 0;
   if (i < n_cur) p.cursor[i] = 0;
+  if (i < 2 && p.n_items) p.n_items[p.KH + i] = 0;   // ticket counters of the backward kernel
 }
 
 // Threads are slot-major (thread i = slot i / Tq of token i % Tq), so a warp holds one slot of 32 consecutive tokens: the

@@ -2,11 +2,13 @@
 // items of the key-block -> queries index (k2q.cu) in order.
 //
 // An item is (key block, slice of the list of query rows that selected it).  The index lists its items range-major
-// (all items whose query rows lie in local rows [r*R, (r+1)*R), then the next range), and CTA c takes items c, c+grid,
-// c+2*grid, ... of that list, so at any moment all CTAs gather q / dO rows of, and reduce into dq rows of, ONE range of
-// R rows: with R sized to a third of L2 those rows are fetched from DRAM once per range instead of once per selected
-// block (16 times).  The same kernel built block-major with each block's whole list in one CTA moved 11x the algorithmic
-// bytes through DRAM and ran at 0.63 of the HBM rate, not at its tensor rate.
+// (all items whose query rows lie in local rows [r*R, (r+1)*R), then the next range), and the CTAs take them off that list
+// one at a time through a global ticket counter, so at any moment the items in flight are neighbours in the list and all
+// CTAs gather q / dO rows of, and reduce into dq rows of, ONE range of R rows: with R sized to a third of L2 those rows are
+// fetched from DRAM once per range instead of once per selected block (16 times).  (Items handed out round-robin drift
+// apart, because item sizes differ by 30x: after a few ranges the CTAs were spread over two or three ranges and 72 % of the
+// dq reductions still missed L2.)  The last CTA to finish puts the ticket counter back to zero for the next launch.
+// The same kernel built block-major with each block's whole list in one CTA moved 11x the algorithmic bytes through DRAM.
 //
 // Per item, as in dkdv_tc.cu: the 64-row K/V tile of the block sits in shared memory; query rows come in tiles of
 // 128 = (128/G tokens) x (G heads of the kv head) gathered by six TMA producer warps (one (64 d) x (G heads) x (1 token)
@@ -21,7 +23,7 @@
 //
 // Barriers keep counting across items: every barrier completes the same number of phases per item (one per round and
 // group; the dQ hand-over barrier one per tile), so a role derives the parity from the number of rounds done so far.
-// One CTA-wide barrier per item separates the items (after the next K/V tile has been loaded).
+// Two CTA-wide barriers per item: one after the ticket has been drawn, one after the item's K/V tile has been loaded.
 #include "tma.cuh"
 
 namespace nsa {
@@ -37,7 +39,7 @@ __device__ __forceinline__ int find_le_slc(const int32_t* cu, int n, int x) {
 
 template <int D>
 __global__ void __launch_bounds__(480, 1)
-    slc_bwd_tc_kernel(NsaAttnParams p, int fuse_dq, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
+    slc_bwd_tc_kernel(const NsaAttnParams p, int fuse_dq, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
                       const __grid_constant__ CUtensorMap tmdq) {
   using namespace tc;
   constexpr int BK = 64, BQ = 128;
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(480, 1)
   const uint32_t bars = sS0 + 2 * P_BYTES;
   // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2], dq_read[2]; then the tensor-memory address slot
   auto bar = [&](int which, int wg) { return bars + (which * 2 + wg) * 8; };
-  const uint32_t tm_slot = bars + 80;
+  const uint32_t tm_slot = bars + 80, ticket_slot = bars + 96;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -92,16 +94,30 @@ __global__ void __launch_bounds__(480, 1)
   bool timed_out = false;
   int jb = 0;   // rounds completed by this CTA in earlier items: the same number in every thread
 
-  int items_before = 0;
-  for (int kh = 0; kh < p.KH; ++kh) {
-    const int n_items = min(__ldg(p.k2q_n_items + kh), p.k2q_items_cap);
-    const int4* items = reinterpret_cast<const int4*>(p.k2q_items) + (int64_t)kh * p.k2q_items_cap;
-    const int32_t* list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
-    // item g of the concatenation over kv heads goes to CTA g % gridDim.x
-    int first = (int)(((int64_t)blockIdx.x - items_before) % (int64_t)gridDim.x);
-    if (first < 0) first += gridDim.x;
-    items_before += n_items;
-    for (int item_i = first; item_i < n_items; item_i += gridDim.x) {
+  int total_items = 0;
+  for (int h = 0; h < p.KH; ++h) total_items += min(__ldg(p.k2q_n_items + h), p.k2q_items_cap);
+  int32_t* ticket = p.k2q_n_items + p.KH;   // [0] next item to hand out, [1] CTAs that have finished
+
+  {
+    for (;;) {
+      // ---- next item: one ticket per CTA (every thread has finished the previous item when it passes this barrier)
+      if (tid == 0) {
+        const int g = atomicAdd(ticket, 1);
+        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ticket_slot), "r"(g) : "memory");
+      }
+      __syncthreads();
+      int g;
+      asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(g) : "r"(ticket_slot));
+      if (g >= total_items) break;
+      int kh = 0, item_i = g;
+      for (;;) {   // item g of the concatenation over kv heads
+        const int n = min(__ldg(p.k2q_n_items + kh), p.k2q_items_cap);
+        if (item_i < n) break;
+        item_i -= n;
+        ++kh;
+      }
+      const int4* items = reinterpret_cast<const int4*>(p.k2q_items) + (int64_t)kh * p.k2q_items_cap;
+      const int32_t* list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
       const int4 item = __ldg(items + item_i);
       const int row = item.x, r_lo = item.y, r_hi = item.z;
       const int b = find_le_slc(p.k2q_blk_cu, p.meta.n_pieces, row);
@@ -109,7 +125,10 @@ __global__ void __launch_bounds__(480, 1)
       const int k0 = (row - p.k2q_blk_cu[b]) * BK;
       const int64_t kv_bos = pc.x_bos;
       const int kv_rows = min(BK, pc.x_len - k0);
-      if (kv_rows <= 0 || r_hi <= r_lo) continue;   // (uniform over the CTA)
+      if (kv_rows <= 0 || r_hi <= r_lo) {   // not produced by nsa_k2q_index; uniform over the CTA
+        __syncthreads();
+        continue;
+      }
       const int n_it = (r_hi - r_lo + TOKQ - 1) / TOKQ;
       const int n_round = (n_it + 1) / 2;
 
@@ -205,6 +224,14 @@ __global__ void __launch_bounds__(480, 1)
           for (int u = 0; u < 4; ++u)
             if (lane + NP * u < n_box) issue(lane + NP * u, rows[u]);
           for (int bx = lane + 4 * NP; bx < n_box; bx += NP) issue(bx, row_of(bx));   // only when G = 1 and D = 128
+          // the boxes of this group's NEXT tile: asked into L2 now, fetched into shared memory when the buffers are free
+          if (it + 2 < n_it) {
+            const int tok2 = tok0 + 2 * TOKQ;
+            for (int bx = lane; bx < n_box; bx += NP) {
+              const int n = bx / (SLABS * 2), rest = bx - n * (SLABS * 2), sl = rest >> 1, which = rest & 1;
+              if (tok2 + n < r_hi) tma::prefetch_3d(which ? &tmo : &tmq, sl * 64, kh * G, __ldg(list + tok2 + n));
+            }
+          }
         }
       } else {
         // ================================================= two warp groups, one query tile each per round
@@ -252,23 +279,37 @@ __global__ void __launch_bounds__(480, 1)
           }
         };
 
+        // my row of a round: its tensor row two rounds ahead, its lse / delta one round ahead, so that neither load is waited for
+        auto row_at = [&](int j) {
+          const int tok = r_lo + (2 * j + wg) * TOKQ + my_n;
+          return (my_n < TOKQ && j < n_round && tok < r_hi) ? __ldg(list + tok) : -1;
+        };
+        int qrow_cur = row_at(0), qrow_nxt = row_at(1);
+        float lse_nxt = 0.f, dl_nxt = 0.f;
+        if (qrow_cur >= 0) {
+          const int64_t a = (int64_t)qrow_cur * p.lse_stride_t + (int64_t)(kh * G + my_g) * p.lse_stride_h;
+          lse_nxt = p.lse[a];
+          dl_nxt = p.delta[a];
+        }
         for (int j = 0; j < n_round; ++j) {
           const int jj = jb + j;
           const int it = 2 * j + wg;
           const int tok0 = r_lo + it * TOKQ;  // first list position of my tile
+          // my own row: lse, delta, absolute position (loaded during the previous round)
+          const bool row_ok = qrow_cur >= 0;
+          const float lse = lse_nxt, dl = dl_nxt;
+          const int ta = row_ok ? pc.off + (qrow_cur - pc.q_start) : -1;
+          qrow_cur = qrow_nxt;
+          lse_nxt = 0.f;
+          dl_nxt = 0.f;
+          if (qrow_cur >= 0) {
+            const int64_t a = (int64_t)qrow_cur * p.lse_stride_t + (int64_t)(kh * G + my_g) * p.lse_stride_h;
+            lse_nxt = p.lse[a];
+            dl_nxt = p.delta[a];
+          }
+          qrow_nxt = row_at(j + 2);
           if (j > 0 && !mbar_wait(bar(3, wg), (jj - 1) & 1, &budget)) timed_out = true;  // my buffers are free again
           if (fuse && j > 0) add_dq(red_row);
-          // my own row: lse, delta, absolute position
-          const bool row_ok = (my_n < TOKQ) && (tok0 + my_n < r_hi);
-          float lse = 0.f, dl = 0.f;
-          int ta = -1;
-          if (row_ok) {
-            const int64_t q_row = (int64_t)__ldg(list + tok0 + my_n);
-            const int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + my_g) * p.lse_stride_h;
-            lse = p.lse[a];
-            dl = p.delta[a];
-            ta = pc.off + (int)(q_row - pc.q_start);
-          }
           if (fuse && t < n_box) {
             const int tok = tok0 + t % TOKQ;
             red_row = (tok < r_hi) ? __ldg(list + tok) : -1;
@@ -352,6 +393,14 @@ __global__ void __launch_bounds__(480, 1)
     }
   }
   if (warp < 8 && fuse && (tid & 127) < TOKQ * SLABS) tma::bulk_wait_all();   // the reductions have been written
+  if (tid == 0) {   // the last CTA to get here leaves both counters at zero for the next launch
+    __threadfence();
+    if (atomicAdd(ticket + 1, 1) == (int)gridDim.x - 1) {
+      ticket[0] = 0;
+      ticket[1] = 0;
+      __threadfence();
+    }
+  }
   if (timed_out && p.status) atomicOr(p.status, 2);
   fence_before_sync();
   __syncthreads();

@@ -13,6 +13,12 @@ __device__ __forceinline__ void load_3d(uint32_t dst, const CUtensorMap* map, in
       "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
 }
+// ask for a box to be brought into L2 (no shared-memory destination, no completion to wait for)
+__device__ __forceinline__ void prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0),
+               "r"(c1), "r"(c2)
+               : "memory");
+}
 // add a box of shared memory into the tensor (element-wise, in the tensor's type); completion is tracked by the
 // thread's bulk async-group.  Coordinates must not be negative, and c0 * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void reduce_add_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {

@@ -105,7 +105,7 @@ def get_bind_from_find(topk, helper=NSAHelper, range_rows=0, item_rows=0):
     if item_rows > 0:
         cap = T * top_n // item_rows + min(n_cells, T * top_n) + 1
         items = torch.empty(KH, cap, 4, dtype=torch.int32, device=dev)
-        n_items = torch.zeros(KH, dtype=torch.int32, device=dev)
+        n_items = torch.zeros(KH + 2, dtype=torch.int32, device=dev)   # + the backward kernel's two ticket counters
         p.items, p.n_items, p.items_cap = ptr(items), ptr(n_items), cap
     call("nsa_k2q_index", p, topk)
     return K2qIndex(offsets, tokens, items, n_items, range_rows, n_ranges, cursor)

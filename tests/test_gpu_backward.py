@@ -255,6 +255,7 @@ def test_k2q_index_with_range_buckets_and_work_items():
         assert pos == int(off[kh, -1]) == int(p_off[kh, -1])
         n_expected = sum(-(-int(off[kh, c + 1] - off[kh, c]) // P) for c in range(idx.n_ranges * n_blocks))
         assert int(n_items[kh]) == n_expected
+    assert n_items[KH:].tolist() == [0, 0]          # the backward kernel's ticket counters start at zero
 
 
 @pytest.mark.parametrize("methods", [("mean", "mean"), ("linear", "sigmoid-mul"), ("swiglu", "mean")])
