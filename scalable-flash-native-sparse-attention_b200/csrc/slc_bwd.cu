@@ -178,8 +178,10 @@ extern "C" int nsa_slc_attn_bwd(const NsaAttnParams* p, void* stream) {
   NSA_REQUIRE(!((p->phases ? p->phases : 7) & 2) || (p->k2q_items && p->k2q_n_items && p->k2q_items_cap > 0), NSA_ERR_BAD_ARG,
               "slc_attn_bwd: the k2q index must carry work items (build it with item_rows > 0)");
   NSA_REQUIRE((((uintptr_t)p->k2q_items) & 15) == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: k2q_items must be 16-byte aligned");
-  NSA_REQUIRE((((uintptr_t)p->q | (uintptr_t)p->dout) & 15) == 0 && (p->q_stride_t * 2) % 16 == 0 && (p->do_stride_t * 2) % 16 == 0,
-              NSA_ERR_BAD_ARG, "slc_attn_bwd: q and dout must be 16-byte aligned with 16-byte-multiple row strides (bulk tensor loads)");
+  NSA_REQUIRE((((uintptr_t)p->q | (uintptr_t)p->dout | (uintptr_t)p->k | (uintptr_t)p->v) & 15) == 0 && (p->q_stride_t * 2) % 16 == 0 &&
+                  (p->do_stride_t * 2) % 16 == 0 && (p->k_stride_t * 2) % 16 == 0 && (p->v_stride_t * 2) % 16 == 0,
+              NSA_ERR_BAD_ARG, "slc_attn_bwd: q, dout, k, v must be 16-byte aligned with 16-byte-multiple row strides (bulk tensor loads)");
+  NSA_REQUIRE(!(p->meta.kv_table), NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_bwd: paged K/V is an inference layout; the backward takes contiguous K/V");
   NSA_REQUIRE(p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_attn_bwd: block_size=%d (only 64 is implemented)", p->hp.block_size);
   NSA_REQUIRE(p->dk_stride_t % 2 == 0 && p->dv_stride_t % 2 == 0, NSA_ERR_BAD_ARG, "slc_attn_bwd: dk/dv row strides must be even");
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0 || p->n_q_rows <= 0) return NSA_OK;

@@ -21,9 +21,14 @@
 // one bulk tensor reduction per (token, 64-column slab).  At the end of an item lane j of the dV^T / dK^T accumulators
 // holds column j of dV / dK: 64 coalesced fp32 atomics per thread.
 //
-// Barriers keep counting across items: every barrier completes the same number of phases per item (one per round and
-// group; the dQ hand-over barrier one per tile), so a role derives the parity from the number of rounds done so far.
-// Two CTA-wide barriers per item: one after the ticket has been drawn, one after the item's K/V tile has been loaded.
+// Items overlap.  The producer warps own the schedule: their leader draws the ticket of item n+1 as soon as the last loads
+// of item n are issued and publishes it through a ticket barrier; once the last MMAs of item n have completed they load
+// the K/V tile (TMA) and the first two query tiles of item n+1 while the compute groups still add the last dQ tile and
+// flush dV / dK of item n; the first S / dP products of item n+1 run under that flush as well, only its first dV / dK
+// products wait until the accumulators have been read (acc_free).  There is no CTA-wide barrier between items.
+// Barriers keep counting across items: every pipeline barrier completes the same number of phases per item (one per
+// round and group; the dQ hand-over barrier one per tile; ticket, K/V and accumulator barriers one per item), so a role
+// derives every parity from the number of rounds and items it has seen.
 #include "tma.cuh"
 
 namespace nsa {
@@ -40,7 +45,8 @@ __device__ __forceinline__ int find_le_slc(const int32_t* cu, int n, int x) {
 template <int D>
 __global__ void __launch_bounds__(480, 1)
     slc_bwd_tc_kernel(const NsaAttnParams p, int fuse_dq, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
-                      const __grid_constant__ CUtensorMap tmdq) {
+                      const __grid_constant__ CUtensorMap tmdq, const __grid_constant__ CUtensorMap tmk,
+                      const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
   constexpr int BK = 64, BQ = 128;
   constexpr uint32_t KV_BYTES = BK * D * 2, Q_BYTES = BQ * D * 2, P_BYTES = BQ * BK * 2;
@@ -59,9 +65,12 @@ __global__ void __launch_bounds__(480, 1)
   const uint32_t sP0 = sO0 + 2 * Q_BYTES;             // [2 groups]
   const uint32_t sS0 = sP0 + 2 * P_BYTES;             // [2 groups]
   const uint32_t bars = sS0 + 2 * P_BYTES;
-  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2], dq_read[2]; then the tensor-memory address slot
+  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2], dq_read[2], ticket_full[2], then kv_full, acc_free; then the
+  // tensor-memory address slot and the two ticket slots.  Item n uses ticket barrier / slot n & 1 (phase n >> 1): the leader
+  // can be one item ahead of the slowest thread, and with one barrier a thread two phases behind would wait for ever.
   auto bar = [&](int which, int wg) { return bars + (which * 2 + wg) * 8; };
-  const uint32_t tm_slot = bars + 80, ticket_slot = bars + 96;
+  const uint32_t kv_full = bars + 96, acc_free = bars + 104;
+  const uint32_t tm_slot = bars + 112, ticket_slot = bars + 120;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -77,6 +86,10 @@ __global__ void __launch_bounds__(480, 1)
       mbar_init(bar(3, w), 1);
       mbar_init(bar(4, w), 128);
     }
+    mbar_init(bar(5, 0), 1);
+    mbar_init(bar(5, 1), 1);
+    mbar_init(kv_full, 1);
+    mbar_init(acc_free, 256);
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(tm_slot, TM_COLS);
@@ -98,57 +111,48 @@ __global__ void __launch_bounds__(480, 1)
   for (int h = 0; h < p.KH; ++h) total_items += min(__ldg(p.k2q_n_items + h), p.k2q_items_cap);
   int32_t* ticket = p.k2q_n_items + p.KH;   // [0] next item to hand out, [1] CTAs that have finished
 
+  const bool leader = tid == 288;   // lane 0 of the first producer warp draws the tickets
+  if (leader) {
+    const int g0 = atomicAdd(ticket, 1);
+    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ticket_slot), "r"(g0) : "memory");
+    mbar_arrive(bar(5, 0));
+  }
+
   {
-    for (;;) {
-      // ---- next item: one ticket per CTA (every thread has finished the previous item when it passes this barrier)
-      if (tid == 0) {
-        const int g = atomicAdd(ticket, 1);
-        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ticket_slot), "r"(g) : "memory");
+    for (int n = 0;; ++n) {
+      // ---- item n of this CTA: its ticket was published by the producer leader (release / acquire through the barrier)
+      if (!mbar_wait(bar(5, n & 1), (n >> 1) & 1, &budget)) {   // no ticket: give up (the slot would hold a stale one)
+        timed_out = true;
+        break;
       }
-      __syncthreads();
       int g;
-      asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(g) : "r"(ticket_slot));
-      if (g >= total_items) break;
+      asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(g) : "r"(ticket_slot + 4 * (n & 1)));
+      if (g >= total_items || g < 0) break;
+      if (warp >= 9) named_barrier(4, 192);   // the producer warps stay within one item of their leader
       int kh = 0, item_i = g;
       for (;;) {   // item g of the concatenation over kv heads
-        const int n = min(__ldg(p.k2q_n_items + kh), p.k2q_items_cap);
-        if (item_i < n) break;
-        item_i -= n;
+        const int cnt = min(__ldg(p.k2q_n_items + kh), p.k2q_items_cap);
+        if (item_i < cnt) break;
+        item_i -= cnt;
         ++kh;
       }
       const int4* items = reinterpret_cast<const int4*>(p.k2q_items) + (int64_t)kh * p.k2q_items_cap;
       const int32_t* list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
       const int4 item = __ldg(items + item_i);
-      const int row = item.x, r_lo = item.y, r_hi = item.z;
+      const int row = item.x, r_lo = item.y;
       const int b = find_le_slc(p.k2q_blk_cu, p.meta.n_pieces, row);
       const Piece pc = load_piece(p.meta, b);
       const int k0 = (row - p.k2q_blk_cu[b]) * BK;
       const int64_t kv_bos = pc.x_bos;
-      const int kv_rows = min(BK, pc.x_len - k0);
-      if (kv_rows <= 0 || r_hi <= r_lo) {   // not produced by nsa_k2q_index; uniform over the CTA
-        __syncthreads();
-        continue;
-      }
+      const int kv_rows = max(min(BK, pc.x_len - k0), 0);
+      const int r_hi = max(item.z, r_lo + 1);   // nsa_k2q_index writes no empty items; a foreign one still runs one (masked) tile
       const int n_it = (r_hi - r_lo + TOKQ - 1) / TOKQ;
       const int n_round = (n_it + 1) / 2;
-
-      // ---- the item's K/V tile (every MMA of the previous item has completed: the compute groups waited for them)
-      if (tid < 256) {
-        fill_tile_async<D>(sK, reinterpret_cast<const __nv_bfloat16*>(p.k) + (kv_bos + k0) * p.k_stride_t + kh * D, p.k_stride_t, BK,
-                           kv_rows, tid, 256);
-        fill_tile_async<D>(sV, reinterpret_cast<const __nv_bfloat16*>(p.v) + (kv_bos + k0) * p.v_stride_t + kh * D, p.v_stride_t, BK,
-                           kv_rows, tid, 256);
-        cp_async_commit();
-        cp_async_wait<0>();
-        fence_proxy_async();
-      }
-      fence_before_sync();
-      __syncthreads();
-      fence_after_sync();
 
       if (warp == 8) {
         // ================================================= MMA issue (one lane)
         if ((tid & 31) == 0) {
+          if (!mbar_wait(kv_full, n & 1, &budget)) timed_out = true;   // the item's K/V tile has landed
           for (int j = 0; j < n_round; ++j) {
             const int jj = jb + j;
             for (int wg = 0; wg < 2; ++wg) {
@@ -169,6 +173,8 @@ __global__ void __launch_bounds__(480, 1)
             }
             for (int wg = 0; wg < 2; ++wg) {
               if (!mbar_wait(bar(2, wg), jj & 1, &budget)) timed_out = true;
+              // the first dV / dK products of an item overwrite the accumulators: the previous item's flush has read them
+              if (j == 0 && wg == 0 && n > 0 && !mbar_wait(acc_free, (n - 1) & 1, &budget)) timed_out = true;
               fence_after_sync();
               const uint32_t tQ = sQ0 + wg * Q_BYTES, tO = sO0 + wg * Q_BYTES;
               const uint32_t tP = sP0 + wg * P_BYTES, tS = sS0 + wg * P_BYTES;
@@ -201,6 +207,18 @@ __global__ void __launch_bounds__(480, 1)
         constexpr int NP = 192;
         const int n_box = TOKQ * SLABS * 2;
         const uint32_t tx = (uint32_t)(TOKQ * G) * D * 2 * 2;
+        if (n > 0) {   // every MMA of the previous item has completed: K/V and both groups' buffers are free
+          if (!mbar_wait(bar(3, 0), (jb - 1) & 1, &budget)) timed_out = true;
+          if (!mbar_wait(bar(3, 1), (jb - 1) & 1, &budget)) timed_out = true;
+        }
+        if (leader) {
+          tma::expect_tx(kv_full, 2 * KV_BYTES);
+#pragma unroll
+          for (int sl = 0; sl < SLABS; ++sl) {
+            tma::load_3d(sK + sl * K_SLAB, &tmk, sl * 64, kh, (int)(kv_bos + k0), kv_full);
+            tma::load_3d(sV + sl * K_SLAB, &tmv, sl * 64, kh, (int)(kv_bos + k0), kv_full);
+          }
+        }
         for (int it = 0; it < 2 * n_round; ++it) {   // an odd tile count still fills group 1's buffers in the last round
           const int wg = it & 1, j = it >> 1;
           const int tok0 = r_lo + it * TOKQ;
@@ -232,6 +250,11 @@ __global__ void __launch_bounds__(480, 1)
               if (tok2 + n < r_hi) tma::prefetch_3d(which ? &tmo : &tmq, sl * 64, kh * G, __ldg(list + tok2 + n));
             }
           }
+        }
+        if (leader) {   // the next item's ticket, while this item is being worked on
+          const int g1 = atomicAdd(ticket, 1);
+          asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ticket_slot + 4 * ((n + 1) & 1)), "r"(g1) : "memory");
+          mbar_arrive(bar(5, (n + 1) & 1));
         }
       } else {
         // ================================================= two warp groups, one query tile each per round
@@ -319,7 +342,7 @@ __global__ void __launch_bounds__(480, 1)
           const float nlse = -lse;
           if (!mbar_wait(bar(1, wg), jj & 1, &budget)) timed_out = true;
           fence_after_sync();
-          if (fuse && j > 0) {   // the reductions of the previous tile have read my P / dS buffers
+          if (fuse && (j > 0 || n > 0)) {   // the reductions of the previous tile (or item) have read my P / dS buffers
             if (t < n_box) tma::bulk_wait_read();
             named_barrier(2 + wg, 128);
           }
@@ -379,15 +402,18 @@ __global__ void __launch_bounds__(480, 1)
           uint32_t v[32];
           tmem_ld32(acc + half * 32, v);
           wait_ld();
+          if (half == 1) {
+            fence_before_sync();
+            mbar_arrive(acc_free);   // both halves are in registers: the next item's products may overwrite the accumulators
+          }
           if (t < D) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              int kc = half * 32 + i;
+              const int kc = half * 32 + i;
               if (kc < kv_rows) atomicAdd(dst + (int64_t)kc * rstride, __uint_as_float(v[i]) * scale);
             }
           }
         }
-        if (fuse && t < n_box) tma::bulk_wait_read();   // my P / dS buffers may be overwritten by the next item
       }
       jb += n_round;
     }
@@ -418,17 +444,19 @@ static int sm_count() {
 
 template <int D>
 static int launch(const NsaAttnParams* p, cudaStream_t st, const char* name, int fuse) {
-  size_t smem = (size_t)(2 * 64 + 4 * 128) * D * 2 + 4 * 128 * 64 * 2 + 128 + 1024;
+  size_t smem = (size_t)(2 * 64 + 4 * 128) * D * 2 + 4 * 128 * 64 * 2 + 160 + 1024;
   cudaError_t e = cudaFuncSetAttribute(slc_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute(%zu B) failed: %s", name, smem, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
   const int G = p->QH / p->KH;
-  CUtensorMap tmq, tmo, tmdq;
-  if (p->n_q_rows <= 0 || !tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, 1, G) ||
-      !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, 1, G)) {
-    set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q/dout must be 16-byte aligned, n_q_rows set)", name);
+  CUtensorMap tmq, tmo, tmdq, tmk, tmv;
+  if (p->n_q_rows <= 0 || p->n_k_rows <= 0 || !tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, 1, G) ||
+      !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, 1, G) ||
+      !tma::make_map(&tmk, p->k, p->n_k_rows, p->KH, D, p->k_stride_t, 64, 1) ||
+      !tma::make_map(&tmv, p->v, p->n_k_rows, p->KH, D, p->v_stride_t, 64, 1)) {
+    set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q, dout, k, v must be 16-byte aligned; n_q_rows, n_k_rows set)", name);
     return NSA_ERR_CUDA;
   }
   if (!fuse) {
@@ -437,7 +465,7 @@ static int launch(const NsaAttnParams* p, cudaStream_t st, const char* name, int
     set_error("%s: cuTensorMapEncodeTiled failed for dq (must be 16-byte aligned with a row stride that is a multiple of 8)", name);
     return NSA_ERR_CUDA;
   }
-  slc_bwd_tc_kernel<D><<<sm_count(), 480, smem, st>>>(*p, fuse, tmq, tmo, tmdq);
+  slc_bwd_tc_kernel<D><<<sm_count(), 480, smem, st>>>(*p, fuse, tmq, tmo, tmdq, tmk, tmv);
   return check_launch(name);
 }
 
