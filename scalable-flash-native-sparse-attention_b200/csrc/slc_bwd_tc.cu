@@ -141,10 +141,14 @@ __global__ void __launch_bounds__(480, 1)
       const int4 item = __ldg(items + item_i);
       const int row = item.x, r_lo = item.y;
       const int b = find_le_slc(p.k2q_blk_cu, p.meta.n_pieces, row);
-      const Piece pc = load_piece(p.meta, b);
       const int k0 = (row - p.k2q_blk_cu[b]) * BK;
-      const int64_t kv_bos = pc.x_bos;
-      const int kv_rows = max(min(BK, pc.x_len - k0), 0);
+      int kv_row0, kv_rows, ta_base;   // first K/V tensor row of the block, its valid rows, position of local row 0 in the sequence
+      {
+        const Piece pc = load_piece(p.meta, b);
+        kv_row0 = pc.x_bos + k0;
+        kv_rows = max(min(BK, pc.x_len - k0), 0);
+        ta_base = pc.off - pc.q_start;
+      }
       const int r_hi = max(item.z, r_lo + 1);   // nsa_k2q_index writes no empty items; a foreign one still runs one (masked) tile
       const int n_it = (r_hi - r_lo + TOKQ - 1) / TOKQ;
       const int n_round = (n_it + 1) / 2;
@@ -153,6 +157,9 @@ __global__ void __launch_bounds__(480, 1)
         // ================================================= MMA issue (one lane)
         if ((tid & 31) == 0) {
           if (!mbar_wait(kv_full, n & 1, &budget)) timed_out = true;   // the item's K/V tile has landed
+          // Issue order per round: S, dP of both groups, then dV, dK, dQ of both groups: a group's softmax arithmetic runs
+          // under the other group's S, dP.  (Per group S dP dV dK dQ, which would put one group's fetch under the other
+          // group's five products, leaves the tensor core idle during that arithmetic and measured 15 % slower.)
           for (int j = 0; j < n_round; ++j) {
             const int jj = jb + j;
             for (int wg = 0; wg < 2; ++wg) {
@@ -215,8 +222,8 @@ __global__ void __launch_bounds__(480, 1)
           tma::expect_tx(kv_full, 2 * KV_BYTES);
 #pragma unroll
           for (int sl = 0; sl < SLABS; ++sl) {
-            tma::load_3d(sK + sl * K_SLAB, &tmk, sl * 64, kh, (int)(kv_bos + k0), kv_full);
-            tma::load_3d(sV + sl * K_SLAB, &tmv, sl * 64, kh, (int)(kv_bos + k0), kv_full);
+            tma::load_3d(sK + sl * K_SLAB, &tmk, sl * 64, kh, kv_row0, kv_full);
+            tma::load_3d(sV + sl * K_SLAB, &tmv, sl * 64, kh, kv_row0, kv_full);
           }
         }
         for (int it = 0; it < 2 * n_round; ++it) {   // an odd tile count still fills group 1's buffers in the last round
@@ -321,7 +328,7 @@ __global__ void __launch_bounds__(480, 1)
           // my own row: lse, delta, absolute position (loaded during the previous round)
           const bool row_ok = qrow_cur >= 0;
           const float lse = lse_nxt, dl = dl_nxt;
-          const int ta = row_ok ? pc.off + (qrow_cur - pc.q_start) : -1;
+          const int ta = row_ok ? ta_base + qrow_cur : -1;
           qrow_cur = qrow_nxt;
           lse_nxt = 0.f;
           dl_nxt = 0.f;
@@ -394,7 +401,7 @@ __global__ void __launch_bounds__(480, 1)
         fence_after_sync();
         // group 0 writes dV, group 1 writes dK: lane t = column t of the gradient
         const uint32_t acc = lane_base + (wg == 0 ? TM_DV : TM_DK);
-        float* dst = (wg == 0 ? p.dv : p.dk) + (kv_bos + k0) * (wg == 0 ? p.dv_stride_t : p.dk_stride_t) + kh * D + t;
+        float* dst = (wg == 0 ? p.dv : p.dk) + (int64_t)kv_row0 * (wg == 0 ? p.dv_stride_t : p.dk_stride_t) + kh * D + t;
         const int64_t rstride = (wg == 0 ? p.dv_stride_t : p.dk_stride_t);
         const float scale = (wg == 0) ? 1.f : p.sm_scale;
 #pragma unroll
