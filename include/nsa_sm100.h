@@ -186,14 +186,19 @@ typedef struct NsaTopkParams {
   int32_t QH, KH, D;
   int32_t ignore_index;
   int32_t quant; /* what the selection compares: 0 = fp32 score, 1 = score rounded to fp16,
-                    2 = score^3 rounded to fp16 (the reference default below 128K tokens)                  */
+                    2 = score^3 rounded to fp16 (the reference default below 128K tokens),
+                    3 = fp32 score pooled from per-row probabilities rounded to fp16 (the reference's general path) */
   int32_t q_rows;  /* rows of the q tensor and of the ck tensor: bounds of the bulk tensor loads           */
   int32_t ck_rows;
 } NsaTopkParams;
-/* replaces slc_topk_indices_for_32_16_64 (kernel pair _slc_probs_kernel + _topk_kernel),
- * flash_nsa/ops/topk.py:499-628; scores and selection are fused, no [KH,T,blocks] scratch is needed.
- * Contiguous (non-paged) inputs with top_n - num_init - num_local == 13 run on the TMA + tcgen05 kernel (any number
- * of query heads per kv head); paged caches and other list sizes run on the warp-MMA kernel (<= 16 heads per kv head). */
+/* replaces slc_topk_indices_for_32_16_64 (kernel pair _slc_probs_kernel + _topk_kernel, flash_nsa/ops/topk.py:499-628)
+ * and the general pair _attn_probs_kernel + _slc_probs_topk_kernel (topk.py:19-218); scores and selection are fused, no
+ * [KH,T,blocks] or [KH,T,rows] scratch is needed.
+ * kernel 32 / stride 16 / block 64, quant 0-2: contiguous (non-paged) inputs with top_n - num_init - num_local == 13 run
+ * on the TMA + tcgen05 kernel (up to 64 query heads per kv head); paged caches and other list sizes (top_n <= 32) run on
+ * the warp-MMA kernel (<= 16 heads per kv head).  Any other kernel_size / stride / block_size, quant 3, or top_n > 32 run on
+ * the general warp-MMA kernel (<= 16 heads per kv head; meta.x_maxlen must bound the sequence length: it sizes the
+ * per-token score array in shared memory, at most about 5000 blocks).                                               */
 int nsa_slc_topk(const NsaTopkParams* p, void* stream);
 
 typedef struct NsaK2qParams {

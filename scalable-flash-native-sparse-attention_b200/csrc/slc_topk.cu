@@ -195,6 +195,7 @@ using namespace nsa;
 
 namespace nsa {
 int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, cudaStream_t st);  // slc_topk_tc.cu
+int launch_slc_topk_general(const NsaTopkParams* p, cudaStream_t st);                               // slc_topk_general.cu
 }
 
 extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
@@ -202,16 +203,23 @@ extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
   NSA_REQUIRE(p->meta.piece_cu && p->meta.x_cu && p->meta.y_cu, NSA_ERR_BAD_ARG, "slc_topk: null metadata pointer");
   NSA_REQUIRE(p->D == 64 || p->D == 128, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: head dim %d not supported (64 or 128)", p->D);
   NSA_REQUIRE(p->KH > 0 && p->QH % p->KH == 0, NSA_ERR_BAD_ARG, "slc_topk: QH=%d must be a multiple of KH=%d", p->QH, p->KH);
-  NSA_REQUIRE(p->hp.kernel_size == 32 && p->hp.stride == 16 && p->hp.block_size == 64, NSA_ERR_UNSUPPORTED_SHAPE,
-              "slc_topk: only kernel_size=32, stride=16, block_size=64 is implemented (got %d/%d/%d)", p->hp.kernel_size,
-              p->hp.stride, p->hp.block_size);
-  NSA_REQUIRE(p->hp.top_n >= 1 && p->hp.top_n <= 32, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: top_n=%d must be in 1..32", p->hp.top_n);
+  NSA_REQUIRE(p->hp.kernel_size > 0 && p->hp.stride > 0 && p->hp.block_size > 0, NSA_ERR_BAD_ARG,
+              "slc_topk: kernel_size, stride, block_size must be positive (got %d/%d/%d)", p->hp.kernel_size, p->hp.stride, p->hp.block_size);
+  NSA_REQUIRE(p->hp.top_n >= 1, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: top_n=%d must be positive", p->hp.top_n);
   NSA_REQUIRE(p->hp.num_init >= 0 && p->hp.num_local >= 0 && p->hp.num_init + p->hp.num_local <= p->hp.top_n, NSA_ERR_BAD_ARG,
               "slc_topk: num_init + num_local exceeds top_n");
-  NSA_REQUIRE(p->quant >= 0 && p->quant <= 2, NSA_ERR_BAD_ARG, "slc_topk: quant=%d", p->quant);
+  NSA_REQUIRE(p->quant >= 0 && p->quant <= 3, NSA_ERR_BAD_ARG, "slc_topk: quant=%d", p->quant);
   NSA_REQUIRE(!p->meta.cmp_table || (p->meta.page_size > 0 && (p->meta.page_size & (p->meta.page_size - 1)) == 0),
               NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: page_size=%d must be a power of two", p->meta.page_size);
   if (p->meta.n_pieces <= 0 || p->meta.max_piece_len <= 0) return NSA_OK;
+  const bool std_sizes = p->hp.kernel_size == 32 && p->hp.stride == 16 && p->hp.block_size == 64;
+  if (!std_sizes || p->quant == 3 || p->hp.top_n > 32) {
+    // any other compression / block geometry, the per-row rounding mode, or a long list: the general kernel
+    NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE,
+                "slc_topk: the general-size kernel takes at most 16 query heads per kv head (got %d); kernel 32 / stride 16 / "
+                "block 64 with the block-level rounding modes takes up to 64", p->QH / p->KH);
+    return launch_slc_topk_general(p, (cudaStream_t)stream);
+  }
   if (p->q_rows > 0 && p->ck_rows > 0 && p->QH / p->KH <= 64) {
     int rc = launch_slc_topk_tc(p, p->q_rows, p->ck_rows, (cudaStream_t)stream);
     if (rc <= 0) return rc;

@@ -152,11 +152,13 @@ def cmp_attn_decode(q, k, v, block_tables, context_lens, out=None, num_splits=0,
 
 
 # ------------------------------------------------------------------------------------------------ top-n
-def _topk(q, k, lse, lse_head_major, meta_args, block_size, top_n, num_inital, num_local, kernel_size, stride, sm_scale):
+def _topk(q, k, lse, lse_head_major, meta_args, block_size, top_n, num_inital, num_local, kernel_size, stride, sm_scale,
+          fixed_num_slc_blocks=2048):
     T, QH, D = q.shape
     kf, page = _flat(k)
     KH = kf.size(1)
     meta = _PagedMeta(*meta_args, page, kernel_size, stride)
+    meta.struct.x_maxlen = int(fixed_num_slc_blocks) * block_size   # bound of the sequence length (general-size kernel)
     topk = torch.empty(KH, T, top_n, dtype=torch.int32, device=q.device)
     p = S["NsaTopkParams"]()
     p.meta, p.hp = meta.struct, _hyper(kernel_size, stride, block_size, 0, top_n, num_inital, num_local)
@@ -181,7 +183,7 @@ def topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables, cont
                  sm_scale=None, fp32=False):
     """-> topk [kh,t,top_n] int32, unused slots = -1"""
     return _topk(q, k, lse, True, (context_lens, x_cu_seqlens, x_maxlen, None, block_tables), block_size, top_n, num_inital,
-                 num_local, kernel_size, stride, sm_scale)
+                 num_local, kernel_size, stride, sm_scale, fixed_num_slc_blocks)
 
 
 @torch.no_grad()
@@ -189,7 +191,7 @@ def topk_decode(q, k, lse, block_tables, context_lens, kernel_size=32, stride=16
                 num_local=2, fixed_num_slc_blocks=2048, fixed_y_maxlen=8192, sm_scale=None, persistent=False, workers=4):
     """-> topk [kh,b,top_n] int32, unused slots = -1; lse is [b,qh]"""
     return _topk(q, k, lse, False, (context_lens, None, 1, None, block_tables), block_size, top_n, num_inital, num_local,
-                 kernel_size, stride, sm_scale)
+                 kernel_size, stride, sm_scale, fixed_num_slc_blocks)
 
 
 # ------------------------------------------------------------------------------------------------ selected + window attention

@@ -12,11 +12,13 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     """q [t,qh,d], k = compressed keys [rows,kh,d], lse [qh,t] of the compressed branch ->
     (topk [kh,t,top_n] int32, block scores or None).
 
-    Selection compares, per (kv head, token), the pooled block scores: in fp32 when `fp32`, otherwise
-    rounded to half after cubing (`scale_slc_p`, applied while the padded block count is <= 2048, as the
-    reference does) or without cubing.  Unused slots hold `ignore_index` (default: number of blocks of the
-    longest sequence).  Only kernel 32 / stride 16 / block 64 is implemented; `maybe_efficient_version`
-    is accepted for source compatibility (scores are never materialised unless `return_slc_prob`)."""
+    Selection compares, per (kv head, token), the pooled block scores.  As in the reference (topk.py:632-776) there are
+    two paths.  `maybe_efficient_version=True` with kernel 32 / stride 16 / block 64 (what every module passes): scores in
+    fp32 when `fp32`, otherwise rounded to half after cubing (`scale_slc_p`, while the padded block count is <= 2048) or
+    without cubing.  Otherwise the general path, for any kernel_size / stride / block_size: per-row probabilities (summed
+    over the kv head's query heads) rounded to half unless `fp32`, pooled in fp32 with the weights
+    overlap(row window, block) / stride.  Unused slots hold `ignore_index` (default: number of blocks of the longest
+    sequence).  Scores are never materialised unless `return_slc_prob`."""
     check_bf16_3d("q", q)
     check_bf16_3d("k", k)
     T, QH, D = q.shape
@@ -29,8 +31,12 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     pad_blocks = max(1 << max(num_slc_blocks - 1, 0).bit_length(), 8) if align else max(num_slc_blocks, 8)
     assert ignore_index is None or ignore_index >= num_slc_blocks
     ignore_index = num_slc_blocks if ignore_index is None else ignore_index
+    std = (NSAHelper.kernel_size, NSAHelper.stride, NSAHelper.block_size) == (32, 16, 64)
+    general = not (maybe_efficient_version and std)
     if fp32:
         quant = 0
+    elif general:
+        quant = 3
     elif scale_slc_p and pad_blocks <= 2048:
         quant = 2
     else:
@@ -38,7 +44,7 @@ def slc_topk_indices(q, k, lse, sm_scale=None, return_slc_prob=False, align=True
     topk = torch.empty(KH, T, NSAHelper.top_n, dtype=torch.int32, device=q.device)
     probs = None
     if return_slc_prob:
-        probs = torch.zeros(KH, T, pad_blocks, device=q.device, dtype=torch.float32 if fp32 else torch.float16)
+        probs = torch.zeros(KH, T, pad_blocks, device=q.device, dtype=torch.float32 if quant in (0, 3) else torch.float16)
     if T == 0:
         return topk, probs
     p = S["NsaTopkParams"]()
