@@ -64,16 +64,17 @@ class Comm:
         Safe to call while kernels that read the other buffer are still queued on the compute stream."""
         out = self.final[key][self.turn[key]]
         self.turn[key] ^= 1
+        src = x.contiguous()
         if self.cp_mode == 1:
-            h = dist.all_gather_into_tensor(out, x.contiguous(), group=self.pg, async_op=True)
-            self.pending[key] = (h, out, None)
+            h = dist.all_gather_into_tensor(out, src, group=self.pg, async_op=True)
+            self.pending[key] = (h, out, None, src)
             return
         stage = self.stage[key]
-        h = dist.all_gather_into_tensor(stage, x.contiguous(), group=self.pg, async_op=True)
+        h = dist.all_gather_into_tensor(stage, src, group=self.pg, async_op=True)
         if self.side is None:                       # CPU tensors
             h.wait()
             out.copy_(_reorder(stage, self.W, "unshuffle"))
-            self.pending[key] = (None, out, None)
+            self.pending[key] = (None, out, None, None)
             return
         # un-zig-zag on the side stream as soon as the gather is done; the staging buffer is free for the next gather by
         # then because that gather is issued after wait(key), i.e. after the compute stream took this event
@@ -83,7 +84,10 @@ class Comm:
             reorder(stage, self.W, shuffle_mode="unshuffle", out=out)
             ev = torch.cuda.Event()
             ev.record(self.side)
-        self.pending[key] = (None, out, ev)
+        # `src` (a packed copy of the shard when the head slice is strided) was allocated on the compute stream and is read by
+        # the collective on another one: it is kept until wait(key), i.e. until the compute stream has waited for this event.
+        # (h.wait() above releases the collective's own hold on it, and the allocator would hand the block out again.)
+        self.pending[key] = (None, out, ev, src)
 
     @torch.no_grad()
     def wait(self, key):
@@ -91,11 +95,12 @@ class Comm:
         [t*W, heads, d] in sequential token order."""
         if key not in self.pending:
             return self.ready.get(key)
-        h, buf, ev = self.pending.pop(key)
+        h, buf, ev, src = self.pending.pop(key)
         if h is not None:
             h.wait()
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
+        del src
         self.ready[key] = buf
         return buf
 
@@ -135,5 +140,5 @@ class Comm:
             out.copy_(full[r * self.t:(r + 1) * self.t])
             return out
         h = dist.reduce_scatter_tensor(out, full, group=self.pg, async_op=True)
-        self.pending[key] = (h, out, None)
+        self.pending[key] = (h, out, None, None)
         return out
