@@ -233,9 +233,11 @@ int nsa_k2q_index(const NsaK2qParams* p, void* stream);
  * For hosts that cannot allocate at the point of the call: an inference server that gave all free device memory to its
  * KV-cache pool at start-up, or code between a framework's caching allocator and a region where cudaMalloc is not
  * allowed.  Limit: KH * n_cells <= 262144 (without range buckets e.g. 4 kv heads and 4 M tokens), larger sizes are refused with
- * NSA_ERR_UNSUPPORTED_SHAPE.  The first call on each device looks up the array's device address (make that call
- * outside any stream capture).  All calls on a device share the array: the cursors are cleared at the start of every
- * call, and two calls whose kernels overlap on the GPU (different streams) corrupt each other.                  */
+ * NSA_ERR_UNSUPPORTED_SHAPE.  The first call on each device looks up the array's device address: make that call outside
+ * any stream capture and at start-up, before the host gives the device's free memory away (the array is materialised
+ * when the library's code is first used on a device; n_blocks_total = 0 is enough for that call).  The address cache covers
+ * device ordinals 0-63.  All calls on a device share the array: the cursors are cleared at the start of every call, and
+ * two calls whose kernels overlap on the GPU (different streams) corrupt each other.                              */
 int nsa_k2q_index_static(const NsaK2qParams* p, void* stream);
 
 /* ---- gated combine ---------------------------------------------------------------------------------- */
