@@ -344,6 +344,21 @@ typedef struct NsaRopeParams {
 /* replaces fused_apply_rope (forward and backward), flash_nsa/ops/rope.py:5-232 */
 int nsa_rope(const NsaRopeParams* p, void* stream);
 
+/* ---- weight gradient of the learned compression ------------------------------------------------------- */
+typedef struct NsaWgradParams {
+  const void* dy;    /* [rows, n_out] bf16: gradient of the compression's hidden state                       */
+  const void* x;     /* [rows, n_in] bf16: the flattened windows (construct_block output, n_in = kernel_size * D) */
+  float* main_grad;  /* [n_out, n_in] fp32: the trainer's accumulation buffer; the product is ADDED (atomics)  */
+  int32_t* status;   /* optional device word for pipeline time-outs, as in NsaAttnParams                     */
+  int64_t rows;
+  int64_t dy_stride, x_stride, grad_stride; /* row strides in elements                                       */
+  int32_t n_out, n_in;                      /* multiples of 128                                              */
+} NsaWgradParams;
+/* replaces the accumulating weight-gradient GEMM of weight_grad(), flash_nsa/modules/megatron_level_nsa.py:20-44
+ * (apex's wgrad_gemm_accum_fp32, or the reference's Triton gemm(..., acc=True, transpose_a=True), ops/gemm.py:134):
+ * main_grad += dy^T x with fp32 accumulation, one launch, split over the rows.                                   */
+int nsa_wgrad_accum(const NsaWgradParams* p, void* stream);
+
 /* ---- misc -------------------------------------------------------------------------------------------- */
 /* No counterpart in the reference (Triton kernels have no bounded waits).  Runs the give-up path of the bounded pipeline
  * wait that every tcgen05 / TMA kernel here uses, on purpose and with nothing in flight: one warp polls a barrier that

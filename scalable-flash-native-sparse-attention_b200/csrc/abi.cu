@@ -90,6 +90,7 @@ extern "C" int nsa_struct_size(const char* name) {
   NSA_SZ(NsaStoreKvParams);
   NSA_SZ(NsaPagedPoolParams);
   NSA_SZ(NsaDecodeParams);
+  NSA_SZ(NsaWgradParams);
 #undef NSA_SZ
   return 0;
 }

@@ -280,7 +280,7 @@ extern "C" int nsa_cmp_attn_bwd(const NsaAttnParams* p, void* stream) {
     if (rc < 0) return rc;
   }
   if ((ph & 2) && p->meta.y_maxlen > 0 && rc == 1) {
-    DkdvLaunch L{2048, 1, nullptr};
+    DkdvLaunch L{2048};
     dim3 grid((p->meta.y_maxlen + 63) / 64, (p->meta.max_piece_len + L.q_chunk - 1) / L.q_chunk, p->meta.n_pieces * p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_CMP>(p, st, "cmp_attn_bwd(dkdv)", grid, L)
                        : launch_dkdv<64, MODE_CMP>(p, st, "cmp_attn_bwd(dkdv)", grid, L);
@@ -306,7 +306,7 @@ extern "C" int nsa_swa_bwd(const NsaAttnParams* p, void* stream) {
     if (rc < 0) return rc;
   }
   if ((ph & 2) && rc == 1) {
-    DkdvLaunch L{0, 1, nullptr};
+    DkdvLaunch L{0};
     dim3 grid((p->meta.max_piece_len + p->hp.window + 63) / 64 + 1, 1, p->meta.n_pieces * p->KH);
     rc = (p->D == 128) ? launch_dkdv<128, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L) : launch_dkdv<64, MODE_SWA>(p, st, "swa_bwd(dkdv)", grid, L);
     if (rc) return rc;

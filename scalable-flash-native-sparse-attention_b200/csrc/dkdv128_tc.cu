@@ -323,7 +323,7 @@ static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name, 
     set_error("%s: cudaFuncSetAttribute failed: %s", name, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
-  DkdvLaunch L{q_chunk, 1, nullptr};
+  DkdvLaunch L{q_chunk};
   dim3 grid;
   if (MODE == MODE_CMP) grid = dim3((p->meta.y_maxlen + 127) / 128, (p->meta.max_piece_len + q_chunk - 1) / q_chunk, p->meta.n_pieces * p->KH);
   else grid = dim3((p->meta.max_piece_len + p->hp.window + 127) / 128 + 1, 1, p->meta.n_pieces * p->KH);

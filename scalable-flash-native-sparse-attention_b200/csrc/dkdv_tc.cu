@@ -1,8 +1,9 @@
-// dK/dV of all three attention branches on the Blackwell tensor core (tcgen05 + tensor memory).
+// dK/dV of the compressed and sliding-window branches with 64-row K/V tiles (tcgen05 + tensor memory): the fallback of
+// dkdv128_tc.cu for head-group sizes that do not divide 128 and for tensors the 128-row TMA boxes cannot address.  (The
+// selected branch has its own persistent kernel built on the same tile machinery, slc_bwd_tc.cu.)
 //
-// One CTA owns a 64-row K/V tile (compressed rows, a 64-key stretch of a sequence, or one selected block) and a slice
-// of the queries that see it.  Query rows come in tiles of 128 = (128/G tokens) x (G heads of the kv head), taken from
-// a contiguous token range (compressed, sliding window) or gathered through the key-block -> queries lists (selected).
+// One CTA owns a 64-row K/V tile (compressed rows or a 64-key stretch of a sequence) and a slice of the queries that see
+// it.  Query rows come in tiles of 128 = (128/G tokens) x (G heads of the kv head), taken from a contiguous token range.
 // Two warp groups of 128 threads each work on their own query tile (ping-pong), a ninth warp issues every MMA and six
 // more fetch the Q / dO tiles with TMA, one (64 d) x (G heads) x (1 token) box per lane, as soon as a group's buffers
 // are free:
@@ -20,29 +21,17 @@ namespace nsa {
 
 constexpr int MODE_CMP = 0;
 constexpr int MODE_SWA = 1;
-constexpr int MODE_SLC = 2;
-
-__device__ __forceinline__ int find_le_tc(const int32_t* cu, int n, int x) {
-  int lo = 0, hi = n;
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (cu[mid] <= x) lo = mid; else hi = mid;
-  }
-  return lo;
-}
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(480, 1)
-    dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo,
-                   const __grid_constant__ CUtensorMap tmdq) {
+    dkdv_tc_kernel(NsaAttnParams p, DkdvLaunch L, const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmo) {
   using namespace tc;
   constexpr int BK = 64, BQ = 128;
   constexpr uint32_t KV_BYTES = BK * D * 2, Q_BYTES = BQ * D * 2, P_BYTES = BQ * BK * 2;
   constexpr uint32_t Q_SLAB = BQ * 128, K_SLAB = BK * 128;
   constexpr uint32_t A_LBO = (D == 128) ? Q_SLAB : 0;  // D = 64: the second half of M re-reads the only slab (rows 64.. of the result are unused)
   constexpr uint32_t IDESC_SD = make_idesc(BQ, BK, false, false), IDESC_KV = make_idesc(128, BK, true, true);
-  constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, true, false);
-  constexpr uint32_t TM_DV = 256, TM_DK = 320, TM_DQ = 384, TM_COLS = 512;
+  constexpr uint32_t TM_DV = 256, TM_DK = 320, TM_COLS = 512;
 
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -52,7 +41,7 @@ __global__ void __launch_bounds__(480, 1)
   const uint32_t sP0 = sO0 + 2 * Q_BYTES;             // [2 groups]
   const uint32_t sS0 = sP0 + 2 * P_BYTES;             // [2 groups]
   const uint32_t bars = sS0 + 2 * P_BYTES;
-  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2], dq_read[2]; then the tensor-memory address slot
+  // barriers: in_full[2], sd_done[2], pds_full[2], kv_done[2]; then the tensor-memory address slot
   auto bar = [&](int which, int wg) { return bars + (which * 2 + wg) * 8; };
   const uint32_t tm_slot = bars + 80;
 
@@ -64,24 +53,7 @@ __global__ void __launch_bounds__(480, 1)
   int kh, k0, kv_rows, r_lo, r_hi;
   int64_t kv_bos;
   Piece pc;
-  const int32_t* list = nullptr;
-  if (MODE == MODE_SLC) {
-    kh = blockIdx.z;
-    const int row = blockIdx.x;
-    const int b = find_le_tc(L.blk_cu, p.meta.n_pieces, row);
-    pc = load_piece(p.meta, b);
-    k0 = (row - L.blk_cu[b]) * BK;
-    kv_bos = pc.x_bos;
-    kv_rows = min(BK, pc.x_len - k0);
-    const int32_t* offs = p.k2q_offsets + (int64_t)kh * (p.n_blocks_total + 1);
-    const int lo = offs[row], hi = offs[row + 1];
-    // at least 64 query tiles per CTA: short lists use fewer of the `splits` CTAs (the others leave at once), which
-    // keeps the K/V load and the atomic write-back of a CTA small against its tile work
-    const int per = max((((hi - lo + L.splits - 1) / L.splits + TOKQ - 1) / TOKQ) * TOKQ, 64 * TOKQ);
-    r_lo = lo + blockIdx.y * per;
-    r_hi = min(hi, r_lo + per);
-    list = p.k2q_tokens + (int64_t)kh * p.k2q_stride_h;
-  } else {
+  {
     kh = blockIdx.z % p.KH;
     pc = load_piece(p.meta, blockIdx.z / p.KH);
     if (MODE == MODE_CMP) {
@@ -110,7 +82,6 @@ __global__ void __launch_bounds__(480, 1)
       mbar_init(bar(1, w), 1);
       mbar_init(bar(2, w), 128);
       mbar_init(bar(3, w), 1);
-      mbar_init(bar(4, w), 128);
     }
     fence_mbar_init();
   }
@@ -135,9 +106,6 @@ __global__ void __launch_bounds__(480, 1)
   asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(tm_slot));
   int budget = kWaitBudget;
   bool timed_out = false;
-  // selected branch with the dQ product fused in: after dV and dK of a tile, dS K goes into columns of its own, shared by
-  // the two groups in turn; the tile's group adds it into dq
-  const bool fuse = (MODE == MODE_SLC) && L.fuse_dq;
 
   if (warp == 8) {
     // ================================================= MMA issue (one lane)
@@ -171,14 +139,6 @@ __global__ void __launch_bounds__(480, 1)
 #pragma unroll
           for (int u = 0; u < BQ / 16; ++u)
             mma_ss(tmem + TM_DK, desc_mnmajor(tQ + u * 2048, A_LBO), desc_mnmajor(tS + u * 2048, 0), IDESC_KV, (u > 0) ? 1u : first);
-          if (fuse) {   // dS K into its own columns, once the other group has read the previous tile's product out of them
-            const int m = 2 * j + wg;
-            if (m > 0 && !mbar_wait(bar(4, 0), (m - 1) & 1, &budget)) timed_out = true;
-            fence_after_sync();
-#pragma unroll
-            for (int u = 0; u < BK / 16; ++u)
-              mma_ss(tmem + TM_DQ, desc_kmajor(tS + u * 32), desc_mnmajor(sK + u * 2048, K_SLAB), IDESC_DQ, u > 0);
-          }
           mma_commit(bar(3, wg));
         }
       }
@@ -198,7 +158,7 @@ __global__ void __launch_bounds__(480, 1)
       // tensor rows of my first four boxes now, so that the index loads overlap the wait for the buffers
       auto row_of = [&](int b) {
         const int tok = min(tok0 + b / (SLABS * 2), r_hi - 1);   // past the end: a valid row again (its P, dS are zero)
-        return (MODE == MODE_SLC) ? __ldg(list + tok) : pc.q_start + tok;
+        return pc.q_start + tok;
       };
       int rows[4];
 #pragma unroll
@@ -223,65 +183,20 @@ __global__ void __launch_bounds__(480, 1)
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float c2 = p.sm_scale * 1.4426950408889634f;
     const int my_n = t / G, my_g = t - my_n * G;
-    // fused dQ: my row of dS K (complete once kv_done has fired) goes, as bf16, into my P and dS
-    // buffers (free by then) in the layout of a q tile; one bulk tensor reduction per (token, 64-column slab) then adds
-    // the token's [G heads x 64] box into dq.  red_row = tensor row of token t % TOKQ of the tile (threads that own a box).
-    constexpr int SLABS = D / 64;
-    const int n_box = TOKQ * SLABS;
-    int red_row = -1;
-    auto add_dq = [&](int row) {
-      fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + TM_DQ + c * 32, v);
-        wait_ld();
-        const uint32_t sb = ((c >> 1) ? tS : tP) + t * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t w[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            w[u] = pack_bf16(__uint_as_float(v[8 * i + 2 * u]) * p.sm_scale, __uint_as_float(v[8 * i + 2 * u + 1]) * p.sm_scale);
-          const uint32_t ch = (c & 1) * 4 + i;
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(sb + ((ch ^ (t & 7)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                       : "memory");
-        }
-      }
-      fence_before_sync();
-      mbar_arrive(bar(4, 0));             // the dQ columns may take the next tile's product
-      fence_proxy_async();
-      named_barrier(2 + wg, 128);
-      if (t < n_box) {
-        if (row >= 0) {
-          for (int b = t; b < n_box; b += 128) {
-            const int n = b % TOKQ, sl = b / TOKQ;
-            tma::reduce_add_3d(&tmdq, sl * 64, kh * G, row, (sl ? tS : tP) + n * G * 128);
-          }
-        }
-        tma::bulk_commit();
-      }
-    };
-
     for (int j = 0; j < n_round; ++j) {
       const int it = 2 * j + wg;
       const int tok0 = r_lo + it * TOKQ;  // first token (range position / list position) of my tile
       if (j > 0 && !mbar_wait(bar(3, wg), (j - 1) & 1, &budget)) timed_out = true;  // my buffers are free again
-      if (fuse && j > 0) add_dq(red_row);
       // my own row: lse, delta, absolute position
       const bool row_ok = (my_n < TOKQ) && (tok0 + my_n < r_hi);
       float lse = 0.f, dl = 0.f;
       int ta = -1;
       if (row_ok) {
-        int64_t q_row = (MODE == MODE_SLC) ? (int64_t)__ldg(list + tok0 + my_n) : (int64_t)pc.q_start + tok0 + my_n;
+        int64_t q_row = (int64_t)pc.q_start + tok0 + my_n;
         int64_t a = q_row * p.lse_stride_t + (int64_t)(kh * G + my_g) * p.lse_stride_h;
         lse = p.lse[a];
         dl = p.delta[a];
         ta = pc.off + (int)(q_row - pc.q_start);
-      }
-      if (fuse && t < n_box) {
-        const int tok = tok0 + t % TOKQ;
-        red_row = (tok < r_hi) ? __ldg(list + tok) : -1;
       }
       // keys kc_lo..kc_hi of the tile are visible to my row
       int kc_lo = 0, kc_hi = -1;
@@ -294,10 +209,6 @@ __global__ void __launch_bounds__(480, 1)
       const float nlse = -lse;
       if (!mbar_wait(bar(1, wg), j & 1, &budget)) timed_out = true;
       fence_after_sync();
-      if (fuse && j > 0) {   // the reductions of the previous tile have read my P / dS buffers
-        if (t < n_box) tma::bulk_wait_read();
-        named_barrier(2 + wg, 128);
-      }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t sv[32], dv[32];
@@ -340,7 +251,6 @@ __global__ void __launch_bounds__(480, 1)
     }
     // ---- all MMAs done (the tensor core retires them in issue order, group 1's last commit is the final one)
     if (!mbar_wait(bar(3, wg), (n_round - 1) & 1, &budget)) timed_out = true;
-    if (fuse) add_dq(red_row);
     if (!mbar_wait(bar(3, 1), (n_round - 1) & 1, &budget)) timed_out = true;
     fence_after_sync();
     // group 0 writes dV, group 1 writes dK: lane t = column t of the gradient
@@ -361,7 +271,6 @@ __global__ void __launch_bounds__(480, 1)
         }
       }
     }
-    if (fuse && t < n_box) tma::bulk_wait_all();
   }
   if (timed_out && p.status) atomicOr(p.status, 2);
   fence_before_sync();
@@ -378,19 +287,13 @@ int launch_dkdv(const NsaAttnParams* p, cudaStream_t st, const char* name, dim3 
     return NSA_ERR_CUDA;
   }
   const int G = p->QH / p->KH;
-  CUtensorMap tmq, tmo, tmdq;
+  CUtensorMap tmq, tmo;
   if (p->n_q_rows <= 0 || !tma::make_map(&tmq, p->q, p->n_q_rows, p->QH, D, p->q_stride_t, 1, G) ||
       !tma::make_map(&tmo, p->dout, p->n_q_rows, p->QH, D, p->do_stride_t, 1, G)) {
     set_error("%s: cuTensorMapEncodeTiled failed or is unavailable (q/dout must be 16-byte aligned, n_q_rows set)", name);
     return NSA_ERR_CUDA;
   }
-  if (!L.fuse_dq) {
-    tmdq = tmq;   // unused
-  } else if (!tma::make_map(&tmdq, p->dq, p->n_q_rows, p->QH, D, p->dq_stride_t, 1, G)) {
-    set_error("%s: cuTensorMapEncodeTiled failed for dq (must be 16-byte aligned with a row stride that is a multiple of 8)", name);
-    return NSA_ERR_CUDA;
-  }
-  dkdv_tc_kernel<D, MODE><<<grid, 480, smem, st>>>(*p, L, tmq, tmo, tmdq);
+  dkdv_tc_kernel<D, MODE><<<grid, 480, smem, st>>>(*p, L, tmq, tmo);
   return check_launch(name);
 }
 

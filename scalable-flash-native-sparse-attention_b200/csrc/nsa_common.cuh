@@ -21,12 +21,9 @@ int check_launch(const char* what);
     }                                           \
   } while (0)
 
-// launch description of the shared dK/dV kernel (dense_bwd.cu), also used by the selected-branch backward
+// launch description of the 64-row-tile dK/dV kernel of the dense branches (dkdv_tc.cu)
 struct DkdvLaunch {
-  int q_chunk;            // compressed branch: query tokens per CTA slice
-  int splits;             // selected branch: CTAs per key block
-  const int32_t* blk_cu;  // selected branch: first table row of each piece
-  int fuse_dq = 0;        // selected branch: also form dS K per tile and add it into dq (bf16 reductions in global memory)
+  int q_chunk;   // compressed branch: query tokens per CTA slice
 };
 
 // ------------------------------------------------------------------ piece lookup

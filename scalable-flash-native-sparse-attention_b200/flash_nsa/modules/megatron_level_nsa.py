@@ -19,20 +19,36 @@ from ..ops.topk import slc_topk_indices
 from ..utils import NSAHelper
 
 
+def wgrad_accum(input, grad_output, main_grad):
+    """main_grad [out, in] fp32 += grad_output [rows, out]^T @ input [rows, in] (bf16 operands) in ONE launch of the tcgen05
+    accumulate GEMM; returns False when the shapes are not its (out, in multiples of 128, aligned rows)."""
+    from ..ops._common import S, call, ptr, status_word
+    rows, n_in = input.shape
+    n_out = grad_output.size(1)
+    ok = (input.is_cuda and input.dtype == torch.bfloat16 and grad_output.dtype == torch.bfloat16 and main_grad.dtype == torch.float32
+          and tuple(main_grad.shape) == (n_out, n_in) and n_out % 128 == 0 and n_in % 128 == 0
+          and input.stride(1) == 1 and grad_output.stride(1) == 1 and main_grad.stride(1) == 1
+          and input.stride(0) % 8 == 0 and grad_output.stride(0) % 8 == 0 and main_grad.stride(0) % 4 == 0
+          and input.data_ptr() % 16 == 0 and grad_output.data_ptr() % 16 == 0 and main_grad.data_ptr() % 16 == 0)
+    if not ok:
+        return False
+    p = S["NsaWgradParams"]()
+    p.dy, p.x, p.main_grad, p.status = ptr(grad_output), ptr(input), ptr(main_grad), ptr(status_word(input.device))
+    p.rows, p.dy_stride, p.x_stride, p.grad_stride = rows, grad_output.stride(0), input.stride(0), main_grad.stride(0)
+    p.n_out, p.n_in = n_out, n_in
+    call("nsa_wgrad_accum", p, input)
+    return True
+
+
 def weight_grad(input, grad_output, weight):
-    """dW = grad_output^T @ input, accumulated into `weight.main_grad` when the trainer provides one."""
+    """dW = grad_output^T @ input, accumulated into `weight.main_grad` when the trainer provides one
+    (flash_nsa/modules/megatron_level_nsa.py:20-44, which uses apex's wgrad_gemm_accum_fp32 or its Triton GEMM for this)."""
     input = input.reshape(-1, input.size(-1))
     grad_output = grad_output.reshape(-1, grad_output.size(-1))
     main_grad = getattr(weight, "main_grad", None)
     if main_grad is not None:
-        # the trainer's fp32 accumulation buffer: one library GEMM on the bf16 operands with an fp32 result, added in place
-        # (flash_nsa/modules/megatron_level_nsa.py:20-44 uses apex's wgrad_gemm_accum_fp32 or its Triton GEMM for this)
-        if main_grad.dtype == torch.float32 and input.dtype != torch.float32:
-            try:
-                main_grad.add_(torch.mm(grad_output.t(), input, out_dtype=torch.float32))
-            except (TypeError, RuntimeError):
-                main_grad.addmm_(grad_output.t().to(main_grad.dtype), input.to(main_grad.dtype))
-        else:
+        if not wgrad_accum(input, grad_output, main_grad):
+            # shapes outside the fused kernel (e.g. 64 output columns): a library GEMM, then the add
             main_grad.addmm_(grad_output.t().to(main_grad.dtype), input.to(main_grad.dtype))
         if hasattr(weight, "grad_added_to_main_grad"):
             weight.grad_added_to_main_grad = True

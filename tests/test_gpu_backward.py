@@ -416,3 +416,24 @@ def test_compress_weight_grads_accumulate_into_main_grad():
     for a, b in zip(res["plain"], res["main_grad"]):
         scale = max(1.0, a.abs().max().item())
         assert (a - b).abs().max().item() <= 1e-2 * scale
+
+
+@pytest.mark.parametrize("rows,n_out,n_in", [(1000, 128, 2048), (16380, 256, 4096), (63, 128, 128), (4096 * 5 + 17, 128, 4096)])
+def test_weight_gradient_accumulate_gemm(rows, n_out, n_in):
+    """main_grad += dY^T X in one launch (the fused-accumulate GEMM behind weight_grad) against an fp32 matmul of the same
+    bf16 operands, on top of a non-zero buffer, for row counts that are not multiples of the 64-row k-step or of the
+    split over CTAs; a strided (column-sliced) dY is taken as it is."""
+    from flash_nsa.modules.megatron_level_nsa import wgrad_accum
+    g = torch.Generator().manual_seed(rows + n_out)
+    wide = torch.randn(rows, n_out + 64, generator=g).bfloat16().cuda()
+    dy = wide[:, 64:]                                   # row stride n_out + 64, 16-byte aligned start
+    x = torch.randn(rows, n_in, generator=g).bfloat16().cuda()
+    acc = torch.full((n_out, n_in), 0.25, dtype=torch.float32, device="cuda")
+    assert wgrad_accum(x, dy, acc)
+    ref = 0.25 + dy.float().t() @ x.float()
+    err = (acc - ref).abs().max().item()
+    assert err <= 2e-3 * max(1.0, ref.abs().max().item()), err
+    assert wgrad_accum(x, dy, acc)                      # a second call adds again
+    assert (acc - (2 * ref - 0.25)).abs().max().item() <= 4e-3 * max(1.0, ref.abs().max().item())
+    # shapes the kernel does not take are reported, not mangled
+    assert not wgrad_accum(x, dy[:, :64], torch.zeros(64, n_in, device="cuda"))
