@@ -300,11 +300,14 @@ typedef struct NsaDecodeParams {
   int32_t B, QH, KH, D;
   int32_t page_size, kv_table_stride, cmp_table_stride;
   int32_t y_cap;               /* most compressed rows a sequence may have (sizes the shared-memory score array)      */
-  int32_t reserved0;
+  int32_t cache_rows;          /* rows of the flat caches (pages * page_size): bounds of the bulk tensor loads; 0 = unknown
+                                  (the kernel then fetches its tiles with per-warp copies)                           */
 } NsaDecodeParams;
 /* replaces the whole body of nsa_decode, flash_nsa/inference/__init__.py:160-257 (8 launches there): pooling of the new
  * compressed row, compressed attention, block scores + top-n, selected and sliding-window attention, gated combine,
- * one CTA per (sequence, kv head).  Needs kernel 32 / stride 16 / block 64 and at most 16 query heads per kv head.   */
+ * one CTA per (sequence, kv head): a producer warp streams the K/V tiles of the step through a shared-memory ring with
+ * bulk tensor loads, six consumer warps work on them.  Needs kernel 32 / stride 16 / block 64 and at most 16 query heads
+ * per kv head.                                                                                                      */
 int nsa_decode_fused(const NsaDecodeParams* p, void* stream);
 
 /* ---- context-parallel chunk reorder ------------------------------------------------------------------ */

@@ -11,6 +11,7 @@
 //      warps 5-7, concurrently with 3
 //   5. o = sigmoid(w0) cmp_o + sigmoid(w1) slc_o + sigmoid(w2) swa_o
 // Bytes read per (sequence, kv head): compressed K twice and V once, 16 selected blocks and <= 9 window tiles of K and V.
+#include <cstdlib>
 #include "warp_tile_smem.cuh"
 
 namespace nsa {
@@ -252,6 +253,10 @@ __global__ void __launch_bounds__(256, 1) decode_fused_kernel(NsaDecodeParams p)
 
 using namespace nsa;
 
+namespace nsa {
+int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st);   // decode_ring.cu
+}
+
 extern "C" int nsa_decode_fused(const NsaDecodeParams* p, void* stream) {
   NSA_REQUIRE(p && p->q && p->k_cache && p->v_cache && p->w && p->o && p->context_lens && p->kv_table && p->cmp_table, NSA_ERR_BAD_ARG,
               "decode_fused: null pointer");
@@ -266,6 +271,13 @@ extern "C" int nsa_decode_fused(const NsaDecodeParams* p, void* stream) {
               "decode_fused: page_size=%d must be a power of two >= 64", p->page_size);
   NSA_REQUIRE(p->y_cap > 0 && p->y_cap % 4 == 0, NSA_ERR_BAD_ARG, "decode_fused: y_cap=%d must be a positive multiple of 4", p->y_cap);
   if (p->B <= 0) return NSA_OK;
+  // the TMA-fed kernel (a ring of K/V tiles filled by a producer warp) when the cache can be addressed by bulk tensor loads;
+  // NSA_DECODE_PER_WARP_LOADS=1 keeps the kernel below, in which every warp fetches its own tiles
+  static const bool per_warp = [] { const char* e = getenv("NSA_DECODE_PER_WARP_LOADS"); return e && e[0] == '1'; }();
+  if (!per_warp) {
+    const int rc = launch_decode_ring(p, (cudaStream_t)stream);
+    if (rc <= 0) return rc;
+  }
   const int D = p->D;
   const size_t states = (size_t)8 * (32 + 16 * D) * 4, scores = ((size_t)p->y_cap + 8 + p->y_cap / 4 + 8) * 4;
   NSA_REQUIRE(scores <= states, NSA_ERR_UNSUPPORTED_SHAPE, "decode_fused: y_cap=%d too large for head dim %d (max %d)", p->y_cap, D,

@@ -80,6 +80,8 @@ __device__ __forceinline__ void wait_ld() { asm volatile("tcgen05.wait::ld.sync.
 __device__ __forceinline__ void wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 // make shared-memory writes done through the generic proxy (cp.async, st.shared) visible to the tensor core
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// the same for global memory: plain stores of this thread become visible to bulk tensor loads issued after a barrier
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;\n" ::: "memory"); }
 
 // each thread of a warp reads 32 consecutive fp32 columns of ITS lane (lane = 32*(warp%4) + laneid)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -83,19 +83,11 @@ __device__ __forceinline__ void scores64(float (&s)[8][4], const uint32_t (&qf)[
   }
 }
 
-// one online-softmax step over a 64-key tile: krow(i) / vrow(i) give the tensor rows of key i (already clamped to valid
-// rows), vis(i) says whether key i takes part.  The buffer holds K first, then V.
-template <int D, class RowFn, class VisFn>
-__device__ __forceinline__ void attend64(Acc<D>& a, const uint32_t (&qf)[D / 16][4], uint32_t buf, const __nv_bfloat16* kbase,
-                                         const __nv_bfloat16* vbase, int64_t kstride, int64_t vstride, RowFn row, VisFn vis, float c2,
-                                         int lane) {
+// online-softmax update of the state with the raw scores of one 64-key tile; on return s holds the probabilities
+// exp2(s*c2 - new max) (0 for keys that do not take part) and the accumulator is rescaled, ready for P.V
+template <int D, class VisFn>
+__device__ __forceinline__ void softmax64(Acc<D>& a, float (&s)[8][4], VisFn vis, float c2, int lane) {
   const int c_ = lane & 3;
-  fill_async<D>(buf, kbase, kstride, row, lane);
-  fill_wait();
-  float s[8][4];
-  scores64<D>(s, qf, buf, lane);
-  __syncwarp();                                         // every lane has read K: the buffer takes V while the softmax runs
-  fill_async<D>(buf, vbase, vstride, row, lane);
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
     const int i = nt * 8 + 2 * c_;
@@ -134,7 +126,11 @@ __device__ __forceinline__ void attend64(Acc<D>& a, const uint32_t (&qf)[D / 16]
   for (int i = 0; i < D / 8; ++i) {
     a.o[i][0] *= al_lo; a.o[i][1] *= al_lo; a.o[i][2] *= al_hi; a.o[i][3] *= al_hi;
   }
-  fill_wait();
+}
+
+// a.o += P V with the probabilities of softmax64 and the 64-row V tile in `buf`
+template <int D>
+__device__ __forceinline__ void pv64(Acc<D>& a, const float (&s)[8][4], uint32_t buf, int lane) {
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const uint32_t a0 = pack_bf16(s[2 * u][0], s[2 * u][1]), a1 = pack_bf16(s[2 * u][2], s[2 * u][3]);
@@ -147,7 +143,43 @@ __device__ __forceinline__ void attend64(Acc<D>& a, const uint32_t (&qf)[D / 16]
       mma_bf16(a.o[2 * np + 1], a0, a1, a2, a3, b[2], b[3]);
     }
   }
+}
+
+// one online-softmax step over a 64-key tile: row(i) gives the tensor row of key i (already clamped to valid
+// rows), vis(i) says whether key i takes part.  The buffer holds K first, then V.
+template <int D, class RowFn, class VisFn>
+__device__ __forceinline__ void attend64(Acc<D>& a, const uint32_t (&qf)[D / 16][4], uint32_t buf, const __nv_bfloat16* kbase,
+                                         const __nv_bfloat16* vbase, int64_t kstride, int64_t vstride, RowFn row, VisFn vis, float c2,
+                                         int lane) {
+  fill_async<D>(buf, kbase, kstride, row, lane);
+  fill_wait();
+  float s[8][4];
+  scores64<D>(s, qf, buf, lane);
+  __syncwarp();                                         // every lane has read K: the buffer takes V while the softmax runs
+  fill_async<D>(buf, vbase, vstride, row, lane);
+  softmax64<D>(a, s, vis, c2, lane);
+  fill_wait();
+  pv64<D>(a, s, buf, lane);
   __syncwarp();                                         // the buffer may be refilled by the next tile
+}
+
+// the same step for K and V tiles that are already in shared memory (filled by TMA): rows >= n_rows of the tiles may hold
+// anything (cache rows past the sequence's end), so their V rows are cleared first: 0 * garbage must not reach the sums
+template <int D, class VisFn>
+__device__ __forceinline__ void attend64_smem(Acc<D>& a, const uint32_t (&qf)[D / 16][4], uint32_t buf_k, uint32_t buf_v, VisFn vis,
+                                              int n_rows, float c2, int lane) {
+  constexpr int CH = D / 8;
+  if (n_rows < kTileRows) {
+    for (int idx = n_rows * CH + lane; idx < kTileRows * CH; idx += 32) {
+      const int r = idx / CH, c = idx - r * CH;
+      asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(buf_v + tc::slab_off(kTileRows, r, c)), "r"(0) : "memory");
+    }
+    __syncwarp();
+  }
+  float s[8][4];
+  scores64<D>(s, qf, buf_k, lane);
+  softmax64<D>(a, s, vis, c2, lane);
+  pv64<D>(a, s, buf_v, lane);
 }
 
 // Dump a warp's state to shared memory as (m[16], l[16], o[16][D]) in plain row-major floats

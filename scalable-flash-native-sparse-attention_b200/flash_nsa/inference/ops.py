@@ -275,6 +275,7 @@ def nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, c
     p.page_size, p.kv_table_stride, p.cmp_table_stride = page, block_tables.stride(0), cmp_block_tables.stride(0)
     fit = ((8 * (32 + 16 * D) - 16) * 4 // 5) // 4 * 4        # what the kernel's shared-memory score array can hold
     p.y_cap = min((int(fixed_y_maxlen) + 3) // 4 * 4, fit)
+    p.cache_rows = kf.size(0)
     for t_ in (context_lens, block_tables, cmp_block_tables, cmp_slot_mapping):
         assert t_.dtype == torch.int32
     if B:

@@ -63,7 +63,7 @@ _mirror = {}   # device index -> [pinned host copy of the word, event of the las
 
 STATUS_BITS = {1: "dense forward", 2: "selected-branch dK/dV", 4: "dense dQ", 8: "misaligned shared memory", 16: "scores + top-n",
                32: "decode: compressed rows exceed y_cap", 64: "dense dK/dV (128-row tiles)", 128: "selected forward",
-               256: "selected dQ", 512: "wait self-test", 1024: "weight-gradient GEMM"}
+               256: "selected dQ", 512: "wait self-test", 1024: "weight-gradient GEMM", 2048: "decode (tile ring)"}
 
 
 def status_word(device):
