@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
   auto full = [&](int s) { return bars + 8 * s; };
   auto empty = [&](int s) { return bars + 8 * (n_slots + s); };
   const uint32_t sel_ready = bars + 16 * n_slots;
+  const uint32_t issued = sel_ready + 8;   // number of jobs whose loads have been issued (written by the producer)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g_ = lane >> 2, c_ = lane & 3;
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
       mbar_init(empty(s), 1);
     }
     mbar_init(sel_ready, 1);
+    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(issued), "r"(0) : "memory");
     fence_mbar_init();
     // job list: (type, consumer, index).  Phase 4 is ordered so that the ring always holds work for both consumer groups:
     // forced blocks (consumers 1-3), two window tiles (4-5), then two selected blocks for every further window tile.
@@ -162,6 +164,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
           tma::load_3d(dst + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, full(s));
           if (type != JOB_CMP_K) tma::load_3d(dst + TILE_BYTES + sl * SLAB_BYTES, &tmv, sl * 64, kh, row, full(s));
         }
+        asm volatile("st.release.cta.shared::cta.b32 [%0], %1;\n" ::"r"(issued), "r"(j + 1) : "memory");
       }
     }
   } else {
@@ -170,7 +173,19 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
     uint32_t qf[D / 16][4];
     wts::load_q<D>(qf, reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)b * p.q_stride_t + (int64_t)kh * G * D, G, lane);
     const float c2 = p.sm_scale * 1.4426950408889634f;
+    // A slot is used by different consumers in turn, so a consumer can get to its wait while the slot's barrier is still
+    // one or more phases behind, where a parity test means nothing.  It therefore first waits until the producer has
+    // issued its job (the barrier is then in that job's phase, open or complete), and only then for the data.
     auto wait_job = [&](int j) {
+      int seen = 0;
+      for (int i = 0; i < budget; ++i) {
+        asm volatile("ld.acquire.cta.shared::cta.b32 %0, [%1];\n" : "=r"(seen) : "r"(issued) : "memory");
+        if (seen > j) break;
+      }
+      if (seen <= j) {
+        timed_out = true;
+        budget = 8;
+      }
       if (!mbar_wait(full(j % n_slots), (j / n_slots) & 1, &budget)) timed_out = true;
     };
     auto release = [&](int j) {
@@ -355,7 +370,7 @@ int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) {
   const size_t tile = (size_t)64 * D * 2;
   const size_t region = (size_t)max(RING_NC * (32 + 16 * D), p->y_cap + 8 + p->y_cap / 4 + 8) * 4;
   const int job_cap = 2 * ((p->y_cap + 63) / 64) + 2 * p->hp.top_n + p->hp.window / 64 + 8;
-  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap) * 4 + 8 + 16 * 8 + 8 + 1024;
+  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap) * 4 + 8 + 16 * 8 + 16 + 1024;
   int n_slots = (int)((227 * 1024 - fixed) / (2 * tile));
   if (n_slots > 5) n_slots = 5;
   if (n_slots < 3) return 1;
