@@ -73,9 +73,37 @@ struct TopList {
   }
 };
 
+// The same list for the half-precision scoring modes, where a score is 16 bits: one sortable word per entry,
+// (half bits << 16) | (0xffff - block), so that a larger word means a better entry (higher score, then lower block index)
+// and an insertion moves 13 registers instead of 26.  Scores are non-negative, so their half bits order like the values;
+// 0 marks an empty entry (a real entry has a block index below 0xffff).
+struct PackedList {
+  uint32_t k[kList];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int j = 0; j < kList; ++j) k[j] = 0u;
+  }
+  static __device__ __forceinline__ uint32_t key(float rounded_score, int blk) {
+    return ((uint32_t)__half_as_ushort(__float2half_rn(rounded_score)) << 16) | (uint32_t)(0xffff - blk);
+  }
+  __device__ __forceinline__ bool wants(uint32_t ck) const { return ck > k[kList - 1]; }
+  __device__ __forceinline__ void insert(uint32_t ck) {   // caller has checked wants(ck); keys are unique
+    int pos = 0;
+#pragma unroll
+    for (int j = 0; j < kList; ++j) pos += (k[j] > ck) ? 1 : 0;
+#pragma unroll
+    for (int j = kList - 1; j >= 0; --j) {
+      const uint32_t from_left = j > 0 ? k[j - 1] : 0u;
+      k[j] = (j == pos) ? ck : ((j > pos) ? from_left : k[j]);
+    }
+  }
+  __device__ __forceinline__ int block(int j) const { return 0xffff - (int)(k[j] & 0xffffu); }
+};
+
 }  // namespace
 
-template <int D>
+// PACKED: the scores are rounded to half before they are compared (quant 1 or 2) and the lists hold one word per entry
+template <int D, bool PACKED>
 __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, const __grid_constant__ CUtensorMap tmq,
                                                              const __grid_constant__ CUtensorMap tmk) {
   using namespace tc;
@@ -200,7 +228,8 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
     const float* lse_p = p.lse + q_row * p.lse_stride_t + (int64_t)kh * G * p.lse_stride_h;
     const int64_t Tq = p.meta.piece_cu[p.meta.n_pieces];
     TopList lst;
-    lst.init();
+    PackedList pl;
+    if (PACKED) pl.init(); else lst.init();
     // Pooling is linear, so every head's probabilities go straight into the tile's 31 block sums (block i = columns
     // 4i .. 4i+4 with weights 1 2 2 2 1): 32 accumulators per thread instead of 128.
     float blk[32];
@@ -259,7 +288,18 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
           if (p.quant == 0) reinterpret_cast<float*>(p.probs)[a] = pv;
           else reinterpret_cast<__half*>(p.probs)[a] = __float2half_rn(pv);
         }
-        if (bi >= ni && bi <= nk - nl) lst.insert_newer(pv, bi);
+        const bool cand = bi >= ni && bi <= nk - nl;
+        if (PACKED) {
+          // most candidates lose against the list's last entry once a few tiles have been seen: the warp skips the
+          // insertion code unless one of its lanes needs it
+          const uint32_t ck = PackedList::key(pv, bi);
+          const bool need = cand && pl.wants(ck);
+          if (__any_sync(0xffffffffu, need)) {
+            if (need) pl.insert(ck);
+          }
+        } else if (cand) {
+          lst.insert_newer(pv, bi);
+        }
       }
     }
     // ---- merge the other groups' lists into group 0's and write the row
@@ -270,8 +310,12 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
     if (wg > 0) {
 #pragma unroll
       for (int k = 0; k < kList; ++k) {
-        mv[((wg - 1) * kList + k) * 128 + t] = lst.v[k];
-        mi[((wg - 1) * kList + k) * 128 + t] = lst.i[k];
+        if (PACKED) {
+          mi[((wg - 1) * kList + k) * 128 + t] = (int)pl.k[k];
+        } else {
+          mv[((wg - 1) * kList + k) * 128 + t] = lst.v[k];
+          mi[((wg - 1) * kList + k) * 128 + t] = lst.i[k];
+        }
       }
     }
     named_barrier(1, 128 * NW);
@@ -279,7 +323,14 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
 #pragma unroll 1
       for (int g = 0; g < NW - 1; ++g) {
 #pragma unroll
-        for (int k = 0; k < kList; ++k) lst.insert(mv[(g * kList + k) * 128 + t], mi[(g * kList + k) * 128 + t]);
+        for (int k = 0; k < kList; ++k) {
+          if (PACKED) {
+            const uint32_t ck = (uint32_t)mi[(g * kList + k) * 128 + t];
+            if (pl.wants(ck)) pl.insert(ck);
+          } else {
+            lst.insert(mv[(g * kList + k) * 128 + t], mi[(g * kList + k) * 128 + t]);
+          }
+        }
       }
       if (tok_ok) {
         const int n_free = max(0, min(top_n, nk + 1) - ni - nl);
@@ -287,7 +338,7 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
         for (int s = 0; s < ni; ++s) out[s] = (s <= nk) ? s : p.ignore_index;
         for (int s = 0; s < nl; ++s) out[ni + s] = (ni + s <= nk) ? nk - s : p.ignore_index;
 #pragma unroll
-        for (int r = 0; r < kList; ++r) out[ni + nl + r] = (r < n_free) ? lst.i[r] : p.ignore_index;
+        for (int r = 0; r < kList; ++r) out[ni + nl + r] = (r < n_free) ? (PACKED ? pl.block(r) : lst.i[r]) : p.ignore_index;
       }
     }
   }
@@ -312,15 +363,17 @@ int launch_slc_topk_tc(const NsaTopkParams* p, int64_t q_rows, int64_t ck_rows, 
   }
   const int D = p->D;
   size_t smem = (size_t)7 * 128 * D * 2 + 256;
-  cudaError_t e = (D == 128) ? cudaFuncSetAttribute(slc_topk_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                             : cudaFuncSetAttribute(slc_topk_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // block indices must fit the 16 bits of a packed list entry; longer sequences compare (value, index) pairs
+  const bool packed = p->quant != 0 && (p->meta.x_maxlen + p->hp.block_size - 1) / p->hp.block_size < 0xffff && p->meta.x_maxlen > 0;
+  auto kern = (D == 128) ? (packed ? slc_topk_tc_kernel<128, true> : slc_topk_tc_kernel<128, false>)
+                         : (packed ? slc_topk_tc_kernel<64, true> : slc_topk_tc_kernel<64, false>);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("slc_topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
   dim3 grid((p->meta.max_piece_len + 127) / 128, p->meta.n_pieces, p->KH);
-  if (D == 128) slc_topk_tc_kernel<128><<<grid, 448, smem, st>>>(*p, tmq, tmk);
-  else slc_topk_tc_kernel<64><<<grid, 448, smem, st>>>(*p, tmq, tmk);
+  kern<<<grid, 448, smem, st>>>(*p, tmq, tmk);
   return check_launch("slc_topk");
 }
 
