@@ -73,29 +73,63 @@ struct TopList {
   }
 };
 
-// The same list for the half-precision scoring modes, where a score is 16 bits: one sortable word per entry,
-// (half bits << 16) | (0xffff - block), so that a larger word means a better entry (higher score, then lower block index)
-// and an insertion moves 13 registers instead of 26.  Scores are non-negative, so their half bits order like the values;
-// 0 marks an empty entry (a real entry has a block index below 0xffff).
+// The list for the half-precision scoring modes, where a score is 16 bits: one sortable word per entry,
+// (half bits << 16) | (0xffff - block), so that a larger word means a better entry (higher score, then lower block index).
+// Scores are non-negative, so their half bits order like the values; 0 marks an empty entry (a real entry has a block
+// index below 0xffff).  With one-word entries the list is maintained by sorting networks instead of insertions: a tile's
+// 32 candidate words are sorted (bitonic, 240 max/min pairs on registers with compile-time indices), and the best 16 of
+// list and candidates are max(list[j], candidates[15 - j]), a bitonic sequence that 32 more pairs put back in order.  No
+// branches, no divergence between the lanes of a warp, no long dependent chains: the per-entry insertion it replaces
+// (31 candidates x ~70 dependent instructions, taken whenever ANY lane of the warp needed it) cost a quarter of the
+// kernel's time.  The list keeps 16 entries (a power of two for the networks); the first 13 are the result.
 struct PackedList {
-  uint32_t k[kList];
+  static constexpr int N = 16;
+  uint32_t k[N];
   __device__ __forceinline__ void init() {
 #pragma unroll
-    for (int j = 0; j < kList; ++j) k[j] = 0u;
+    for (int j = 0; j < N; ++j) k[j] = 0u;
   }
   static __device__ __forceinline__ uint32_t key(float rounded_score, int blk) {
     return ((uint32_t)__half_as_ushort(__float2half_rn(rounded_score)) << 16) | (uint32_t)(0xffff - blk);
   }
-  __device__ __forceinline__ bool wants(uint32_t ck) const { return ck > k[kList - 1]; }
-  __device__ __forceinline__ void insert(uint32_t ck) {   // caller has checked wants(ck); keys are unique
-    int pos = 0;
+  template <int LEN>
+  static __device__ __forceinline__ void bitonic_merge_desc(uint32_t (&c)[LEN]) {   // c bitonic -> c descending
 #pragma unroll
-    for (int j = 0; j < kList; ++j) pos += (k[j] > ck) ? 1 : 0;
+    for (int j = LEN / 2; j > 0; j >>= 1) {
 #pragma unroll
-    for (int j = kList - 1; j >= 0; --j) {
-      const uint32_t from_left = j > 0 ? k[j - 1] : 0u;
-      k[j] = (j == pos) ? ck : ((j > pos) ? from_left : k[j]);
+      for (int i = 0; i < LEN; ++i) {
+        const int l = i ^ j;
+        if (l > i) {
+          const uint32_t a = c[i], b = c[l];
+          c[i] = max(a, b);
+          c[l] = min(a, b);
+        }
+      }
     }
+  }
+  static __device__ __forceinline__ void sort32_desc(uint32_t (&c)[32]) {
+#pragma unroll
+    for (int kk = 2; kk <= 32; kk <<= 1) {
+#pragma unroll
+      for (int j = kk >> 1; j > 0; j >>= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int l = i ^ j;
+          if (l > i) {
+            const uint32_t a = c[i], b = c[l];
+            const bool desc = (i & kk) == 0;
+            c[i] = desc ? max(a, b) : min(a, b);
+            c[l] = desc ? min(a, b) : max(a, b);
+          }
+        }
+      }
+    }
+  }
+  // b: 16 words in descending order (e.g. the head of a sorted candidate array, or another list)
+  __device__ __forceinline__ void merge(const uint32_t* b) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) k[j] = max(k[j], b[N - 1 - j]);
+    bitonic_merge_desc<N>(k);
   }
   __device__ __forceinline__ int block(int j) const { return 0xffff - (int)(k[j] & 0xffffu); }
 };
@@ -277,42 +311,43 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
         }
       }
       // ---- this tile's 31 blocks
+      if (PACKED) {
+        uint32_t cand[32];
 #pragma unroll
-      for (int i = 0; i < 31; ++i) {
-        float pv = blk[i];
-        if (p.quant == 1) pv = __half2float(__float2half_rn(pv));
-        else if (p.quant == 2) pv = __half2float(__float2half_rn(pv * pv * pv));
-        const int bi = 31 * j + i;
-        if (p.probs && tok_ok && bi < (int)p.probs_stride_t) {
-          const int64_t a = ((int64_t)kh * Tq + q_row) * p.probs_stride_t + bi;
-          if (p.quant == 0) reinterpret_cast<float*>(p.probs)[a] = pv;
-          else reinterpret_cast<__half*>(p.probs)[a] = __float2half_rn(pv);
+        for (int i = 0; i < 31; ++i) {
+          float pv = blk[i];
+          pv = __half2float(__float2half_rn(p.quant == 2 ? pv * pv * pv : pv));
+          const int bi = 31 * j + i;
+          if (p.probs && tok_ok && bi < (int)p.probs_stride_t)
+            reinterpret_cast<__half*>(p.probs)[((int64_t)kh * Tq + q_row) * p.probs_stride_t + bi] = __float2half_rn(pv);
+          cand[i] = (bi >= ni && bi <= nk - nl) ? PackedList::key(pv, bi) : 0u;
         }
-        const bool cand = bi >= ni && bi <= nk - nl;
-        if (PACKED) {
-          // most candidates lose against the list's last entry once a few tiles have been seen: the warp skips the
-          // insertion code unless one of its lanes needs it
-          const uint32_t ck = PackedList::key(pv, bi);
-          const bool need = cand && pl.wants(ck);
-          if (__any_sync(0xffffffffu, need)) {
-            if (need) pl.insert(ck);
-          }
-        } else if (cand) {
-          lst.insert_newer(pv, bi);
+        cand[31] = 0u;
+        PackedList::sort32_desc(cand);
+        pl.merge(cand);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 31; ++i) {
+          const float pv = blk[i];
+          const int bi = 31 * j + i;
+          if (p.probs && tok_ok && bi < (int)p.probs_stride_t)
+            reinterpret_cast<float*>(p.probs)[((int64_t)kh * Tq + q_row) * p.probs_stride_t + bi] = pv;
+          if (bi >= ni && bi <= nk - nl) lst.insert_newer(pv, bi);
         }
       }
     }
     // ---- merge the other groups' lists into group 0's and write the row
     __syncwarp();
     float* mv = reinterpret_cast<float*>(smem_raw);            // the Q stages are idle now (all MMAs have completed)
-    int* mi = reinterpret_cast<int*>(smem_raw + (NW - 1) * 128 * kList * 4);
+    int* mi = reinterpret_cast<int*>(smem_raw + (NW - 1) * 128 * 16 * 4);
     named_barrier(1, 128 * NW);
     if (wg > 0) {
+      if (PACKED) {
 #pragma unroll
-      for (int k = 0; k < kList; ++k) {
-        if (PACKED) {
-          mi[((wg - 1) * kList + k) * 128 + t] = (int)pl.k[k];
-        } else {
+        for (int k = 0; k < PackedList::N; ++k) mi[((wg - 1) * PackedList::N + k) * 128 + t] = (int)pl.k[k];
+      } else {
+#pragma unroll
+        for (int k = 0; k < kList; ++k) {
           mv[((wg - 1) * kList + k) * 128 + t] = lst.v[k];
           mi[((wg - 1) * kList + k) * 128 + t] = lst.i[k];
         }
@@ -322,14 +357,14 @@ __global__ void __launch_bounds__(448, 1) slc_topk_tc_kernel(NsaTopkParams p, co
     if (wg == 0) {
 #pragma unroll 1
       for (int g = 0; g < NW - 1; ++g) {
+        if (PACKED) {
+          uint32_t other[PackedList::N];
 #pragma unroll
-        for (int k = 0; k < kList; ++k) {
-          if (PACKED) {
-            const uint32_t ck = (uint32_t)mi[(g * kList + k) * 128 + t];
-            if (pl.wants(ck)) pl.insert(ck);
-          } else {
-            lst.insert(mv[(g * kList + k) * 128 + t], mi[(g * kList + k) * 128 + t]);
-          }
+          for (int k = 0; k < PackedList::N; ++k) other[k] = (uint32_t)mi[(g * PackedList::N + k) * 128 + t];
+          pl.merge(other);
+        } else {
+#pragma unroll
+          for (int k = 0; k < kList; ++k) lst.insert(mv[(g * kList + k) * 128 + t], mi[(g * kList + k) * 128 + t]);
         }
       }
       if (tok_ok) {
