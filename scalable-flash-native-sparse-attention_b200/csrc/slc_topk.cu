@@ -1,7 +1,8 @@
 // Block-importance scores and top-n selection, fused (no [KH,T,blocks] score tensor is materialised).
 //
-// One warp owns one query token and the (<= 16) query heads of one kv head as the 16 rows of an MMA tile;
-// the 8 warps of a CTA (8 consecutive tokens) share the compressed-key tiles staged in shared memory.
+// One warp owns one query token; the query heads of one kv head are the 16 rows of an MMA tile, taken 16 at a time
+// (HG head groups: the probabilities of all groups are summed before the pooling, so the selection is shared by every
+// head of the kv head).  The 8 warps of a CTA (8 consecutive tokens) share the compressed-key tiles in shared memory.
 // Per 64 compressed rows:  P_cmp[j] = sum_heads exp2(q.k_j*c - lse_head)  (0 where row j is not yet visible),
 // pooled into 16 selection blocks  P_slc[b] = P_cmp[4b-1] + 2(P_cmp[4b]+P_cmp[4b+1]+P_cmp[4b+2]) + P_cmp[4b+3],
 // and the warp keeps a running, descending list of the best free blocks (ties: lower block index first).
@@ -10,13 +11,13 @@
 
 namespace nsa {
 
-template <int D>
-__global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
+template <int D, int HG>
+__global__ void __launch_bounds__(256, HG == 1 ? 2 : 1) slc_topk_kernel(NsaTopkParams p) {
   constexpr int BN = 64, CH = D / 8, KS = D / 16, TOK = 8;
   extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t sQ = smem_u32(smem);
-  const uint32_t sK = sQ + 128 * D * 2;
-  float* pc_all = reinterpret_cast<float*>(smem + 128 * D * 2 + 2 * BN * D * 2);
+  const uint32_t sQ = smem_u32(smem);                 // [HG][8 tokens x 16 heads][D]
+  const uint32_t sK = sQ + HG * 128 * D * 2;
+  float* pc_all = reinterpret_cast<float*>(smem + HG * 128 * D * 2 + 2 * BN * D * 2);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.QH / p.KH;
@@ -36,12 +37,13 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   {
     const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)(pc.q_start + t0) * p.q_stride_t +
                               (int64_t)kh * G * D;
-    for (int i = tid; i < 128 * CH; i += 256) {
-      int r = i / CH, c = i % CH;
-      int tok = r >> 4, g = r & 15;
+    for (int i = tid; i < HG * 128 * CH; i += 256) {
+      int hg = i / (128 * CH), j = i - hg * 128 * CH;
+      int r = j / CH, c = j % CH;
+      int tok = r >> 4, g = 16 * hg + (r & 15);
       bool ok = tok < ntok && g < G;
       const __nv_bfloat16* src = qb + (ok ? (int64_t)tok * p.q_stride_t + g * D : 0) + c * 8;
-      cp_async16(sQ + tile_off<D>(r, c), src, ok);
+      cp_async16(sQ + hg * 128 * D * 2 + tile_off<D>(r, c), src, ok);
     }
     cp_async_commit();
   }
@@ -60,9 +62,11 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   cp_async_wait<1>();
   __syncthreads();
 
-  uint32_t qf[KS][4];
+  uint32_t qf[KS][4];   // one head group: loaded once; several: re-read from shared memory for every key tile
+  if (HG == 1) {
 #pragma unroll
-  for (int kk = 0; kk < KS; ++kk) load_a_frag<D>(qf[kk], sQ, warp * 16, kk, lane);
+    for (int kk = 0; kk < KS; ++kk) load_a_frag<D>(qf[kk], sQ, warp * 16, kk, lane);
+  }
 
   const int g_ = lane >> 2, c_ = lane & 3;
   const bool tok_ok = warp < ntok;
@@ -72,11 +76,16 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
   const int nk = t_abs >= 0 ? t_abs / bs : -1;  // a padded row (empty sequence) selects nothing
   const int n_free = tok_ok ? max(0, min(top_n, nk + 1) - ni - nl) : 0;
   const float c2 = p.sm_scale * 1.4426950408889634f;
-  // -lse of this thread's two rows (heads g_ and g_+8); rows beyond G contribute nothing
-  float nl_lo = 0.f, nl_hi = 0.f;
-  const bool h_lo = tok_ok && g_ < G, h_hi = tok_ok && (g_ + 8) < G;
-  if (h_lo) nl_lo = -p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_) * p.lse_stride_h];
-  if (h_hi) nl_hi = -p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + g_ + 8) * p.lse_stride_h];
+  // -lse of this thread's two rows of every head group (heads 16hg + g_ and + 8); rows beyond G contribute nothing
+  float nl_lo[HG], nl_hi[HG];
+  bool h_lo[HG], h_hi[HG];
+#pragma unroll
+  for (int hg = 0; hg < HG; ++hg) {
+    h_lo[hg] = tok_ok && 16 * hg + g_ < G;
+    h_hi[hg] = tok_ok && 16 * hg + g_ + 8 < G;
+    nl_lo[hg] = h_lo[hg] ? -p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + 16 * hg + g_) * p.lse_stride_h] : 0.f;
+    nl_hi[hg] = h_hi[hg] ? -p.lse[q_row * p.lse_stride_t + (int64_t)(kh * G + 16 * hg + g_ + 8) * p.lse_stride_h] : 0.f;
+  }
 
   float* pcw = pc_all + warp * 72;  // [0] = carry (compressed row kv0-1), [1..64] = this tile
   float my_v = -1.f;                // running list entry of this lane (lanes < n_free)
@@ -92,29 +101,44 @@ __global__ void __launch_bounds__(256, 2) slc_topk_kernel(NsaTopkParams p) {
     const uint32_t tK = sK + (it & 1) * BN * D * 2;
     const int kv0 = it * BN;
     if (tok_ok) {
-      float s[8][4];
+      float v0s[8], v1s[8];   // per compressed row: probabilities summed over the heads of all groups
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int nt = 0; nt < 8; ++nt) v0s[nt] = v1s[nt] = 0.f;
 #pragma unroll
-      for (int kk = 0; kk < KS; ++kk) {
+      for (int hg = 0; hg < HG; ++hg) {
+        if (HG > 1) {
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
-          uint32_t b[4];
-          load_b_frag_nk<D>(b, tK, np * 16, kk, lane);
-          mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
-          mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+          for (int kk = 0; kk < KS; ++kk) load_a_frag<D>(qf[kk], sQ + hg * 128 * D * 2, warp * 16, kk, lane);
+        }
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            uint32_t b[4];
+            load_b_frag_nk<D>(b, tK, np * 16, kk, lane);
+            mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+            mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          int col = kv0 + nt * 8 + 2 * c_;
+          float e0 = (h_lo[hg] && col < nvis) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo[hg])) : 0.f;
+          float e1 = (h_lo[hg] && col + 1 < nvis) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo[hg])) : 0.f;
+          float e2 = (h_hi[hg] && col < nvis) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi[hg])) : 0.f;
+          float e3 = (h_hi[hg] && col + 1 < nvis) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi[hg])) : 0.f;
+          v0s[nt] += e0 + e2;
+          v1s[nt] += e1 + e3;
         }
       }
       if (lane == 0) pcw[0] = pcw[64];
       __syncwarp();
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        int col = kv0 + nt * 8 + 2 * c_;
-        float e0 = (h_lo && col < nvis) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo)) : 0.f;
-        float e1 = (h_lo && col + 1 < nvis) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo)) : 0.f;
-        float e2 = (h_hi && col < nvis) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi)) : 0.f;
-        float e3 = (h_hi && col + 1 < nvis) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi)) : 0.f;
-        float v0 = e0 + e2, v1 = e1 + e3;
+        float v0 = v0s[nt], v1 = v1s[nt];
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
           v0 += __shfl_xor_sync(0xffffffffu, v0, o);
@@ -224,20 +248,22 @@ extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
     int rc = launch_slc_topk_tc(p, p->q_rows, p->ck_rows, (cudaStream_t)stream);
     if (rc <= 0) return rc;
   }
-  NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE,
-              "slc_topk: this configuration runs on the warp-MMA kernel, which takes at most 16 query heads per kv head (got %d)",
-              p->QH / p->KH);
+  const int G = p->QH / p->KH, HG = G <= 16 ? 1 : (G <= 32 ? 2 : 4);
+  NSA_REQUIRE(G <= 64, NSA_ERR_UNSUPPORTED_SHAPE, "slc_topk: at most 64 query heads per kv head (got %d)", G);
   const int D = p->D;
-  size_t smem = (size_t)128 * D * 2 + 2 * 64 * D * 2 + 8 * 72 * sizeof(float);
-  cudaError_t e = cudaSuccess;
-  if (D == 128) e = cudaFuncSetAttribute(slc_topk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  else e = cudaFuncSetAttribute(slc_topk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  size_t smem = (size_t)HG * 128 * D * 2 + 2 * 64 * D * 2 + 8 * 72 * sizeof(float);
+  dim3 grid((p->meta.max_piece_len + 7) / 8, p->meta.n_pieces, p->KH);
+  auto go = [&](auto kernel) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(*p);
+    return e;
+  };
+  cudaError_t e;
+  if (D == 128) e = HG == 1 ? go(slc_topk_kernel<128, 1>) : (HG == 2 ? go(slc_topk_kernel<128, 2>) : go(slc_topk_kernel<128, 4>));
+  else e = HG == 1 ? go(slc_topk_kernel<64, 1>) : (HG == 2 ? go(slc_topk_kernel<64, 2>) : go(slc_topk_kernel<64, 4>));
   if (e != cudaSuccess) {
     set_error("slc_topk: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
-  dim3 grid((p->meta.max_piece_len + 7) / 8, p->meta.n_pieces, p->KH);
-  if (D == 128) slc_topk_kernel<128><<<grid, 256, smem, (cudaStream_t)stream>>>(*p);
-  else slc_topk_kernel<64><<<grid, 256, smem, (cudaStream_t)stream>>>(*p);
   return check_launch("slc_topk");
 }

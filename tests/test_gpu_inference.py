@@ -165,6 +165,47 @@ def test_prefill_chunked_prefill_and_decode(QH, KH, D):
     assert float(o[-1].float().abs().max()) == 0.0      # padding row: no tokens -> zeros
 
 
+@pytest.mark.parametrize("QH,KH,D", [(32, 1, 128), (64, 2, 64), (24, 1, 64)])
+def test_more_than_16_query_heads_per_kv_head_on_the_paged_path(QH, KH, D):
+    """The reference loops groups of min(G, 16) heads in its paged kernels; here the scorer sums the groups' probabilities
+    before the pooling, the attention kernels run the groups as separate tiles, and nsa_decode takes the op-by-op path."""
+    from flash_nsa import nsa_prefill, nsa_decode
+    lens = [520, 203]
+    seqs = _seqs(lens, QH, KH, D, seed=21 + QH)
+    B = len(lens)
+    cache = Cache([L + 1 for L in lens], KH, D, seed=6)
+    for b, s in enumerate(seqs):
+        cache.store(b, s["k"][:lens[b] - 1], s["v"][:lens[b] - 1])
+    cache.cuda()
+    end = [L - 1 for L in lens]
+    y_len = [max((e - 32) // 16 + 1, 0) for e in end]
+    x_cu = torch.tensor([0, end[0], end[0] + end[1]], dtype=torch.int32, device="cuda")
+    y_cu = torch.tensor([0, y_len[0], y_len[0] + y_len[1]], dtype=torch.int32, device="cuda")
+    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    q = torch.cat([seqs[b]["q"][:end[b]] for b in range(B)]).cuda()
+    w = torch.cat([seqs[b]["w"][:end[b]] for b in range(B)]).cuda()
+    o = nsa_prefill(q, cache.k, cache.v, w, x_cu, y_cu, max(end), max(y_len), torch.tensor(end, dtype=torch.int32, device="cuda"),
+                    cache.block_tables, slots, cache.cmp_block_tables)
+    off = 0
+    for b in range(B):
+        assert _bulk_ok(o[off:off + end[b]], _oracle(seqs[b], end[b])), f"prefill seq {b}"
+        off += end[b]
+    # decode the last token of every sequence
+    for b, s in enumerate(seqs):
+        p = lens[b] - 1
+        pg = int(cache.block_tables[b, p // PAGE])
+        cache.k[pg, p % PAGE] = s["k"][p].cuda()
+        cache.v[pg, p % PAGE] = s["v"][p].cuda()
+    slot = [cache.cmp_slot(b, (L - 32) // 16) if (L % 16 == 0 and L >= 32) else -1 for b, L in enumerate(lens)]
+    qd = torch.stack([seqs[b]["q"][lens[b] - 1] for b in range(B)]).cuda()
+    wd = torch.stack([seqs[b]["w"][lens[b] - 1] for b in range(B)]).cuda()
+    od = nsa_decode(qd, cache.k, cache.v, wd, torch.tensor(lens, dtype=torch.int32, device="cuda"), cache.block_tables,
+                    torch.tensor(slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+    for b in range(B):
+        ref = _oracle(seqs[b], lens[b])[-1:]
+        assert (od[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"decode seq {b}"
+
+
 def test_decode_writes_the_new_compressed_row():
     from flash_nsa.inference import kv_mean_pooling_decode
     KH, D = 2, 64
