@@ -1003,7 +1003,7 @@ def kernel_breakdown(q, k, v, w, do, lens):
         slc_o, slc_lse = slc_attn_fwd(qd, kd, vd, topk)
         swa_o, swa_lse = swa_fwd(qd, kd, vd)
         from flash_nsa.ops.topk import backward_index_sizes
-        rr, ir = backward_index_sizes(qd.size(1) // kd.size(1), qd.size(2), qd.size(0))
+        rr, ir = backward_index_sizes(qd.size(1) // kd.size(1), qd.size(2), qd.size(0), NSAHelper.k_maxlen, topk.size(-1))
         index = get_bind_from_find(topk, range_rows=rr, item_rows=ir)
         dq = torch.empty_like(qd)
         dkf, dvf = torch.zeros(kd.shape, device=kd.device), torch.zeros(vd.shape, device=vd.device)

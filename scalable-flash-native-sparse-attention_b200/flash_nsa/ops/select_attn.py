@@ -45,7 +45,8 @@ def slc_attn_bwd(q, k, v, topk, o, lse, do, dq=None, dk=None, dv=None, sm_scale=
     if not have_delta:
         delta = torch.empty_like(lse)
     if T > 0:
-        auto_r, auto_i = backward_index_sizes(QH // k.size(1), D, T)
+        auto_r, auto_i = backward_index_sizes(QH // k.size(1), D, T, helper.cp_k_maxlen if is_cp(helper) else helper.k_maxlen,
+                                              topk.size(-1))
         range_rows = auto_r if range_rows is None else range_rows
         item_rows = auto_i if item_rows is None else item_rows
         index = get_bind_from_find(topk, helper=helper, range_rows=range_rows, item_rows=item_rows)
