@@ -12,9 +12,14 @@
 //   0. the window of 32 tokens ending at the new token is pooled into the new compressed K/V row (when it completes one)
 //   1. compressed attention: tiles of compressed K/V round-robin over the six consumers            -> cmp_o, lse
 //   2. block scores: the same K tiles again (from L2), P[j] = sum_heads exp2(s - lse)               -> pcm[]
-//   3. top-n on consumer 0 (pool 4 -> 1 + the row before, then rounds of warp-wide arg-max; ties: lowest block index) WHILE
-//   4. consumers 4-5 work through the sliding-window tiles and consumers 1-3 through the forced blocks; then the free
-//      blocks round-robin over consumers 0-3 (the producer waits for the selection before it fetches them)
+//   3. top-n (pool 4 -> 1 + the row before; ties: lowest block index): up to 256 blocks by rank counting on the 128
+//      threads of consumers 0-3 (rank = number of candidates that beat mine), longer contexts by rounds of warp-wide
+//      arg-max on consumer 0
+//   4. consumers 1-3 work through the forced blocks meanwhile; then the free blocks round-robin over consumers 0-3 (the
+//      producer waits for the selection before it fetches them)
+//   W. consumers 4-5 do the sliding-window tiles once their share of 1 is stored: these depend on nothing, and their
+//      jobs are spread through the list from phase 2 on (one after every two compressed tiles), so that their loads fill
+//      the time in which the others synchronise, merge and select and would leave the memory system idle
 //   5. o = sigmoid(w0) cmp_o + sigmoid(w1) slc_o + sigmoid(w2) swa_o
 // Partial softmax states are merged through shared memory after 1 and after 4; that region holds the score arrays in
 // between.  Bytes read per (sequence, kv head): compressed K twice and V once, 16 selected blocks and <= 9 window tiles.
@@ -23,13 +28,16 @@
 
 namespace nsa {
 
-constexpr int RING_NC = 6;        // consumer warps
+// RING_NC consumer warps, of which 0..RING_NS-1 do the compressed and selected branches and the others the window (all share
+// the compressed tiles).  Built as 6 / 4 with a ring of five slots, one CTA per SM; 3 / 2 with two slots and two CTAs per SM
+// measured the same within 3 % (config 4), so the time is not a matter of how many CTAs an SM holds.
+constexpr int RING_WIN_ROWS = 16;   // window tiles at most
 constexpr int JOB_CMP_KV = 0, JOB_CMP_K = 1, JOB_WIN = 2, JOB_SLC = 3;
 
 __host__ __device__ constexpr int job_pack(int type, int cons, int idx) { return type | (cons << 2) | (idx << 5); }
 
-template <int D>
-__global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
+template <int D, int RING_NC, int RING_NS>
+__global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     decode_ring_kernel(NsaDecodeParams p, int n_slots, int job_cap, const __grid_constant__ CUtensorMap tmk,
                        const __grid_constant__ CUtensorMap tmv) {
   using namespace tc;
@@ -47,7 +55,13 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
   float* lse_s = cmp_o_s + 16 * D;                                // [16]
   int* sel = reinterpret_cast<int*>(lse_s + 16);                  // [32]
   int* jobs = sel + 32;                                           // [job_cap]
-  const uint32_t bars = (smem_u32(jobs + job_cap) + 7u) & ~7u;    // full[n_slots], empty[n_slots], sel_ready
+  // first cache row of a job's tile, by type: compressed tiles [ct_cap], window tiles [RING_WIN_ROWS], selected slots [32]
+  int* rows = jobs + job_cap;
+  int* rows_win = rows + ((p.y_cap + 63) >> 6);
+  int* rows_slc = rows_win + RING_WIN_ROWS;
+  float* fac = reinterpret_cast<float*>(rows_slc + 32);          // [RING_NC][16] merge weights, then [3][16] gates
+  int* marks = reinterpret_cast<int*>(fac + (RING_NC + 3) * 16);  // [2] end of the phase-1 / phase-2 part of the job list
+  const uint32_t bars = (smem_u32(marks + 2) + 7u) & ~7u;         // full[n_slots], empty[n_slots], sel_ready
   auto full = [&](int s) { return bars + 8 * s; };
   auto empty = [&](int s) { return bars + 8 * (n_slots + s); };
   const uint32_t sel_ready = bars + 16 * n_slots;
@@ -55,7 +69,9 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g_ = lane >> 2, c_ = lane & 3;
-  const int b = blockIdx.x, kh = blockIdx.y;
+  // the kv heads of a sequence are neighbours in launch order: they read the same token rows (window, forced blocks,
+  // compressed rows) at about the same time, 256 bytes each out of the same 2 KB of DRAM
+  const int kh = blockIdx.x, b = blockIdx.y;
   const int G = p.QH / p.KH;
   const int ctx = p.context_lens[b];
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)b * p.o_stride_t + (int64_t)kh * G * D;
@@ -95,6 +111,10 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
   const int n_jobs = 2 * n_ct + nf + n_wt + n_free;
 
   // ---- set-up: barriers, the job list, the new compressed row
+  if (tid == RING_NC * 32) {
+    tma::prefetch_map(&tmk);
+    tma::prefetch_map(&tmv);
+  }
   if (tid == 0) {
     for (int s = 0; s < n_slots; ++s) {
       mbar_init(full(s), 1);
@@ -103,18 +123,36 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
     mbar_init(sel_ready, 1);
     asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(issued), "r"(0) : "memory");
     fence_mbar_init();
-    // job list: (type, consumer, index).  Phase 4 is ordered so that the ring always holds work for both consumer groups:
-    // forced blocks (consumers 1-3), two window tiles (4-5), then two selected blocks for every further window tile.
-    int n = 0;
-    for (int i = 0; i < n_ct; ++i) jobs[n++] = job_pack(JOB_CMP_KV, i % RING_NC, i);
-    for (int i = 0; i < n_ct; ++i) jobs[n++] = job_pack(JOB_CMP_K, i % RING_NC, i);
-    for (int s = 0; s < nf; ++s) jobs[n++] = job_pack(JOB_SLC, 1 + s % 3, s);
-    int wi = 0, fi = 0;
-    for (; wi < min(n_wt, 2); ++wi) jobs[n++] = job_pack(JOB_WIN, 4 + (wi & 1), wi);
-    while (wi < n_wt || fi < n_free) {
-      for (int u = 0; u < 2 && fi < n_free; ++u, ++fi) jobs[n++] = job_pack(JOB_SLC, fi & 3, nf + fi);
-      if (wi < n_wt) { jobs[n++] = job_pack(JOB_WIN, 4 + (wi & 1), wi); ++wi; }
+  }
+  // The first cache row of every tile whose place is known now: the page-table look-ups of all tiles are in flight at
+  // once (the rows of the free blocks are filled in by the selection).
+  for (int i = tid; i < n_ct + n_wt + nf; i += blockDim.x) {
+    if (i < n_ct) rows[i] = (int)cmprow(i << 6);
+    else if (i < n_ct + n_wt) rows_win[i - n_ct] = (int)tokrow(w_k0 + ((i - n_ct) << 6));
+    else {
+      const int sidx = i - n_ct - n_wt;
+      rows_slc[sidx] = (int)tokrow(max(0, min(sidx < ni ? sidx : nk - (sidx - ni), nk)) << 6);
     }
+  }
+  // Job list: (type, consumer, index) in the order the producer fetches them.
+  if (tid == 32) {
+    int n = 0, wi = 0;
+    auto win = [&]() {
+      if (wi < n_wt) {
+        jobs[n++] = job_pack(JOB_WIN, RING_NS + wi % (RING_NC - RING_NS), wi);
+        ++wi;
+      }
+    };
+    for (int i = 0; i < n_ct; ++i) jobs[n++] = job_pack(JOB_CMP_KV, i % RING_NC, i);
+    marks[0] = n;
+    for (int i = 0; i < n_ct; ++i) {
+      jobs[n++] = job_pack(JOB_CMP_K, i % RING_NC, i);
+      if (i & 1) win();
+    }
+    marks[1] = n;
+    for (int sidx = 0; sidx < nf; ++sidx) jobs[n++] = job_pack(JOB_SLC, RING_NS > 1 ? 1 + sidx % (RING_NS - 1) : 0, sidx);
+    while (wi < n_wt) win();
+    for (int fi = 0; fi < n_free; ++fi) jobs[n++] = job_pack(JOB_SLC, fi % RING_NS, nf + fi);
   }
   {
     const int slot = p.slot_mapping ? p.slot_mapping[b] : -1;
@@ -147,16 +185,9 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
         const int job = jobs[j], type = job & 3, idx = job >> 5;
         const int s = j % n_slots;
         if (j >= n_slots && !mbar_wait(empty(s), ((j / n_slots) - 1) & 1, &budget)) timed_out = true;
-        int row;
-        if (type == JOB_CMP_KV || type == JOB_CMP_K) {
-          row = (int)cmprow(idx << 6);
-        } else if (type == JOB_WIN) {
-          row = (int)tokrow(w_k0 + (idx << 6));
-        } else {
-          if (idx >= nf && idx == nf && !mbar_wait(sel_ready, 0, &budget)) timed_out = true;   // first free block: the list is there
-          const int blk = idx >= nf ? sel[idx] : (idx < ni ? idx : nk - (idx - ni));
-          row = (int)tokrow(max(0, min(blk, nk)) << 6);
-        }
+        // the first free block: the selection warp has written the list and the rows of all free blocks
+        if (type == JOB_SLC && idx == nf && !mbar_wait(sel_ready, 0, &budget)) timed_out = true;
+        const int row = type <= JOB_CMP_K ? rows[idx] : (type == JOB_WIN ? rows_win[idx] : rows_slc[idx]);
         const uint32_t dst = ring + (uint32_t)s * 2 * TILE_BYTES;
         tma::expect_tx(full(s), type == JOB_CMP_K ? TILE_BYTES : 2 * TILE_BYTES);
 #pragma unroll
@@ -195,200 +226,253 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), 1)
         mbar_arrive(empty(j % n_slots));
       }
     };
-    // merge the states of consumers [w0, w0+nw) for row r, column c: the normalised value, optionally the lse
-    auto merged = [&](int w0, int nw, int r, int c, float* lse_out) -> float {
+    // merge weights of the states of consumers [w0, w0+nw) for row r: fac[w][r] = exp2(m_w - M) / L (0 for an empty row);
+    // returns the merged log-sum-exp
+    auto merge_weights = [&](int w0, int nw, int r) -> float {
       float M = -INFINITY;
       for (int w = 0; w < nw; ++w) M = fmaxf(M, state[(w0 + w) * STATE + r]);
-      if (M == -INFINITY) {
-        if (lse_out) *lse_out = 0.f;
-        return 0.f;
-      }
-      float L = 0.f, O = 0.f;
-      for (int w = 0; w < nw; ++w) {
-        const float* sp = state + (w0 + w) * STATE;
-        const float f = fast_exp2(sp[r] - M);
-        L += sp[16 + r] * f;
-        O += sp[32 + r * D + c] * f;
-      }
-      if (lse_out) *lse_out = L > 0.f ? M + log2f(L) : 0.f;
-      return L > 0.f ? O / L : 0.f;
+      float L = 0.f;
+      if (M != -INFINITY)
+        for (int w = 0; w < nw; ++w) L += state[(w0 + w) * STATE + 16 + r] * fast_exp2(state[(w0 + w) * STATE + r] - M);
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      for (int w = 0; w < nw; ++w) fac[(w0 + w) * 16 + r] = L > 0.f ? fast_exp2(state[(w0 + w) * STATE + r] - M) * inv : 0.f;
+      return L > 0.f ? M + log2f(L) : 0.f;
     };
 
+    constexpr int NST = RING_NS * 32;   // threads of consumers 0-3 (named barrier 2)
+    const int end_a = marks[0], end_b = marks[1];
     int j = 0;
-    // ---- 1. compressed attention
+    // ---- 1. compressed attention (all six consumers)
     {
-      wts::Acc<D> acc;
-      acc.init();
-      for (; j < n_ct; ++j) {
+      wts::Acc<D> ca;
+      ca.init();
+      for (; j < end_a; ++j) {
         if (((jobs[j] >> 2) & 7) != cw) continue;
         const int j0 = (jobs[j] >> 5) << 6;
         wait_job(j);
         const uint32_t bk = ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES;
-        wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int i) { return j0 + i < Y; }, min(64, Y - j0), c2, lane);
+        wts::attend64_smem<D>(ca, qf, bk, bk + TILE_BYTES, [&](int i) { return j0 + i < Y; }, min(64, Y - j0), c2, lane);
         release(j);
       }
-      wts::store_state<D>(acc, state + cw * STATE, lane);
+      wts::store_state<D>(ca, state + cw * STATE, lane);
     }
     named_barrier(1, NCT);
+    if (ctid < 16) lse_s[ctid] = merge_weights(0, RING_NC, ctid);
+    named_barrier(1, NCT);
     for (int idx = ctid; idx < 16 * D; idx += NCT) {
-      const int r = idx / D, c = idx - r * D;
-      float l;
-      cmp_o_s[idx] = merged(0, RING_NC, r, c, &l);
-      if (c == 0) lse_s[r] = l;
+      const int r = idx / D;
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < RING_NC; ++w) o += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+      cmp_o_s[idx] = o;
     }
     named_barrier(1, NCT);   // the states are dead until phase 4 is over: the score arrays live there
 
-    // ---- 2. head-summed probabilities of every compressed row -> pcm[1 + j]
-    {
-      const float nl_lo = (g_ < G) ? -lse_s[g_] : 0.f, nl_hi = (g_ + 8 < G) ? -lse_s[g_ + 8] : 0.f;
-      const bool h_lo = g_ < G, h_hi = g_ + 8 < G;
-      if (ctid == 0) pcm[0] = 0.f;
-      for (; j < 2 * n_ct; ++j) {
-        if (((jobs[j] >> 2) & 7) != cw) continue;
-        const int j0 = (jobs[j] >> 5) << 6;
-        wait_job(j);
-        float s[8][4];
-        wts::scores64<D>(s, qf, ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES, lane);
-        release(j);
+    // ---- 2. head-summed probabilities of every compressed row -> pcm[1 + j]; consumers 4-5 also start on the window
+    wts::Acc<D> acc;   // the state a consumer ends with: selected branch (consumers 0-3) or window (4-5)
+    acc.init();
+    const float nl_lo = (g_ < G) ? -lse_s[g_] : 0.f, nl_hi = (g_ + 8 < G) ? -lse_s[g_ + 8] : 0.f;
+    const bool h_lo = g_ < G, h_hi = g_ + 8 < G;
+    auto window_tile = [&](int jj) {
+      const int k0 = w_k0 + ((jobs[jj] >> 5) << 6);
+      wait_job(jj);
+      const uint32_t bk = ring + (uint32_t)(jj % n_slots) * 2 * TILE_BYTES;
+      wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int x) { return k0 + x >= lo && k0 + x <= t; }, min(64, t - k0 + 1), c2, lane);
+      release(jj);
+    };
+    if (ctid == 0) pcm[0] = 0.f;
+    for (; j < end_b; ++j) {
+      const int job = jobs[j];
+      if (((job >> 2) & 7) != cw) continue;
+      if ((job & 3) == JOB_WIN) {
+        window_tile(j);
+        continue;
+      }
+      const int j0 = (job >> 5) << 6;
+      wait_job(j);
+      float s[8][4];
+      wts::scores64<D>(s, qf, ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES, lane);
+      release(j);
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          const int col = j0 + nt * 8 + 2 * c_;
-          float e0 = (h_lo && col < Y) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo)) : 0.f;
-          float e1 = (h_lo && col + 1 < Y) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo)) : 0.f;
-          float e2 = (h_hi && col < Y) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi)) : 0.f;
-          float e3 = (h_hi && col + 1 < Y) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi)) : 0.f;
-          float v0 = e0 + e2, v1 = e1 + e3;
+      for (int nt = 0; nt < 8; ++nt) {
+        const int col = j0 + nt * 8 + 2 * c_;
+        float e0 = (h_lo && col < Y) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo)) : 0.f;
+        float e1 = (h_lo && col + 1 < Y) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo)) : 0.f;
+        float e2 = (h_hi && col < Y) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi)) : 0.f;
+        float e3 = (h_hi && col + 1 < Y) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi)) : 0.f;
+        float v0 = e0 + e2, v1 = e1 + e3;
 #pragma unroll
-          for (int o = 4; o < 32; o <<= 1) {
-            v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-            v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-          }
-          if (g_ == nt) {
-            pcm[1 + col] = v0;
-            pcm[2 + col] = v1;
-          }
+        for (int o = 4; o < 32; o <<= 1) {
+          v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+          v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+        }
+        if (g_ == nt) {
+          pcm[1 + col] = v0;
+          pcm[2 + col] = v1;
         }
       }
     }
-    named_barrier(1, NCT);
+    named_barrier(1, NCT);   // pcm[] is complete
 
-    // ---- 3 + 4. selection on consumer 0; window tiles on consumers 4-5, selected blocks on consumers 0-3
-    const int n_blk = nk + 1;
-    if (cw == 0) {
-      for (int blk = lane; blk < n_blk; blk += 32) {
+    if (cw >= RING_NS) {
+      // ================================ W. the rest of the sliding window
+      for (; j < n_jobs; ++j)
+        if (((jobs[j] >> 2) & 7) == cw) window_tile(j);
+    } else {
+      // ---- 3. selection
+      const int n_blk = nk + 1;
+      const bool by_rank = n_blk <= 2 * NST;   // CTA-uniform
+      auto pooled = [&](int blk) -> float {
         auto at = [&](int jj) { return (jj >= 0 && jj < Y) ? pcm[1 + jj] : 0.f; };
         const int jj = 4 * blk;
-        float pv = at(jj - 1) + ((2.f * at(jj) + 2.f * at(jj + 1)) + (2.f * at(jj + 2) + at(jj + 3)));
-        psl[blk] = (blk >= ni && blk <= nk - nl) ? pv : -1.f;   // forced blocks are not candidates
-      }
-      sel[lane] = -1;
-      __syncwarp();
-      for (int r = 0; r < n_free; ++r) {
-        float bv = -1.f;
-        int bi = 0x7fffffff;
-        for (int blk = lane; blk < n_blk; blk += 32) {
-          const float v = psl[blk];
-          if (v > bv) {  // ascending scan keeps the lowest index among equals
-            bv = v;
-            bi = blk;
+        const float pv = at(jj - 1) + ((2.f * at(jj) + 2.f * at(jj + 1)) + (2.f * at(jj + 2) + at(jj + 3)));
+        return (blk >= ni && blk <= nk - nl) ? pv : -1.f;   // forced blocks are not candidates
+      };
+      if (by_rank) {
+        // every thread owns blocks ctid and ctid + 128; its rank among the candidates is the number of candidates with a
+        // larger score, or the same score and a lower index: ranks 0..n_free-1 are the list, in the order the rounds of
+        // arg-max would have produced it
+        for (int blk = ctid; blk < n_blk; blk += NST) psl[blk] = pooled(blk);
+        if (ctid < 32) sel[ctid] = -1;
+        named_barrier(2, NST);
+        for (int my = ctid; my < n_blk; my += NST) {
+          const float v = psl[my];
+          if (v < 0.f) continue;
+          int rank = 0;
+#pragma unroll 4
+          for (int o = 0; o < n_blk; ++o) {
+            const float u = psl[o];
+            rank += (u > v || (u == v && o < my)) ? 1 : 0;
           }
+          if (rank < n_free) sel[ni + nl + rank] = my;
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-          if (ov > bv || (ov == bv && oi < bi)) {
-            bv = ov;
-            bi = oi;
+        if (ctid < ni) sel[ctid] = (ctid <= nk) ? ctid : -1;
+        else if (ctid < ni + nl) sel[ctid] = (ctid <= nk) ? nk - (ctid - ni) : -1;
+        named_barrier(2, NST);
+      } else if (cw == 0) {
+        for (int blk = lane; blk < n_blk; blk += 32) psl[blk] = pooled(blk);
+        sel[lane] = -1;
+        __syncwarp();
+        // Rounds of warp-wide arg-max.  A lane owns `per` CONSECUTIVE blocks and keeps the best of them (ascending scan: the
+        // lowest index among equals); a round is one warp reduction (largest score) and a ballot: the lowest lane that holds
+        // that score holds the lowest such block.  Only the winner rescans its blocks.  Scores are >= 0, so their bit
+        // patterns order like unsigned integers; 0 = no candidate.
+        const int per = (n_blk + 31) >> 5, b0 = lane * per;
+        unsigned key;
+        int bi;
+        auto local_best = [&]() {
+          key = 0u;
+          bi = 0x7fffffff;
+          for (int blk = b0; blk < min(n_blk, b0 + per); ++blk) {
+            const float v = psl[blk];
+            const unsigned kk = v >= 0.f ? __float_as_uint(v) + 1u : 0u;
+            if (kk > key) {
+              key = kk;
+              bi = blk;
+            }
           }
-        }
-        if (lane == 0 && bv >= 0.f) {
-          sel[ni + nl + r] = bi;
-          psl[bi] = -1.f;
+        };
+        local_best();
+        for (int r = 0; r < n_free; ++r) {
+          const unsigned best = __reduce_max_sync(0xffffffffu, key);
+          if (best == 0u) break;   // fewer candidates than slots
+          const int wl = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1;
+          if (lane == wl) {
+            sel[ni + nl + r] = bi;
+            psl[bi] = -1.f;
+            local_best();
+          }
         }
         __syncwarp();
+        if (lane < ni) sel[lane] = (lane <= nk) ? lane : -1;
+        else if (lane < ni + nl) sel[lane] = (lane <= nk) ? nk - (lane - ni) : -1;
+        __syncwarp();
       }
-      if (lane < ni) sel[lane] = (lane <= nk) ? lane : -1;
-      else if (lane < ni + nl) sel[lane] = (lane <= nk) ? nk - (lane - ni) : -1;
-      __syncwarp();
-      if (p.topk_out && lane < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + lane] = sel[lane];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sel_ready);
-    }
-    {
-      wts::Acc<D> acc;
-      acc.init();
-      bool have_sel = cw == 0;
+      if (cw == 0) {
+        if (p.topk_out && lane < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + lane] = sel[lane];
+        // the cache rows of the free blocks, for the producer (an unused slot fetches block 0 and takes no part)
+        if (lane >= nf && lane < n_valid) rows_slc[lane] = (int)tokrow(max(0, min(sel[lane], nk)) << 6);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sel_ready);
+      }
+      // ---- 4. the selected blocks
+      bool have_sel = cw == 0 || by_rank;
       for (; j < n_jobs; ++j) {
         const int job = jobs[j];
         if (((job >> 2) & 7) != cw) continue;
-        const int type = job & 3, idx = job >> 5;
-        int k0;
-        if (type == JOB_WIN) {
-          k0 = w_k0 + (idx << 6);
-        } else {
-          if (idx >= nf && !have_sel) {
-            if (!mbar_wait(sel_ready, 0, &budget)) timed_out = true;
-            have_sel = true;
-          }
-          const int blk = idx >= nf ? sel[idx] : (idx < ni ? idx : nk - (idx - ni));
-          k0 = max(0, min(blk, nk)) << 6;
-          if (blk < 0 || blk > nk) k0 = -1;   // an unused slot: its tile was fetched (block 0) but takes no part
+        const int idx = job >> 5;
+        if (idx >= nf && !have_sel) {
+          if (!mbar_wait(sel_ready, 0, &budget)) timed_out = true;
+          have_sel = true;
         }
+        const int blk = idx >= nf ? sel[idx] : (idx < ni ? idx : nk - (idx - ni));
+        int k0 = max(0, min(blk, nk)) << 6;
+        if (blk < 0 || blk > nk) k0 = -1;   // an unused slot: its tile was fetched (block 0) but takes no part
         wait_job(j);
         const uint32_t bk = ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES;
-        if (k0 >= 0) {
-          if (type == JOB_WIN)
-            wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int x) { return k0 + x >= lo && k0 + x <= t; }, min(64, t - k0 + 1), c2, lane);
-          else
-            wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int x) { return k0 + x <= t; }, min(64, t - k0 + 1), c2, lane);
-        }
+        if (k0 >= 0)
+          wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int x) { return k0 + x <= t; }, min(64, t - k0 + 1), c2, lane);
         release(j);
       }
-      named_barrier(1, NCT);   // every read of the score arrays is done: the states may be written again
-      wts::store_state<D>(acc, state + cw * STATE, lane);
     }
+    named_barrier(1, NCT);   // every read of the score arrays is done: the states may be written again
+    wts::store_state<D>(acc, state + cw * STATE, lane);
     named_barrier(1, NCT);
     // ---- 5. merge + gated combine
     const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t)b * p.w_stride_t + (int64_t)kh * G * 3;
+    if (ctid < 16) merge_weights(0, RING_NS, ctid);
+    else if (ctid < 32) merge_weights(RING_NS, RING_NC - RING_NS, ctid - 16);
+    else if (ctid < 32 + 3 * 16) {
+      const int i = ctid - 32, r = i / 3;   // gates: sigmoid of the three logits of head r
+      fac[RING_NC * 16 + i] = r < G ? 1.f / (1.f + __expf(-__bfloat162float(wp[i]))) : 0.f;
+    }
+    named_barrier(1, NCT);
+    const float* gate = fac + RING_NC * 16;
     for (int idx = ctid; idx < G * D; idx += NCT) {
-      const int r = idx / D, c = idx - r * D;
-      const float slc = merged(0, 4, r, c, nullptr), swa = merged(4, 2, r, c, nullptr);
-      const float s0 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 0])));
-      const float s1 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 1])));
-      const float s2 = 1.f / (1.f + __expf(-__bfloat162float(wp[r * 3 + 2])));
-      out[idx] = __float2bfloat16(s0 * cmp_o_s[idx] + s1 * slc + s2 * swa);
+      const int r = idx / D;
+      float slc = 0.f, swa = 0.f;
+#pragma unroll
+      for (int w = 0; w < RING_NS; ++w) slc += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+#pragma unroll
+      for (int w = RING_NS; w < RING_NC; ++w) swa += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+      out[idx] = __float2bfloat16(gate[r * 3] * cmp_o_s[idx] + gate[r * 3 + 1] * slc + gate[r * 3 + 2] * swa);
     }
   }
   if (timed_out && p.status) atomicOr(p.status, 2048);
+}
+
+template <int D, int NC, int NS>
+static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_t smem_cap) {
+  const size_t tile = (size_t)64 * D * 2;
+  const int job_cap = 2 * ((p.y_cap + 63) / 64) + 2 * p.hp.top_n + p.hp.window / 64 + 8;
+  const int rows_cap = (p.y_cap + 63) / 64 + RING_WIN_ROWS + 32;
+  const size_t region = (size_t)max(NC * (32 + 16 * D), p.y_cap + 8 + p.y_cap / 4 + 8) * 4;
+  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap + rows_cap + (NC + 3) * 16 + 2) * 4 + 8 + 16 * 8 + 16 + 1024;
+  if (fixed + 2 * 2 * tile > smem_cap) return 1;
+  int n_slots = (int)((smem_cap - fixed) / (2 * tile));
+  if (n_slots > max_slots) n_slots = max_slots;
+  if (n_slots < 2) return 1;
+  const size_t smem = (size_t)n_slots * 2 * tile + fixed;
+  CUtensorMap tmk, tmv;
+  if (!tma::make_map(&tmk, p.k_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1) ||
+      !tma::make_map(&tmv, p.v_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1))
+    return 1;
+  cudaError_t e = cudaFuncSetAttribute(decode_ring_kernel<D, NC, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("decode_fused: cudaFuncSetAttribute(%zu B) failed: %s", smem, cudaGetErrorString(e));
+    return NSA_ERR_CUDA;
+  }
+  dim3 grid(p.KH, p.B);
+  decode_ring_kernel<D, NC, NS><<<grid, 32 * (NC + 1), smem, st>>>(p, n_slots, job_cap, tmk, tmv);
+  return check_launch("decode_fused");
 }
 
 // returns 1 when the configuration is not covered (decode_fused_kernel then runs), 0 on launch, < 0 on error
 int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) {
   const int D = p->D;
   if (p->cache_rows <= 0 || (p->cache_stride_t * 2) % 16 || (((uintptr_t)p->k_cache | (uintptr_t)p->v_cache) & 15)) return 1;
-  const size_t tile = (size_t)64 * D * 2;
-  const size_t region = (size_t)max(RING_NC * (32 + 16 * D), p->y_cap + 8 + p->y_cap / 4 + 8) * 4;
-  const int job_cap = 2 * ((p->y_cap + 63) / 64) + 2 * p->hp.top_n + p->hp.window / 64 + 8;
-  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap) * 4 + 8 + 16 * 8 + 16 + 1024;
-  int n_slots = (int)((227 * 1024 - fixed) / (2 * tile));
-  if (n_slots > 5) n_slots = 5;
-  if (n_slots < 3) return 1;
-  const size_t smem = (size_t)n_slots * 2 * tile + fixed;
-  CUtensorMap tmk, tmv;
-  if (!tma::make_map(&tmk, p->k_cache, p->cache_rows, p->KH, D, p->cache_stride_t, 64, 1) ||
-      !tma::make_map(&tmv, p->v_cache, p->cache_rows, p->KH, D, p->cache_stride_t, 64, 1))
-    return 1;
-  cudaError_t e = (D == 128) ? cudaFuncSetAttribute(decode_ring_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                             : cudaFuncSetAttribute(decode_ring_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) {
-    set_error("decode_fused: cudaFuncSetAttribute(%zu B) failed: %s", smem, cudaGetErrorString(e));
-    return NSA_ERR_CUDA;
-  }
-  dim3 grid(p->B, p->KH);
-  if (D == 128) decode_ring_kernel<128><<<grid, 32 * (RING_NC + 1), smem, st>>>(*p, n_slots, job_cap, tmk, tmv);
-  else decode_ring_kernel<64><<<grid, 32 * (RING_NC + 1), smem, st>>>(*p, n_slots, job_cap, tmk, tmv);
-  return check_launch("decode_fused");
+  if (p->hp.window / 64 + 2 > RING_WIN_ROWS || p->hp.top_n > 32) return 1;
+  return D == 128 ? launch_shape<128, 6, 4>(*p, st, 5, 227 * 1024) : launch_shape<64, 6, 4>(*p, st, 5, 227 * 1024);
 }
 
 }  // namespace nsa

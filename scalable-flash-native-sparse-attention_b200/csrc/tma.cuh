@@ -13,6 +13,10 @@ __device__ __forceinline__ void load_3d(uint32_t dst, const CUtensorMap* map, in
       "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
       : "memory");
 }
+// fetch the descriptor itself ahead of its first use
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 // ask for a box to be brought into L2 (no shared-memory destination, no completion to wait for)
 __device__ __forceinline__ void prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0),

@@ -206,6 +206,44 @@ def test_more_than_16_query_heads_per_kv_head_on_the_paged_path(QH, KH, D):
         assert (od[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"decode seq {b}"
 
 
+def test_decode_long_contexts_use_the_round_based_selection():
+    """Above 256 selection blocks (16K tokens) the one-launch decode step selects by rounds of warp-wide arg-max instead of
+    rank counting: same list as the op-by-op path (which runs the scoring kernel of prefill), same output."""
+    from flash_nsa.inference import nsa_decode_unfused, nsa_decode_fused
+    QH, KH, D = 8, 2, 64
+    lens = [20000, 16500, 3000]
+    B = len(lens)
+    g = torch.Generator().manual_seed(77)
+    cache = Cache(lens, KH, D, seed=8)
+    flat_k = cache.k.view(-1, KH, D)
+    flat_v = cache.v.view(-1, KH, D)
+    for b, L in enumerate(lens):
+        pos = torch.arange(L)
+        rows = cache.block_tables[b].long()[pos // PAGE] * PAGE + pos % PAGE
+        flat_k[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
+        flat_v[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
+    cache.cuda()
+    from flash_nsa.inference import mean_pooling_prefill
+    y_len = [(L - 32) // 16 + 1 for L in lens]
+    y_cu = torch.tensor([0] + torch.tensor(y_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    for c in (cache.k, cache.v):
+        mean_pooling_prefill(c, y_cu, max(y_len), slot_mapping=slots, block_table=cache.block_tables)
+    q = torch.randn(B, QH, D, generator=g).bfloat16().cuda()
+    w = torch.randn(B, QH, 3, generator=g).bfloat16().cuda()
+    args = (q, cache.k, cache.v, w, torch.tensor(lens, dtype=torch.int32, device="cuda"), cache.block_tables,
+            torch.full((B,), -1, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+    o_ref = nsa_decode_unfused(*args)
+    o, tk = nsa_decode_fused(*args, return_topk=True)
+    assert (o.float() - o_ref.float()).abs().max().item() <= TOL
+    for b, L in enumerate(lens):
+        nkb = (L - 1) // 64
+        for h in range(KH):
+            row = tk[h, b].tolist()
+            assert row[0] == 0 and row[1] == nkb and row[2] == nkb - 1
+            assert len(set(row)) == 16 and min(row) >= 0 and max(row) <= nkb
+
+
 def test_decode_writes_the_new_compressed_row():
     from flash_nsa.inference import kv_mean_pooling_decode
     KH, D = 2, 64
