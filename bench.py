@@ -340,6 +340,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
     ap.add_argument("--no-inference", action="store_true", help="skip the paged decode / chunked prefill measurement")
+    ap.add_argument("--no-decode-sweep", action="store_true", help="inference part: config 4 only (profiling runs)")
     ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the strong-scaling and no-recompute side measurements")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -598,7 +599,7 @@ def main():
         line["roofline"] = roofline
         line["kernels_ms"] = kernels
     if world == 1 and not args.no_inference:
-        line["inference"] = inference_bench(dev)
+        line["inference"] = inference_bench(dev, sweep=not args.no_decode_sweep)
         status_ok("inference")
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_config0()
@@ -874,7 +875,7 @@ class Config4:
         return {"max_err": err, "rows": len(rows), "near_tie_rows": flips}
 
 
-def inference_bench(dev, check_seqs=16):
+def inference_bench(dev, check_seqs=16, sweep=True):
     """BASELINE config 4: fused paged decode of 64 sequences and a chunked prefill of 2048 tokens on a 6144-token prefix.
     Both results are checked against the CPU oracle (un-paged sequences) BEFORE anything is timed: the decode on
     `check_seqs` of the 64 sequences (tests/test_gpu_inference.py checks all 64), the prefill on 64 sampled rows."""
@@ -918,7 +919,7 @@ def inference_bench(dev, check_seqs=16):
     n_dec, n_chunk = c4.B, c4.Cn
     del c4, o, tk, o_pre              # the sweep below fills its own 4 GiB cache
     torch.cuda.empty_cache()
-    sweep = decode_sweep_4gib(dev)
+    sweep = decode_sweep_4gib(dev) if sweep else None
     return {"workload": "decode batch 64, contexts U[4096,8192] (seed 1004), 32 q heads / 8 kv heads / d=128, page 256, shuffled "
                         "page table; chunked prefill 2048 new tokens on a 6144-token prefix",
             "checked_against_oracle": {"decode": chk_dec, "prefill": chk_pre, "tolerance": TOL},
