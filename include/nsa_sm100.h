@@ -280,6 +280,14 @@ typedef struct NsaPagedPoolParams {
 /* replaces mean_pooling_prefill / mean_pooling_decode / kv_mean_pooling_decode,
  * flash_nsa/inference/compress_kv.py:191-286 */
 int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream);
+/* Clears the cache rows [len_b, next multiple of 128) of every sequence b (cache0 and, if given, cache1), where len_b =
+ * context_lens[b] counts the rows of the kind kv_table lists (token rows with the token page table and the context
+ * lengths; compressed rows with the compressed-row page table and the compressed-row counts).  The TMA-fed prefill kernels
+ * read whole 128-row tiles of a page, and rows past a sequence's end may be never-written memory; the reference's kernels
+ * mask per row instead (flash_nsa/inference/compress_attn.py:60-120).  Uses cache0, cache1, kv_table, context_lens,
+ * row_stride, B, page_size, table_stride; with decode = 2, context_lens holds TOKEN counts and len_b is the number of
+ * compressed rows they give, (tokens - kernel_size) / stride + 1. */
+int nsa_paged_zero_tails(const NsaPagedPoolParams* p, void* stream);
 
 /* ---- fused paged decode step ---------------------------------------------------------------------------- */
 typedef struct NsaDecodeParams {

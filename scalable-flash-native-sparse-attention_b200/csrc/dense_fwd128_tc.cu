@@ -124,7 +124,10 @@ __global__ void __launch_bounds__(576, 1)
           for (int sl = 0; sl < SLABS; ++sl)
             tma::load_3d(sQ + w * Q_BYTES + sl * Q_SLAB, &tmq, sl * 64, kh * G, pc.q_start + im.t0 + w * TOK, q_full);
         for (int it = 0; it < im.ntiles; ++it) {
-          const int g = gt + it, s = g & 1, row = kv_bos + im.kv_lo + it * BN;
+          const int g = gt + it, s = g & 1;
+          // paged cache: a 128-row tile lies inside one page (page sizes are multiples of 128), one table look-up per tile
+          const int row = (MODE == MODE_CMP) ? (pc.y_tab ? (int)cmp_row(pc, im.kv_lo + it * BN) : kv_bos + im.kv_lo + it * BN)
+                                             : (pc.x_tab ? (int)tok_row(pc, im.kv_lo + it * BN) : kv_bos + im.kv_lo + it * BN);
           if (g >= 2 && !mbar_wait(k_free + 8 * s, ((g >> 1) - 1) & 1, &budget)) timed_out = true;
           tma::expect_tx(k_full + 8 * s, KV_BYTES);
 #pragma unroll
@@ -358,7 +361,12 @@ template <int D, int MODE>
 static int launch128(const NsaAttnParams* p, cudaStream_t st, const char* name) {
   const int G = p->QH / p->KH;
   if (G > 128 || (128 % G) != 0) return 1;
-  if (p->meta.kv_table || p->meta.cmp_table || p->n_k_rows <= 0 || p->n_q_rows <= 0) return 1;
+  if (p->n_k_rows <= 0 || p->n_q_rows <= 0) return 1;
+  // a paged cache: pages must hold whole 128-row tiles (the caller clears the rows past each sequence's end, nsa_paged_zero_tails)
+  // (prefill chunks only: one-token pieces of a decode step are better served by the 64-row-tile kernel)
+  if ((p->meta.kv_table || p->meta.cmp_table) &&
+      (p->meta.page_size < 128 || (p->meta.page_size & (p->meta.page_size - 1)) || p->meta.max_piece_len < 64))
+    return 1;
   if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v) & 15) return 1;
   if ((p->q_stride_t * 2) % 16 || (p->k_stride_t * 2) % 16 || (p->v_stride_t * 2) % 16) return 1;
   const int TOK = 128 / G;

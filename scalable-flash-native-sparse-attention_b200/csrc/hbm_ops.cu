@@ -523,6 +523,39 @@ extern "C" int nsa_reorder(const NsaReorderParams* p, void* stream) {
   return check_launch("reorder");
 }
 
+namespace nsa {
+// rows [len_b, next multiple of 128) of every sequence's paged rows are cleared in both caches: the TMA-fed kernels read
+// whole 128-row tiles, and rows past a sequence's end (never-written memory of its last page) must be finite
+__global__ void paged_zero_tails_kernel(NsaPagedPoolParams p) {
+  const int b = blockIdx.x;
+  int len = p.context_lens[b];
+  if (p.decode == 2) len = len >= p.kernel_size ? (len - p.kernel_size) / p.stride + 1 : 0;   // compressed rows of the context
+  if (len <= 0) return;
+  const int end = min((len + 127) / 128 * 128, p.table_stride * p.page_size);
+  const int sh = 31 - __clz(p.page_size);
+  const int chunks = (int)(p.row_stride / 8);   // 16-byte pieces of one cache row (all heads)
+  const int32_t* tab = p.kv_table + (int64_t)b * p.table_stride;
+  for (int i = threadIdx.x; i < (end - len) * chunks; i += blockDim.x) {
+    const int r = len + i / chunks, c = i % chunks;
+    const int page = tab[r >> sh];
+    if (page < 0) continue;
+    const int64_t off = (((int64_t)page << sh) + (r & (p.page_size - 1))) * p.row_stride + c * 8;
+    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.cache0) + off)[0] = make_uint4(0, 0, 0, 0);
+    if (p.cache1) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.cache1) + off)[0] = make_uint4(0, 0, 0, 0);
+  }
+}
+}  // namespace nsa
+
+extern "C" int nsa_paged_zero_tails(const NsaPagedPoolParams* p, void* stream) {
+  NSA_REQUIRE(p && p->cache0 && p->kv_table && p->context_lens, NSA_ERR_BAD_ARG, "paged_zero_tails: null pointer");
+  NSA_REQUIRE(p->page_size > 0 && (p->page_size & (p->page_size - 1)) == 0 && p->row_stride % 8 == 0, NSA_ERR_UNSUPPORTED_SHAPE,
+              "paged_zero_tails: page=%d must be a power of two and rows multiples of 16 bytes", p->page_size);
+  NSA_REQUIRE(p->decode != 2 || (p->kernel_size > 0 && p->stride > 0), NSA_ERR_BAD_ARG, "paged_zero_tails: kernel_size / stride");
+  if (p->B <= 0) return NSA_OK;
+  paged_zero_tails_kernel<<<p->B, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("paged_zero_tails");
+}
+
 extern "C" int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream) {
   NSA_REQUIRE(p && p->cache0 && p->slot_mapping && p->kv_table, NSA_ERR_BAD_ARG, "paged_mean_pool: null pointer");
   NSA_REQUIRE(p->decode ? p->context_lens != nullptr : p->y_cu != nullptr, NSA_ERR_BAD_ARG, "paged_mean_pool: missing length table");

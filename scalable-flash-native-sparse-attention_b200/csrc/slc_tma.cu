@@ -95,6 +95,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   int my_blk = -1;
   if (lane < n_valid) my_blk = __ldg(p.topk + (int64_t)kh * p.topk_stride_h + q_row * p.hp.top_n + lane);
   unsigned todo = __ballot_sync(0xffffffffu, my_blk >= 0 && my_blk <= nk);
+  // first row of my block in the K/V tensor: with a paged cache one page-table look-up per lane, all in flight at once (a
+  // 64-row block never straddles a page)
+  const int my_row = (my_blk >= 0 && my_blk <= nk) ? (int)tok_row(pc, my_blk * BS) : 0;
+  const bool paged = pc.x_tab != nullptr;
   int budget = tc::kWaitBudget;
   bool timed_out = false;
 
@@ -108,14 +112,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   int cur = -1;
   if (todo) {
     cur = __shfl_sync(0xffffffffu, my_blk, __ffs(todo) - 1);
+    const int row = __shfl_sync(0xffffffffu, my_row, __ffs(todo) - 1);
     todo &= todo - 1;
     if (lane == 0) {
-      fetch<D>(wp.bufK, wp.barK, &tmk, kh, pc.x_bos + cur * BS);
-      fetch<D>(wp.bufV, wp.barV, &tmv, kh, pc.x_bos + cur * BS);
+      fetch<D>(wp.bufK, wp.barK, &tmk, kh, row);
+      fetch<D>(wp.bufV, wp.barV, &tmv, kh, row);
     }
   }
   while (cur >= 0) {
     const int nxt = todo ? __shfl_sync(0xffffffffu, my_blk, __ffs(todo) - 1) : -1;
+    const int nxt_row = todo ? __shfl_sync(0xffffffffu, my_row, __ffs(todo) - 1) : 0;
     todo &= todo - 1;
     const int key0 = cur * BS;
     if (!tc::mbar_wait(wp.barK, wp.nK & 1, &budget)) timed_out = true;
@@ -134,7 +140,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
       }
     }
     __syncwarp();
-    if (lane == 0 && nxt >= 0) fetch<D>(wp.bufK, wp.barK, &tmk, kh, pc.x_bos + nxt * BS);  // K buffer is free again
+    if (lane == 0 && nxt >= 0) fetch<D>(wp.bufK, wp.barK, &tmk, kh, nxt_row);  // K buffer is free again
     if (cur == nk) {   // the token's own block: keys after it do not take part
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
@@ -182,6 +188,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     }
     if (!tc::mbar_wait(wp.barV, wp.nV & 1, &budget)) timed_out = true;
     ++wp.nV;
+    if (paged && key0 + BS > pc.x_len) {
+      // rows of the page past the sequence's end may hold anything (never-written memory): their probabilities are 0, and
+      // 0 * garbage must not reach the sums, so those V rows are cleared
+      constexpr int CH = D / 8;
+      for (int idx = (pc.x_len - key0) * CH + lane; idx < BS * CH; idx += 32) {
+        const int r = idx / CH, c = idx - r * CH;
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(wp.bufV + tc::slab_off(BS, r, c)), "r"(0) : "memory");
+      }
+      __syncwarp();
+    }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const uint32_t a0 = pack_bf16(s[2 * u][0], s[2 * u][1]), a1 = pack_bf16(s[2 * u][2], s[2 * u][3]);
@@ -195,7 +211,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
       }
     }
     __syncwarp();
-    if (lane == 0 && nxt >= 0) fetch<D>(wp.bufV, wp.barV, &tmv, kh, pc.x_bos + nxt * BS);
+    if (lane == 0 && nxt >= 0) fetch<D>(wp.bufV, wp.barV, &tmv, kh, nxt_row);
     cur = nxt;
   }
 
@@ -368,9 +384,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   if (timed_out && lane == 0 && p.status) atomicOr(p.status, 256);
 }
 
-// returns 1 when not applicable (paged cache or unaligned tensors): the fragment-direct kernels then run
+// returns 1 when not applicable (unaligned tensors; a paged cache in backward or with pages under 64 rows): the
+// fragment-direct kernels then run
 int launch_slc_tma(const NsaAttnParams* p, cudaStream_t st, bool backward) {
-  if (p->meta.kv_table || p->n_k_rows <= 0) return 1;
+  if (p->n_k_rows <= 0) return 1;
+  if (p->meta.kv_table && (backward || p->meta.page_size < 64 || (p->meta.page_size & (p->meta.page_size - 1)))) return 1;
   if ((((uintptr_t)p->k | (uintptr_t)p->v) & 15) || (p->k_stride_t * 2) % 16 || (p->v_stride_t * 2) % 16) return 1;
   const int D = p->D;
   CUtensorMap tmk, tmv;

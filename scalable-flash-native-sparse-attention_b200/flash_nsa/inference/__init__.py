@@ -11,7 +11,7 @@ any of these calls, shapes depend only on the arguments, so a decode step can be
 from ..ops._common import poll_status, post_status
 from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
                   topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
-                  combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported)
+                  combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported, zero_cache_tails)
 
 
 def store_kvcache(key, value, k_cache, v_cache, slot_mapping):

@@ -82,7 +82,7 @@ def _attn_params(q, kf, vf, meta, hp, sm_scale, o, lse, lse_head_major, topk=Non
     p.sm_scale = float(sm_scale)
     p.QH, p.KH, p.D = QH, KH, D
     p.status = ptr(status_word(q.device))
-    p.n_q_rows = T
+    p.n_q_rows, p.n_k_rows = T, kf.size(0)   # the cache as one flat [pages * page_size, kh, d] tensor: the TMA-fed kernels map it
     return p
 
 
@@ -102,6 +102,26 @@ def _pool(cache0, cache1, slot_mapping, block_table, y_cu_seqlens, y_maxlen, con
     p.kernel_size, p.stride, p.decode = kernel_size, stride, int(decode)
     assert slot_mapping.dtype == torch.int32 and block_table.dtype == torch.int32
     call("nsa_paged_mean_pool", p, cache0)
+
+
+def zero_cache_tails(k_cache, v_cache, lens, block_table, compressed=None):
+    """Clear the cache rows [lens[b], next multiple of 128) of every sequence (rows of the kind `block_table` lists: token
+    rows with the context lengths, compressed rows with the compressed-row counts).  The TMA-fed prefill kernels read whole
+    128-row tiles of a page, and what lies past a sequence's end may be never-written memory (0 * NaN); those rows belong
+    to no one yet, so clearing them changes nothing a later step reads.  `compressed=(kernel_size, stride)`: `lens` are
+    token counts and the rows are the compressed rows they give."""
+    f0, page = _flat(k_cache)
+    p = S["NsaPagedPoolParams"]()
+    p.cache0, p.cache1 = ptr(f0), ptr(_flat(v_cache)[0])
+    p.kv_table, p.context_lens = ptr(block_table), ptr(lens)
+    p.row_stride = f0.stride(0)
+    p.B = block_table.size(0)
+    p.H, p.D = f0.size(1), f0.size(2)
+    p.page_size, p.table_stride = page, block_table.stride(0)
+    if compressed is not None:
+        p.kernel_size, p.stride, p.decode = int(compressed[0]), int(compressed[1]), 2
+    assert lens.dtype == torch.int32 and block_table.dtype == torch.int32 and lens.numel() >= p.B
+    call("nsa_paged_zero_tails", p, k_cache)
 
 
 def mean_pooling_prefill(x, y_cu_seqlens, y_maxlen, slot_mapping, block_table, kernel_size=32, stride=16):
@@ -132,6 +152,8 @@ def cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables, context_lens
     o = torch.empty(T, QH, D, device=q.device, dtype=q.dtype)
     lse = torch.empty(QH, T, device=q.device, dtype=torch.float32)
     if T:
+        if x_maxlen >= 64 and page >= 128:   # the 128-row-tile kernel will run: the rows after each sequence's last compressed row
+            zero_cache_tails(k, v, context_lens, block_tables, compressed=(kernel_size, stride))
         call("nsa_cmp_attn_fwd", _attn_params(q, kf, vf, meta, _hyper(kernel_size, stride), sm_scale, o, lse, True), q)
     return o, lse
 
@@ -222,6 +244,8 @@ def slc_attn_decode(q, k, v, topk, block_tables, context_lens, block_size=64, to
 def swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables, context_lens, window_size=512, sm_scale=None):
     """Sliding-window attention of the new tokens over the paged cache (the reference calls flash-attn here,
     flash_nsa/inference/__init__.py:125-155)."""
+    if q.size(0) and x_maxlen >= 64 and k.size(1) >= 128:   # the 128-row-tile kernel will run (see zero_cache_tails)
+        zero_cache_tails(k, v, context_lens, block_tables)
     return _token_branch("nsa_swa_fwd", q, k, v, (context_lens, x_cu_seqlens, x_maxlen, block_tables, None),
                          _hyper(window=window_size), sm_scale)[0]
 
