@@ -567,6 +567,13 @@ def main():
             core = make_core(recompute)
             extras["strong_128k"] = strong_scaling_128k(make_core, run_step, timed, status_ok, dev, rank, world)
 
+    if world == 1 and not args.no_extras and not args.tokens_per_gpu:
+        # the point the multi-GPU runs are set against: the 131 072-token sequence of `strong_128k`, which is also the
+        # per-GPU token count of the weak-scaling runs, on this one GPU
+        del q, k, v, w, do
+        torch.cuda.empty_cache()
+        extras["single_gpu_128k"] = single_gpu_128k(make_core, run_step, timed, status_ok, dev)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -673,6 +680,33 @@ def cp_step_profile(step, sync_all):
         out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
     exposed = out.pop("comm_wait", 0.0)
     return out, exposed
+
+
+def single_gpu_128k(make_core, run_step, timed, status_ok, dev):
+    """One causal sequence of 131 072 tokens on one GPU, no recompute: the single-GPU point of `strong_128k` (efficiency at N
+    GPUs = this ms / N / that ms) and the per-GPU token count of the weak-scaling runs."""
+    T = 131072
+    g = torch.Generator().manual_seed(2001)
+    mk = lambda h, dd: torch.randn(T, h, dd, generator=g).bfloat16().to(dev)
+    q, k, v, w, do = mk(QH, D), mk(KH, D), mk(KH, D), mk(QH, 3), mk(QH, D)
+    for t in (q, k, v, w):
+        t.requires_grad_(True)
+    cu_host = np.array([0, T], dtype=np.int64)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device=dev)
+    core = make_core(False)
+    ms_step = timed(lambda: run_step(core, cu, cu_host, (q, k, v, w, do)), 3, 2)
+
+    def fwd_only():
+        with torch.no_grad():
+            core(q, k, v, w, cu, cu_seqlens_np=cu_host, cp_mode=2)
+
+    ms_fwd = timed(fwd_only, 3, 1)
+    status_ok("single_gpu_128k")
+    fm = flops_model([T])
+    alg = sum(fm[n] for n in ALG_KEYS)
+    return {"tokens": T, "ms_fwd": ms_fwd, "ms_bwd": ms_step - ms_fwd, "ms_per_step": ms_step, "tokens_per_s": T / (ms_step * 1e-3),
+            "algorithmic_tflops": alg / (ms_step * 1e-3) / 1e12,
+            "reference_h800_ms": {"fwd": 101.123, "bwd": 213.904}}
 
 
 def strong_scaling_128k(make_core, run_step, timed, status_ok, dev, rank, world):
