@@ -244,6 +244,53 @@ def test_decode_long_contexts_use_the_round_based_selection():
             assert len(set(row)) == 16 and min(row) >= 0 and max(row) <= nkb
 
 
+def test_rows_past_a_sequence_end_may_hold_anything():
+    """Never-written cache memory (here: NaN everywhere a row was not stored) must not reach a result: the tile kernels read
+    whole tiles of a page, and a zero probability times NaN is NaN."""
+    from flash_nsa import nsa_prefill, nsa_decode
+    from flash_nsa.inference import nsa_decode_unfused
+    QH, KH, D = 16, 4, 128
+    lens = [333, 1000, 70]
+    seqs = _seqs(lens, QH, KH, D, seed=31)
+    B = len(lens)
+    cache = Cache(lens, KH, D, seed=12)
+    cache.k.fill_(float("nan"))
+    cache.v.fill_(float("nan"))
+    end = [L - 1 for L in lens]
+    for b, s in enumerate(seqs):
+        cache.store(b, s["k"][:end[b]], s["v"][:end[b]])
+    cache.cuda()
+    y_len = [max((e - 32) // 16 + 1, 0) for e in end]
+    x_cu = torch.tensor([0] + torch.tensor(end).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    y_cu = torch.tensor([0] + torch.tensor(y_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    q = torch.cat([seqs[b]["q"][:end[b]] for b in range(B)]).cuda()
+    w = torch.cat([seqs[b]["w"][:end[b]] for b in range(B)]).cuda()
+    o = nsa_prefill(q, cache.k, cache.v, w, x_cu, y_cu, max(end), max(y_len), torch.tensor(end, dtype=torch.int32, device="cuda"),
+                    cache.block_tables, slots, cache.cmp_block_tables)
+    assert bool(torch.isfinite(o).all())
+    off = 0
+    for b in range(B):
+        assert _bulk_ok(o[off:off + end[b]], _oracle(seqs[b], end[b])), f"prefill seq {b}"
+        off += end[b]
+    for b, s in enumerate(seqs):
+        p = lens[b] - 1
+        pg = int(cache.block_tables[b, p // PAGE])
+        cache.k[pg, p % PAGE] = s["k"][p].cuda()
+        cache.v[pg, p % PAGE] = s["v"][p].cuda()
+    slot = [cache.cmp_slot(b, (L - 32) // 16) if (L % 16 == 0 and L >= 32) else -1 for b, L in enumerate(lens)]
+    qd = torch.stack([seqs[b]["q"][lens[b] - 1] for b in range(B)]).cuda()
+    wd = torch.stack([seqs[b]["w"][lens[b] - 1] for b in range(B)]).cuda()
+    args = (qd, cache.k, cache.v, wd, torch.tensor(lens, dtype=torch.int32, device="cuda"), cache.block_tables,
+            torch.tensor(slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+    for fn in (nsa_decode, nsa_decode_unfused):
+        od = fn(*args)
+        assert bool(torch.isfinite(od).all()), fn.__name__
+        for b in range(B):
+            ref = _oracle(seqs[b], lens[b])[-1:]
+            assert (od[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"{fn.__name__} seq {b}"
+
+
 def test_decode_writes_the_new_compressed_row():
     from flash_nsa.inference import kv_mean_pooling_decode
     KH, D = 2, 64
