@@ -739,7 +739,7 @@ def strong_scaling_128k(make_core, run_step, timed, status_ok, dev, rank, world)
     alg = sum(fm[n] for n in ALG_KEYS)
     return {"tokens": T, "tokens_per_gpu": per, "kv_head_stride": 4, "ms_fwd": ms_fwd, "ms_bwd": ms_step - ms_fwd, "ms_per_step": ms_step,
             "per_gpu_algorithmic_tflops": alg / (ms_step * 1e-3) / 1e12 / world,
-            "single_gpu_reference_point": "python bench.py --tokens-per-gpu 131072 (one GPU, same sequence): efficiency = that ms / N / this ms"}
+            "single_gpu_reference_point": "`single_gpu_128k` of the N=1 line (same sequence on one GPU): efficiency = that ms / N / this ms"}
 
 
 # ----------------------------------------------------------------------------------------------- paged inference (config 4)
