@@ -83,7 +83,7 @@ def backward_index_sizes(G, D, rows, max_blocks=None, top_n=16):
     r * top_n / max_blocks rows.  So the range is the power of two that gives >= 128 rows per cell, at least 4096 rows, and
     no ranges at all once that needs more than 32 MiB of q per range (measured on B200, one kv head of 16 heads, d = 128:
     64K tokens 2.85 ms without ranges / 2.63 with 8192-row ranges; one shard of 8 at 1M tokens 6.1 ms without / 19.3 with
-    4096-row ranges).  An item holds at most 32 query tiles of 128 / G tokens."""
+    4096-row ranges).  An item holds at most 64 query tiles of 128 / G tokens (32: 2 % slower at 64K, 16: 9 %)."""
     per_row = G * D * 2
     cap = 1 << (((32 << 20) // per_row).bit_length() - 1)
     if max_blocks is None:
@@ -93,7 +93,7 @@ def backward_index_sizes(G, D, rows, max_blocks=None, top_n=16):
     range_rows = max(want, min(4096, cap))
     if want > cap or rows <= range_rows:
         range_rows = 0
-    return range_rows, 32 * max(128 // G, 1)
+    return range_rows, 64 * max(128 // G, 1)
 
 
 @torch.no_grad()
