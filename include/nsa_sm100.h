@@ -274,7 +274,8 @@ typedef struct NsaPagedPoolParams {
   int32_t page_size, table_stride;
   int32_t y_maxlen;            /* prefill: most compressed rows in one sequence (grid sizing)                       */
   int32_t kernel_size, stride;
-  int32_t decode;              /* 0: prefill (every row with a slot), 1: decode (only the window ending at the last token) */
+  int32_t decode;              /* 0: prefill (every row with a slot), 1: decode (only the window ending at the last token);
+                                  nsa_paged_zero_tails: 2 = context_lens are token counts, clear the compressed-row tails */
   int32_t reserved0;
 } NsaPagedPoolParams;
 /* replaces mean_pooling_prefill / mean_pooling_decode / kv_mean_pooling_decode,

@@ -239,9 +239,6 @@ extern "C" int nsa_slc_topk(const NsaTopkParams* p, void* stream) {
   const bool std_sizes = p->hp.kernel_size == 32 && p->hp.stride == 16 && p->hp.block_size == 64;
   if (!std_sizes || p->quant == 3 || p->hp.top_n > 32) {
     // any other compression / block geometry, the per-row rounding mode, or a long list: the general kernel
-    NSA_REQUIRE(p->QH / p->KH <= 16, NSA_ERR_UNSUPPORTED_SHAPE,
-                "slc_topk: the general-size kernel takes at most 16 query heads per kv head (got %d); kernel 32 / stride 16 / "
-                "block 64 with the block-level rounding modes takes up to 64", p->QH / p->KH);
     return launch_slc_topk_general(p, (cudaStream_t)stream);
   }
   if (p->q_rows > 0 && p->ck_rows > 0 && p->QH / p->KH <= 64) {

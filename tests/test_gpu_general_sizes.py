@@ -67,6 +67,26 @@ def test_general_scoring_and_selection(ks, st, fp32):
         assert ((got - sc[b]).abs() <= tol).float().mean().item() > 0.999
 
 
+@pytest.mark.parametrize("QH,KH", [(40, 1), (64, 2)])
+def test_general_scoring_with_more_than_16_heads_per_kv_head(QH, KH):
+    """Head groups of 16 are summed before the pooling (the reference loops min(G, 16) heads the same way)."""
+    ks, st, D = 64, 32, 64
+    lens = [300, 70, 513]
+    q, k, v, w, do, cu = _mk(lens, QH, KH, D, seed=QH)
+    _setup(cu, kernel_size=ks, stride=st, block_size=64)
+    from flash_nsa.ops import mean_pooling_fwd, cmp_attn_fwd, slc_topk_indices
+    qd = q.cuda()
+    ck, cv = mean_pooling_fwd(k.cuda()), mean_pooling_fwd(v.cuda())
+    cmp_o, lse = cmp_attn_fwd(qd, ck, cv)
+    for fp32 in (True, False):
+        topk, _ = slc_topk_indices(qd, ck, lse, fp32=fp32, maybe_efficient_version=False, return_slc_prob=True)
+        sc = O.slc_scores(q.float(), ck.float().cpu(), lse.float().cpu(), cu, ks, st, 64, quant="fp32" if fp32 else "fp16_rows")
+        ref = O.topk_select(sc, cu)
+        ign = O.cdiv(max(lens), 64)
+        n_diff, n_bad, n_rows = topk_mismatch_report(topk.cpu(), ref, sc, cu, ign, ign, rel_tol=1e-3 if fp32 else 2e-3)
+        assert n_bad == 0, (fp32, n_diff, n_bad)
+
+
 def test_core_forward_backward_with_another_geometry():
     ks, st = 64, 32
     lens, QH, KH, D = [700, 450], 8, 2, 64
