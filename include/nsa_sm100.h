@@ -289,6 +289,12 @@ int nsa_paged_mean_pool(const NsaPagedPoolParams* p, void* stream);
  * row_stride, B, page_size, table_stride; with decode = 2, context_lens holds TOKEN counts and len_b is the number of
  * compressed rows they give, (tokens - kernel_size) / stride + 1. */
 int nsa_paged_zero_tails(const NsaPagedPoolParams* p, void* stream);
+/* Copies the rows that kv_table lists for every sequence b, rows 0 .. y_cu[b+1] - y_cu[b] - 1, from the paged cache0 into
+ * the contiguous buffer cache1 at rows y_cu[b] + j (same row layout).  The prefill scoring uses it on the compressed K rows
+ * so that the tcgen05 scoring kernel, whose 128-row tiles start every 124 rows and cannot follow a page table, serves
+ * a paged cache too (the reference's paged scoring kernel reads the pages directly, flash_nsa/inference/topk.py:19-190).
+ * Uses cache0, cache1, kv_table, y_cu, y_maxlen, row_stride, B, page_size, table_stride. */
+int nsa_paged_gather_rows(const NsaPagedPoolParams* p, void* stream);
 
 /* ---- fused paged decode step ---------------------------------------------------------------------------- */
 typedef struct NsaDecodeParams {

@@ -1,6 +1,7 @@
 // Memory-bound pieces of the NSA path: window pooling, window gather (im2col), gate activations, the gated
 // combine and the context-parallel chunk reorder.  All of them move 16 bytes per thread per access and do
 // their arithmetic in fp32.
+#include <algorithm>
 #include "nsa_common.cuh"
 
 namespace nsa {
@@ -545,6 +546,34 @@ __global__ void paged_zero_tails_kernel(NsaPagedPoolParams p) {
   }
 }
 }  // namespace nsa
+
+namespace nsa {
+// dst[y_cu[b] + j] = cache[row of (b, j) in the page table], all heads of a row, for j < y_cu[b+1] - y_cu[b]
+__global__ void paged_gather_rows_kernel(NsaPagedPoolParams p) {
+  const int b = blockIdx.y;
+  const int y0 = p.y_cu[b], n = p.y_cu[b + 1] - y0;
+  const int sh = 31 - __clz(p.page_size);
+  const int chunks = (int)(p.row_stride / 8);
+  const int32_t* tab = p.kv_table + (int64_t)b * p.table_stride;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n * chunks; i += gridDim.x * blockDim.x) {
+    const int j = i / chunks, c = i - j * chunks;
+    const int64_t src = (((int64_t)tab[j >> sh] << sh) + (j & (p.page_size - 1))) * p.row_stride + c * 8;
+    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.cache1) + ((int64_t)y0 + j) * p.row_stride + c * 8)[0] =
+        *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.cache0) + src);
+  }
+}
+}  // namespace nsa
+
+extern "C" int nsa_paged_gather_rows(const NsaPagedPoolParams* p, void* stream) {
+  NSA_REQUIRE(p && p->cache0 && p->cache1 && p->kv_table && p->y_cu, NSA_ERR_BAD_ARG, "paged_gather_rows: null pointer");
+  NSA_REQUIRE(p->page_size > 0 && (p->page_size & (p->page_size - 1)) == 0 && p->row_stride % 8 == 0, NSA_ERR_UNSUPPORTED_SHAPE,
+              "paged_gather_rows: page=%d must be a power of two and rows multiples of 16 bytes", p->page_size);
+  if (p->B <= 0 || p->y_maxlen <= 0) return NSA_OK;
+  const int64_t work = (int64_t)p->y_maxlen * (p->row_stride / 8);
+  dim3 grid((unsigned)std::min<int64_t>((work + 255) / 256, 1024), p->B);
+  paged_gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*p);
+  return check_launch("paged_gather_rows");
+}
 
 extern "C" int nsa_paged_zero_tails(const NsaPagedPoolParams* p, void* stream) {
   NSA_REQUIRE(p && p->cache0 && p->kv_table && p->context_lens, NSA_ERR_BAD_ARG, "paged_zero_tails: null pointer");

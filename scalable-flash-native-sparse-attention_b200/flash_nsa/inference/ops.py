@@ -175,17 +175,35 @@ def cmp_attn_decode(q, k, v, block_tables, context_lens, out=None, num_splits=0,
 
 # ------------------------------------------------------------------------------------------------ top-n
 def _topk(q, k, lse, lse_head_major, meta_args, block_size, top_n, num_inital, num_local, kernel_size, stride, sm_scale,
-          fixed_num_slc_blocks=2048):
+          fixed_num_slc_blocks=2048, y_maxlen=0):
     T, QH, D = q.shape
     kf, page = _flat(k)
     KH = kf.size(1)
     meta = _PagedMeta(*meta_args, page, kernel_size, stride)
     meta.struct.x_maxlen = int(fixed_num_slc_blocks) * block_size   # bound of the sequence length (general-size kernel)
     topk = torch.empty(KH, T, top_n, dtype=torch.int32, device=q.device)
+    ck_rows = 0
+    x_maxlen = meta_args[2]
+    if (y_maxlen and x_maxlen >= 64 and (kernel_size, stride, block_size) == (32, 16, 64) and top_n - num_inital - num_local == 13
+            and QH // KH <= 64 and T):
+        # a prefill chunk: the compressed K rows of the batch are few (tokens / 16), so they are copied out of their pages
+        # into one contiguous buffer and the tcgen05 scoring kernel runs on that (its tiles cannot follow a page table)
+        B = meta_args[0].numel()
+        ck_rows = B * int(y_maxlen)
+        gathered = torch.empty(ck_rows, KH, D, dtype=kf.dtype, device=kf.device)
+        g = S["NsaPagedPoolParams"]()
+        g.cache0, g.cache1 = ptr(kf), ptr(gathered)
+        g.kv_table, g.y_cu = ptr(meta.cmp_table), ptr(meta.y_cu)
+        g.row_stride, g.B, g.H, g.D = kf.stride(0), B, KH, D
+        g.page_size, g.table_stride, g.y_maxlen = page, meta.cmp_table.stride(0), int(y_maxlen)
+        call("nsa_paged_gather_rows", g, q)
+        kf = gathered
+        meta.struct.cmp_table, meta.struct.cmp_table_stride = 0, 0
     p = S["NsaTopkParams"]()
     p.meta, p.hp = meta.struct, _hyper(kernel_size, stride, block_size, 0, top_n, num_inital, num_local)
     p.q, p.ck, p.lse, p.topk, p.probs = ptr(q), ptr(kf), ptr(lse), ptr(topk), 0
     p.q_stride_t, p.ck_stride_t = q.stride(0), kf.stride(0)
+    p.q_rows, p.ck_rows = T, ck_rows
     p.status = ptr(status_word(q.device))
     if lse_head_major:
         p.lse_stride_t, p.lse_stride_h = 1, lse.stride(0)
@@ -205,7 +223,7 @@ def topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables, cont
                  sm_scale=None, fp32=False):
     """-> topk [kh,t,top_n] int32, unused slots = -1"""
     return _topk(q, k, lse, True, (context_lens, x_cu_seqlens, x_maxlen, None, block_tables), block_size, top_n, num_inital,
-                 num_local, kernel_size, stride, sm_scale, fixed_num_slc_blocks)
+                 num_local, kernel_size, stride, sm_scale, fixed_num_slc_blocks, y_maxlen=y_maxlen)
 
 
 @torch.no_grad()
