@@ -11,7 +11,7 @@ any of these calls, shapes depend only on the arguments, so a decode step can be
 from ..ops._common import poll_status, post_status
 from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
                   topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
-                  combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported, zero_cache_tails)
+                  combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported, zero_cache_tails, one_step)
 
 
 def store_kvcache(key, value, k_cache, v_cache, slot_mapping):
@@ -41,17 +41,18 @@ def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, cont
         sm_scale = q.size(-1) ** -0.5
     poll_status(q.device)      # a pipeline time-out of an earlier call raises here, without synchronising
     hp = dict(kernel_size=kernel_size, stride=stride)
-    mean_pooling_prefill(k, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
-    mean_pooling_prefill(v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
-    cmp_o, lse = cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
-                                  sm_scale=sm_scale, **hp)
-    topk = topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
-                        fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks, sm_scale=sm_scale,
-                        block_size=block_size, top_n=top_n, num_inital=num_init_blocks, num_local=num_local_blocks, **hp)
-    slc_o, _ = slc_attn_prefill(q, k, v, topk, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
-                                block_size=block_size, top_n=top_n, sm_scale=sm_scale)
-    swa_o = swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
-                        window_size=window_size, sm_scale=sm_scale)
+    with one_step():   # the four attention ops share the length tables derived from context_lens / x_cu_seqlens
+        mean_pooling_prefill(k, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
+        mean_pooling_prefill(v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
+        cmp_o, lse = cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
+                                      sm_scale=sm_scale, **hp)
+        topk = topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
+                            fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks, sm_scale=sm_scale,
+                            block_size=block_size, top_n=top_n, num_inital=num_init_blocks, num_local=num_local_blocks, **hp)
+        slc_o, _ = slc_attn_prefill(q, k, v, topk, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
+                                    block_size=block_size, top_n=top_n, sm_scale=sm_scale)
+        swa_o = swa_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=block_tables, context_lens=context_lens,
+                            window_size=window_size, sm_scale=sm_scale)
     o = combine_prefill(cmp_o, slc_o, swa_o, w)
     post_status(q.device)
     return o
@@ -87,13 +88,14 @@ def nsa_decode_unfused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping,
     if sm_scale is None:
         sm_scale = q.size(-1) ** -0.5
     hp = dict(kernel_size=kernel_size, stride=stride)
-    kv_mean_pooling_decode(k, v, block_table=block_tables, slot_mapping=cmp_slot_mapping, context_lens=context_lens, **hp)
-    cmp_o, lse = cmp_attn_decode(q, k, v, block_tables=cmp_block_tables, context_lens=context_lens, num_splits=cmp_num_splits,
-                                 sm_scale=sm_scale, **hp)
-    topk = topk_decode(q, k, lse, fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks,
-                       block_tables=cmp_block_tables, context_lens=context_lens, block_size=block_size, top_n=top_n,
-                       num_inital=num_init_blocks, num_local=num_local_blocks, sm_scale=sm_scale, **hp)
-    slc_o, swa_o = fused_slc_swa_attn_decode(q, k, v, topk, num_splits=slc_num_splits, block_tables=block_tables,
-                                             context_lens=context_lens, block_size=block_size, top_n=top_n,
-                                             window_size=window_size, sm_scale=sm_scale)
+    with one_step():
+        kv_mean_pooling_decode(k, v, block_table=block_tables, slot_mapping=cmp_slot_mapping, context_lens=context_lens, **hp)
+        cmp_o, lse = cmp_attn_decode(q, k, v, block_tables=cmp_block_tables, context_lens=context_lens, num_splits=cmp_num_splits,
+                                     sm_scale=sm_scale, **hp)
+        topk = topk_decode(q, k, lse, fixed_y_maxlen=fixed_y_maxlen, fixed_num_slc_blocks=fixed_num_slc_blocks,
+                           block_tables=cmp_block_tables, context_lens=context_lens, block_size=block_size, top_n=top_n,
+                           num_inital=num_init_blocks, num_local=num_local_blocks, sm_scale=sm_scale, **hp)
+        slc_o, swa_o = fused_slc_swa_attn_decode(q, k, v, topk, num_splits=slc_num_splits, block_tables=block_tables,
+                                                 context_lens=context_lens, block_size=block_size, top_n=top_n,
+                                                 window_size=window_size, sm_scale=sm_scale)
     return combine_decode(cmp_o, slc_o, swa_o, w)

@@ -20,25 +20,52 @@ def _hyper(kernel_size=32, stride=16, block_size=64, window=512, top_n=16, num_i
     return h
 
 
+_STEP_TENSORS = None   # inside one_step(): the length tables of the step, built once and shared by its ops
+
+
+class one_step:
+    """Scope of one prefill / decode step: the ops called inside it share the piece tables they derive from the step's
+    context_lens / x_cu_seqlens (about ten tiny launches per op otherwise).  The caller must not change those tensors inside."""
+
+    def __enter__(self):
+        global _STEP_TENSORS
+        self.prev, _STEP_TENSORS = _STEP_TENSORS, {}
+        return self
+
+    def __exit__(self, *exc):
+        global _STEP_TENSORS
+        _STEP_TENSORS = self.prev
+        return False
+
+
 class _PagedMeta:
     """Piece table of an inference step, built with device-side ops only (no synchronisation)."""
 
     def __init__(self, context_lens, x_cu_seqlens, x_maxlen, kv_table, cmp_table, page_size, kernel_size, stride):
         dev = context_lens.device
         B = context_lens.numel()
-        ctx = context_lens.to(torch.int32)
-        if x_cu_seqlens is None:      # decode: one row per sequence
-            self.piece_cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
-            x_len = torch.ones(B, dtype=torch.int32, device=dev)
-            x_maxlen = 1
+        key = (context_lens.data_ptr(), B, None if x_cu_seqlens is None else x_cu_seqlens.data_ptr(), kernel_size, stride)
+        shared = _STEP_TENSORS.get(key) if _STEP_TENSORS is not None else None
+        if shared is not None:
+            self.piece_cu, self.piece_off, self.x_cu, self.y_cu = shared
+            if x_cu_seqlens is None:
+                x_maxlen = 1
         else:
-            self.piece_cu = x_cu_seqlens.to(torch.int32).contiguous()
-            x_len = self.piece_cu[1:] - self.piece_cu[:-1]
-        self.piece_off = (ctx - x_len).contiguous()                     # position of the first new token; -1 for padding rows
-        zero = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.x_cu = torch.cat([zero, torch.cumsum(ctx, 0, dtype=torch.int32)]).contiguous()
-        y_len = torch.clamp((ctx - kernel_size) // stride + 1, min=0).to(torch.int32)
-        self.y_cu = torch.cat([zero, torch.cumsum(y_len, 0, dtype=torch.int32)]).contiguous()
+            ctx = context_lens.to(torch.int32)
+            if x_cu_seqlens is None:      # decode: one row per sequence
+                self.piece_cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+                x_len = torch.ones(B, dtype=torch.int32, device=dev)
+                x_maxlen = 1
+            else:
+                self.piece_cu = x_cu_seqlens.to(torch.int32).contiguous()
+                x_len = self.piece_cu[1:] - self.piece_cu[:-1]
+            self.piece_off = (ctx - x_len).contiguous()                     # position of the first new token; -1 for padding rows
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.x_cu = torch.cat([zero, torch.cumsum(ctx, 0, dtype=torch.int32)]).contiguous()
+            y_len = torch.clamp((ctx - kernel_size) // stride + 1, min=0).to(torch.int32)
+            self.y_cu = torch.cat([zero, torch.cumsum(y_len, 0, dtype=torch.int32)]).contiguous()
+            if _STEP_TENSORS is not None:
+                _STEP_TENSORS[key] = (self.piece_cu, self.piece_off, self.x_cu, self.y_cu)
         self.kv_table = kv_table
         self.cmp_table = cmp_table
         m = S["NsaSeqMeta"]()
