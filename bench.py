@@ -573,6 +573,7 @@ def main():
         del q, k, v, w, do
         torch.cuda.empty_cache()
         extras["single_gpu_128k"] = single_gpu_128k(make_core, run_step, timed, status_ok, dev)
+        extras["varlen_config2"] = varlen_config2(run_step, timed, status_ok, dev)
 
     if rank != 0:
         if world > 1:
@@ -680,6 +681,43 @@ def cp_step_profile(step, sync_all):
         out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
     exposed = out.pop("comm_wait", 0.0)
     return out, exposed
+
+
+def varlen_config2(run_step, timed, status_ok, dev):
+    """BASELINE config 2: four packed sequences with lengths U[4096, 8192] (seed 1002), mean K compression and sigmoid-mul V
+    compression with N(0, 0.02) weights, forward + backward through NSACore on one GPU (the reference publishes no time for
+    it; tests/test_gpu_fullsize.py checks the same case against the oracle)."""
+    import flash_nsa
+    from flash_nsa import NSAHelper
+    rng = random.Random(1002)
+    lens = [rng.randint(4096, 8192) for _ in range(4)]
+    T = sum(lens)
+    g = torch.Generator().manual_seed(1002)
+    mk = lambda h, dd: torch.randn(T, h, dd, generator=g).bfloat16().to(dev)
+    q, k, v, w, do = mk(QH, D), mk(KH, D), mk(KH, D), mk(QH, 3), mk(QH, D)
+    for t in (q, k, v, w):
+        t.requires_grad_(True)
+    cu_host = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    cu = torch.tensor(cu_host, dtype=torch.int32, device=dev)
+    NSAHelper.reset_context_parallel()
+    cfg = flash_nsa.NSAConfig(head_dim=D, num_heads=QH, num_kv_heads=KH, cmp_k_method="mean", cmp_v_method="sigmoid-mul")
+    core = flash_nsa.NSACore(cfg)
+    if core.cmp_v_weight is not None:
+        core.cmp_v_weight.data = (torch.randn(core.cmp_v_weight.shape, generator=g) * 0.02).bfloat16().to(dev)
+
+    def step():
+        out = run_step(core, cu, cu_host, (q, k, v, w, do))
+        for prm in core.parameters():
+            prm.grad = None
+        return out
+
+    ms = timed(step, 5, 3)
+    status_ok("varlen_config2")
+    fm = flops_model(lens)
+    alg = sum(fm[n] for n in ALG_KEYS)
+    NSAHelper.reset_context_parallel()
+    return {"lens": lens, "tokens": T, "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "algorithmic_tflops": alg / (ms * 1e-3) / 1e12,
+            "compression": "K mean, V sigmoid-mul (learned, N(0, 0.02) weights)"}
 
 
 def single_gpu_128k(make_core, run_step, timed, status_ok, dev):
