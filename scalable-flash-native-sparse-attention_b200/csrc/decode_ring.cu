@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   const int n_valid = min(top_n, nk + 1);
   const int nf = min(ni + nl, n_valid);                  // forced slots
   const int n_free = n_valid - nf;
-  const int n_jobs = 2 * n_ct + nf + n_wt + n_free;
+  const int n_jobs = n_ct + ((n_ct + 1) >> 1) + nf + n_wt + n_free;   // the second pass fetches the compressed K tiles in pairs
 
   // ---- set-up: barriers, the job list, the new compressed row
   if (tid == RING_NC * 32) {
@@ -145,9 +145,9 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     };
     for (int i = 0; i < n_ct; ++i) jobs[n++] = job_pack(JOB_CMP_KV, i % RING_NC, i);
     marks[0] = n;
-    for (int i = 0; i < n_ct; ++i) {
-      jobs[n++] = job_pack(JOB_CMP_K, i % RING_NC, i);
-      if (i & 1) win();
+    for (int i = 0; i < n_ct; i += 2) {   // tiles i and i + 1 in the two halves of one slot
+      jobs[n++] = job_pack(JOB_CMP_K, (i >> 1) % RING_NC, i);
+      win();
     }
     marks[1] = n;
     for (int sidx = 0; sidx < nf; ++sidx) jobs[n++] = job_pack(JOB_SLC, RING_NS > 1 ? 1 + sidx % (RING_NS - 1) : 0, sidx);
@@ -189,11 +189,14 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
         if (type == JOB_SLC && idx == nf && !mbar_wait(sel_ready, 0, &budget)) timed_out = true;
         const int row = type <= JOB_CMP_K ? rows[idx] : (type == JOB_WIN ? rows_win[idx] : rows_slc[idx]);
         const uint32_t dst = ring + (uint32_t)s * 2 * TILE_BYTES;
-        tma::expect_tx(full(s), type == JOB_CMP_K ? TILE_BYTES : 2 * TILE_BYTES);
+        const bool k_pair = type == JOB_CMP_K && idx + 1 < n_ct;
+        tma::expect_tx(full(s), (type == JOB_CMP_K && !k_pair) ? TILE_BYTES : 2 * TILE_BYTES);
+        const int row2 = k_pair ? rows[idx + 1] : row;
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
           tma::load_3d(dst + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, full(s));
           if (type != JOB_CMP_K) tma::load_3d(dst + TILE_BYTES + sl * SLAB_BYTES, &tmv, sl * 64, kh, row, full(s));
+          else if (k_pair) tma::load_3d(dst + TILE_BYTES + sl * SLAB_BYTES, &tmk, sl * 64, kh, row2, full(s));
         }
         asm volatile("st.release.cta.shared::cta.b32 [%0], %1;\n" ::"r"(issued), "r"(j + 1) : "memory");
       }
@@ -288,27 +291,32 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
         window_tile(j);
         continue;
       }
-      const int j0 = (job >> 5) << 6;
       wait_job(j);
-      float s[8][4];
-      wts::scores64<D>(s, qf, ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES, lane);
-      release(j);
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int ti = (job >> 5) + half;   // the slot holds K tiles ti (first half) and ti + 1 (second half)
+        if (ti >= n_ct) break;
+        const int j0 = ti << 6;
+        float s[8][4];
+        wts::scores64<D>(s, qf, ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES + half * TILE_BYTES, lane);
+        if (half == 1 || ti + 1 >= n_ct) release(j);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = j0 + nt * 8 + 2 * c_;
-        float e0 = (h_lo && col < Y) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo)) : 0.f;
-        float e1 = (h_lo && col + 1 < Y) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo)) : 0.f;
-        float e2 = (h_hi && col < Y) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi)) : 0.f;
-        float e3 = (h_hi && col + 1 < Y) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi)) : 0.f;
-        float v0 = e0 + e2, v1 = e1 + e3;
+        for (int nt = 0; nt < 8; ++nt) {
+          const int col = j0 + nt * 8 + 2 * c_;
+          float e0 = (h_lo && col < Y) ? fast_exp2(fmaf(s[nt][0], c2, nl_lo)) : 0.f;
+          float e1 = (h_lo && col + 1 < Y) ? fast_exp2(fmaf(s[nt][1], c2, nl_lo)) : 0.f;
+          float e2 = (h_hi && col < Y) ? fast_exp2(fmaf(s[nt][2], c2, nl_hi)) : 0.f;
+          float e3 = (h_hi && col + 1 < Y) ? fast_exp2(fmaf(s[nt][3], c2, nl_hi)) : 0.f;
+          float v0 = e0 + e2, v1 = e1 + e3;
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-          v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-        }
-        if (g_ == nt) {
-          pcm[1 + col] = v0;
-          pcm[2 + col] = v1;
+          for (int o = 4; o < 32; o <<= 1) {
+            v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+          }
+          if (g_ == nt) {
+            pcm[1 + col] = v0;
+            pcm[2 + col] = v1;
+          }
         }
       }
     }
