@@ -520,9 +520,9 @@ def main():
                 t.record_stream(s_out)
         s_main.wait_stream(s_out)
 
-    # enough steps to amortise the un-hidden first copy-in / last copy-out (42 ms each at 64K over PCIe): 48 short steps on one
-    # GPU, 16 of the long multi-GPU steps
-    n_e2e = 0 if args.no_e2e else (48 if world == 1 else 16)
+    # enough steps to amortise the un-hidden first copy-in / last copy-out (42 ms each at 64K over PCIe): 96 short steps on one
+    # GPU (5 s), 16 of the long multi-GPU steps
+    n_e2e = 0 if args.no_e2e else (96 if world == 1 else 16)
     if n_e2e:
         e2e_loop(2)
     sync_all()
