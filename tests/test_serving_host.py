@@ -96,3 +96,17 @@ def test_prefill_and_decode_step_tensors():
                 assert st.cmp_slot_mapping[i].item() == s.cmp_block_table[j // 16] * 16 + j % 16
             else:
                 assert st.cmp_slot_mapping[i].item() == -1
+
+
+def test_index_ranges_follow_the_cell_size():
+    """Host-side rule of the selected backward's index: a range as long as it takes for a (range, block) cell to hold 128 rows,
+    at least 4096 rows, none once that needs more than 32 MiB of q per range (long sequences under context parallelism)."""
+    from flash_nsa.ops.topk import backward_index_sizes
+    G, D = 16, 128
+    assert backward_index_sizes(G, D, 65536, 1024) == (8192, 512)        # 64K tokens on one GPU
+    assert backward_index_sizes(G, D, 32768, 512) == (4096, 512)
+    assert backward_index_sizes(G, D, 131072, 2048)[0] == 0              # 128K tokens: cells of 128 rows would need 16K-row ranges
+    assert backward_index_sizes(G, D, 131072, 16384)[0] == 0             # one shard of 8 at 1M tokens
+    assert backward_index_sizes(G, D, 23888, 118) == (4096, 512)         # packed short sequences: the floor of 4096 rows
+    assert backward_index_sizes(G, D, 2048, 32)[0] == 0                  # fewer rows than one range
+    assert backward_index_sizes(4, 64, 65536, 1024)[1] == 64 * 32        # 32 tokens per query tile at G = 4
