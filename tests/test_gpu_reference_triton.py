@@ -1,0 +1,20 @@
+"""This build against the reference's own Triton kernels on the same GPU and inputs (o and every gradient of NSACore on two
+packed sequences of 4096 tokens in all, 64 q heads / 4 kv heads / d = 128).  The reference package is the pip-installed copy
+under baseline/_ref (git-ignored; it travels with the repository to the GPU box); each side runs in a process of its own
+because both packages are called flash_nsa.  Skips where that copy is absent or its kernels do not compile or run."""
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_core_matches_the_reference_kernels():
+    import reference_gpu_compare as R
+    res = R.compare()
+    if "unavailable" in res:
+        pytest.skip(res["unavailable"])
+    for name in ("o", "dq", "dk", "dv", "dw"):
+        r = res[name]
+        # two bf16 implementations, each within 2e-2 * max(1, max|x|) of the fp32 oracle: the bulk is held to that bound
+        # against each other as well (measured: at most 1e-5 of the elements beyond it, none beyond twice the bound)
+        assert r["frac_over_2e-2"] <= 1e-3, (name, r)
+        assert r["max_abs_diff"] <= 4e-2 * max(1.0, r["max_abs_ref"]), (name, r)
