@@ -19,3 +19,17 @@ def test_core_matches_the_reference_kernels():
         # (measured over several runs: at most 1.2e-5 of the elements beyond it, the largest difference 0.06 of max|ref|)
         assert r["frac_over_2e-2"] <= 1e-3, (name, r)
         assert r["max_abs_diff"] <= 0.15 * max(1.0, r["max_abs_ref"]), (name, r)
+
+
+def test_paged_prefill_and_decode_match_the_reference_kernels():
+    """nsa_prefill of three prompts and one nsa_decode step over the same paged caches (pages of 256 rows: the reference's
+    window branch over a paged cache needs that), against the reference's inference kernels."""
+    import reference_gpu_compare as R
+    res = R.compare_inference()
+    if "unavailable" in res:
+        pytest.skip(res["unavailable"])
+    for name in ("prefill", "decode"):
+        r = res[name]
+        assert r["frac_over_2e-2"] <= 1e-3, (name, r)
+        assert r["max_abs_diff"] <= 0.15 * max(1.0, r["max_abs_ref"]), (name, r)
+
