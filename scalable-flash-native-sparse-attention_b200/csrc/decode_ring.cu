@@ -111,35 +111,18 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   const int n_jobs = n_ct + ((n_ct + 1) >> 1) + nf + n_wt + n_free;   // the second pass fetches the compressed K tiles in pairs
 
   // ---- set-up: barriers, the job list, the new compressed row
-  // The producer warp sets the barriers up and fetches the first compressed tiles at once (the job list starts with them,
-  // and a lane per tile looks its page up), while the other warps build the job list and the row tables; the last
-  // compressed tile is left to the loop below: the row that this step pools lies in it and is written during the set-up.
-  const int n_first = max(0, min(n_slots, n_ct - 1));
-  if (warp == RING_NC) {
-    if (lane == 0) {
-      tma::prefetch_map(&tmk);
-      tma::prefetch_map(&tmv);
-      for (int s = 0; s < n_slots; ++s) {
-        mbar_init(full(s), 1);
-        mbar_init(empty(s), 1);
-      }
-      mbar_init(sel_ready, 1);
-      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(issued), "r"(n_first) : "memory");
-      fence_mbar_init();
+  if (tid == RING_NC * 32) {
+    tma::prefetch_map(&tmk);
+    tma::prefetch_map(&tmv);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < n_slots; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), 1);
     }
-    const int my_row = lane < n_first ? (int)cmprow(lane << 6) : 0;
-    for (int j = 0; j < n_first; ++j) {
-      const int row = __shfl_sync(0xffffffffu, my_row, j);
-      if (lane == 0) {
-        const uint32_t dst = ring + (uint32_t)j * 2 * TILE_BYTES;
-        tma::expect_tx(full(j), 2 * TILE_BYTES);
-#pragma unroll
-        for (int sl = 0; sl < SLABS; ++sl) {
-          tma::load_3d(dst + sl * SLAB_BYTES, &tmk, sl * 64, kh, row, full(j));
-          tma::load_3d(dst + TILE_BYTES + sl * SLAB_BYTES, &tmv, sl * 64, kh, row, full(j));
-        }
-      }
-    }
+    mbar_init(sel_ready, 1);
+    asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(issued), "r"(0) : "memory");
+    fence_mbar_init();
   }
   // The first cache row of every tile whose place is known now: the page-table look-ups of all tiles are in flight at
   // once (the rows of the free blocks are filled in by the selection).
@@ -198,7 +181,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   if (warp == RING_NC) {
     // ================================================= producer (one lane)
     if (lane == 0) {
-      for (int j = n_first; j < n_jobs; ++j) {
+      for (int j = 0; j < n_jobs; ++j) {
         const int job = jobs[j], type = job & 3, idx = job >> 5;
         const int s = j % n_slots;
         if (j >= n_slots && !mbar_wait(empty(s), ((j / n_slots) - 1) & 1, &budget)) timed_out = true;
