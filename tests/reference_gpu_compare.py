@@ -51,8 +51,19 @@ def run_side(which, out_path):
     o = core(q, k, v, w, cu)
     o.backward(do)
     torch.cuda.synchronize()
+    # the selection itself, from the ops both packages export under the same names
+    from flash_nsa.ops.compress_kv import mean_pooling_fwd
+    from flash_nsa.ops.compress_attn import cmp_attn_fwd
+    from flash_nsa.ops.topk import slc_topk_indices
+    pkg.NSAHelper.init_cu_seqlens(cu)
+    with torch.no_grad():
+        ck, cv = mean_pooling_fwd(k), mean_pooling_fwd(v)
+        _, lse = cmp_attn_fwd(q, ck, cv)
+        res = slc_topk_indices(q, ck, lse, maybe_efficient_version=True)
+    topk = res[0] if isinstance(res, (tuple, list)) else res
+    torch.cuda.synchronize()
     torch.save({"o": o.detach().float().cpu(), "dq": q.grad.float().cpu(), "dk": k.grad.float().cpu(), "dv": v.grad.float().cpu(),
-                "dw": w.grad.float().cpu()}, out_path)
+                "dw": w.grad.float().cpu(), "topk": topk.to(torch.int64).cpu()}, out_path)
 
 
 INF_LENS = [700, 1025, 3000]      # contexts of the paged case (prompt = all but the last token, then one decode step)
@@ -135,6 +146,19 @@ def compare():
                 return {"unavailable": f"{which} side failed: " + (r.stderr.strip().splitlines() or ["?"])[-1][:300]}
             res[which] = torch.load(path)
     out = {"tokens": sum(LENS), "lens": LENS, "heads": [QH, KH, D]}
+    # selections as sets of the valid entries (blocks 0 .. the token's own block) of every (kv head, token) row
+    ta, tb = res["ours"]["topk"], res["ref"]["topk"]
+    pos = torch.cat([torch.arange(L) for L in LENS])
+    nk = (pos // 64).view(1, -1, 1)
+    n_blk = int(nk.max()) + 1
+    def member(t):      # [kh, rows, n_blk] membership of the valid entries
+        valid = (t >= 0) & (t <= nk)
+        m = torch.zeros(t.shape[0], t.shape[1], n_blk + 1, dtype=torch.bool)
+        m.scatter_(2, torch.where(valid, t, torch.full_like(t, n_blk)), True)
+        return m[..., :n_blk]
+    sym = (member(ta) ^ member(tb)).sum(-1)          # size of the symmetric difference per (kv head, token) row
+    out["topk"] = {"rows": int(sym.numel()), "rows_with_a_different_set": int((sym > 0).sum()),
+                   "fraction": (sym > 0).float().mean().item(), "largest_symmetric_difference": int(sym.max())}
     for name in ("o", "dq", "dk", "dv", "dw"):
         a, b = res["ours"][name], res["ref"][name]
         err = (a - b).abs()

@@ -12,6 +12,11 @@ def test_core_matches_the_reference_kernels():
     res = R.compare()
     if "unavailable" in res:
         pytest.skip(res["unavailable"])
+    # selections: both kernels round the block scores to half precision (p^3), so near-ties at the end of a list can fall
+    # either way (measured: 0.6-0.9 % of the rows differ, by one swapped block; the reference's own kernel disagrees with its
+    # fp32 torch code on a similar share of rows)
+    tk = res["topk"]
+    assert tk["fraction"] <= 0.03 and tk["largest_symmetric_difference"] <= 6, tk
     for name in ("o", "dq", "dk", "dv", "dw"):
         r = res[name]
         # two bf16 implementations, each within 2e-2 * max(1, max|x|) of the fp32 oracle, with unordered fp32 / bf16 adds on
