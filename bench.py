@@ -266,11 +266,72 @@ def reference_gpu_arm(args):
                      "ms_forward": ms_fwd, "ms_backward": ms - ms_fwd, "ms_per_step_4k": times[4096][0],
                      "config": {"workload": f"reference NSACore fwd+bwd, one causal sequence of {T} tokens, {QH}/{KH}/{D}", "tokens": T},
                      "versions": {"triton": __import__("triton").__version__, "torch": torch.__version__}})
+        try:
+            line["decode"] = reference_gpu_decode(dev)
+        except Exception as e:  # noqa: BLE001
+            line["decode"] = {"unavailable": f"{type(e).__name__}: {(str(e).strip().splitlines() or [''])[0]}"[:300]}
         print(json.dumps(line))
     except BaseException as e:  # noqa: BLE001  (an import error, a JIT failure, an unsupported op: all are "did not run")
         if isinstance(e, KeyboardInterrupt):
             raise
         unavailable(f"{type(e).__name__}: {str(e).strip().splitlines()[0] if str(e).strip() else ''}")
+
+
+def reference_gpu_decode(dev):
+    """The reference's own nsa_decode on the shapes of config 4 (batch 64, contexts U[4096, 8192] with seed 1004, 32 q / 8 kv
+    heads, d = 128, page 256, shuffled page tables) and of its 4 GiB sweep at 8K and 64K tokens; caches filled with seeded
+    N(0,1) values (the timing does not depend on them), eager and replayed from a CUDA graph."""
+    from flash_nsa.inference import nsa_decode
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    def case(ctx, qh, kh, d, page, seed):
+        rng = random.Random(seed)
+        B = len(ctx)
+        n_tok = [-(-L // page) for L in ctx]
+        n_cmp = [-(-max((L - 32) // 16 + 1, 1) // page) for L in ctx]
+        total = sum(n_tok) + sum(n_cmp)
+        free = list(range(total))
+        rng.shuffle(free)
+        g = torch.Generator(device=dev).manual_seed(seed)
+        kc = torch.randn(total, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        vc = torch.randn(total, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        bt = torch.full((B, max(n_tok)), -1, dtype=torch.int32)
+        cbt = torch.full((B, max(n_cmp)), -1, dtype=torch.int32)
+        for b in range(B):
+            for i in range(n_tok[b]):
+                bt[b, i] = free.pop()
+            for i in range(n_cmp[b]):
+                cbt[b, i] = free.pop()
+        q = torch.randn(B, qh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        w = torch.randn(B, qh, 3, device=dev, dtype=torch.bfloat16, generator=g)
+        args = (q, kc, vc, w, torch.tensor(ctx, dtype=torch.int32, device=dev), bt.to(dev),
+                torch.full((B,), -1, dtype=torch.int32, device=dev), cbt.to(dev))
+        out = {"ms_eager": timed(lambda: nsa_decode(*args), 20)}
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                nsa_decode(*args)
+            out["ms_cuda_graph"] = timed(graph.replay, 50)
+        except Exception as e:  # noqa: BLE001
+            out["cuda_graph"] = f"not captured: {type(e).__name__}"
+        return out
+
+    rng = random.Random(1004)
+    res = {"config4": case([rng.randint(4096, 8192) for _ in range(64)], 32, 8, 128, 256, 1004)}
+    for L in (8192, 65536):
+        res[f"sweep_4gib_{L}"] = case([L] * (1024 * 2048 // L), 64, 4, 128, 256, L)
+    return res
 
 
 # ----------------------------------------------------------------------------------------------- context-parallel parity check
