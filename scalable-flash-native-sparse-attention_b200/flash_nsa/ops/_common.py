@@ -11,8 +11,21 @@ def stream_ptr(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+_empty_stub = {}
+
+
 def ptr(t):
-    return 0 if t is None else t.data_ptr()
+    """Device address of a tensor for the C ABI; None -> NULL.  An EMPTY tensor has no storage (data_ptr() is 0), but the
+    entry points treat NULL as a missing argument, so it gets the address of a small per-device stub instead (nothing is read
+    or written through it: every entry point returns before launching when there are no rows)."""
+    if t is None:
+        return 0
+    if t.numel() == 0 and t.is_cuda:
+        key = t.device.index
+        if key not in _empty_stub:
+            _empty_stub[key] = torch.zeros(256, dtype=torch.uint8, device=t.device)
+        return _empty_stub[key].data_ptr()
+    return t.data_ptr()
 
 
 def hyper(window=None):

@@ -320,6 +320,35 @@ def test_nsa_core_forward_backward(methods):
         bulk("dWv", core.cmp_v_weight.grad, wvr.grad, frac=0.99)
 
 
+def test_nsa_core_with_empty_and_tiny_sequences_in_the_batch():
+    """A packed batch with zero-length sequences, a one-token sequence and one shorter than the compression window (no
+    compressed row at all), next to ordinary ones: forward and every gradient against the oracle; then an empty batch."""
+    lens = [70, 0, 1, 513, 0, 31]
+    QH, KH, D = 8, 2, 64
+    q, k, v, w, do, cu = _mk(lens, QH, KH, D, seed=23)
+    fn = _setup(cu)
+    core = fn.NSACore(fn.NSAConfig(head_dim=D, num_heads=QH, num_kv_heads=KH))
+    qd, kd, vd, wd = [t.cuda().clone().requires_grad_(True) for t in (q, k, v, w)]
+    o = core(qd, kd, vd, wd, torch.tensor(cu, dtype=torch.int32, device="cuda"))
+    topk_gpu = o.grad_fn.saved_tensors[-1].cpu()
+    (o.float() * do.cuda().float()).sum().backward()
+    qr, kr, vr, wr = _leaf(q, k, v, w)
+    o_ref = O.nsa_forward(qr, kr, vr, wr, cu, quant="fp16_cubed", topk=topk_gpu)
+    (o_ref * do.float()).sum().backward()
+    for name, got, ref in (("o", o, o_ref), ("dq", qd.grad, qr.grad), ("dk", kd.grad, kr.grad), ("dv", vd.grad, vr.grad),
+                           ("dw", wd.grad, wr.grad)):
+        assert torch.isfinite(got).all(), name
+        err = (got.float().cpu() - ref.float()).abs().max().item()
+        assert err <= TOL * max(1.0, ref.abs().max().item()), (name, err)
+    # no tokens at all: shapes are kept, nothing is launched that could fault
+    z = lambda h, d_: torch.zeros(0, h, d_, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+    q0, k0, v0, w0 = z(QH, D), z(KH, D), z(KH, D), z(QH, 3)
+    o0 = core(q0, k0, v0, w0, torch.tensor([0, 0], dtype=torch.int32, device="cuda"))
+    assert o0.shape == (0, QH, D)
+    o0.sum().backward()
+    assert q0.grad is not None and q0.grad.shape == (0, QH, D)
+
+
 def test_hf_core_equals_megatron_core():
     """The identity the reference's own test prints (test.py:320-349): both module flavours agree."""
     lens = [500, 400]
