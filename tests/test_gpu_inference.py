@@ -291,6 +291,37 @@ def test_rows_past_a_sequence_end_may_hold_anything():
             assert (od[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"{fn.__name__} seq {b}"
 
 
+def test_decode_of_very_short_contexts():
+    """The first tokens of a sequence: no compressed row yet (context < 32), the first one (32), a single selection block,
+    the first block boundary (64, 65): one fused decode step each, against the oracle."""
+    from flash_nsa import nsa_decode
+    QH, KH, D = 16, 4, 128
+    lens = [1, 2, 31, 32, 33, 63, 64, 65, 128, 129]
+    B = len(lens)
+    seqs = _seqs(lens, QH, KH, D, seed=91)
+    cache = Cache(lens, KH, D, seed=13)
+    for b, s_ in enumerate(seqs):
+        cache.store(b, s_["k"], s_["v"])
+    cache.cuda()
+    # the compressed rows that earlier steps would have written: all but the one this step completes
+    from flash_nsa.inference import mean_pooling_prefill
+    y_old = [max((L - 1 - 32) // 16 + 1, 0) for L in lens]
+    y_cu = torch.tensor([0] + torch.tensor(y_old).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    slots_old = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_old[b])], dtype=torch.int32, device="cuda")
+    if slots_old.numel():
+        for c in (cache.k, cache.v):
+            mean_pooling_prefill(c, y_cu, max(y_old), slot_mapping=slots_old, block_table=cache.block_tables)
+    slot = [cache.cmp_slot(b, (L - 32) // 16) if (L % 16 == 0 and L >= 32) else -1 for b, L in enumerate(lens)]
+    qd = torch.stack([seqs[b]["q"][lens[b] - 1] for b in range(B)]).cuda()
+    wd = torch.stack([seqs[b]["w"][lens[b] - 1] for b in range(B)]).cuda()
+    od = nsa_decode(qd, cache.k, cache.v, wd, torch.tensor(lens, dtype=torch.int32, device="cuda"), cache.block_tables,
+                    torch.tensor(slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+    assert bool(torch.isfinite(od).all())
+    for b in range(B):
+        ref = _oracle(seqs[b], lens[b])[-1:]
+        assert (od[b:b + 1].float().cpu() - ref).abs().max().item() <= TOL, f"context {lens[b]}"
+
+
 def test_decode_writes_the_new_compressed_row():
     from flash_nsa.inference import kv_mean_pooling_decode
     KH, D = 2, 64
