@@ -694,8 +694,9 @@ def roofline_of(name, ms, flops, tokens, peak_tf, peak_gbs, peak_src):
             out.update({"traffic": traffic, "traffic_source": f"{t['source']}: dram__bytes_read.sum + dram__bytes_write.sum at {t['tokens']} "
                                                               f"tokens" + (f" x {tokens}/{t['tokens']}" if tokens != t["tokens"] else ""),
                         "dram_gbs_from_traffic": gbs, "dram_frac_from_traffic": gbs / peak_gbs, "hbm_peak_gbs": peak_gbs})
-            if gbs / peak_gbs > ach / peak_tf:
-                bound = "hbm"
+            # achieved / peak / frac above are the contraction's FLOPs against the tensor roof, so `bound` stays "tensor"; the
+            # DRAM side (measured traffic, not algorithmic bytes) is reported beside it and flagged when it is the busier unit
+            out["dram_busier_than_tensor"] = bool(gbs / peak_gbs > ach / peak_tf)
     out["bound"] = bound
     return out
 
