@@ -1093,9 +1093,12 @@ def decode_sweep_4gib(dev):
     out = []
     row = kh * d * 2
     peak_gbs = load_peaks()[1]
-    for L in (4096, 8192, 16384, 32768, 65536, 131072):
-        B = total_tokens // L
-        perm = torch.randperm(tok_pages, generator=torch.Generator().manual_seed(L)).to(torch.int32)
+    from flash_nsa.inference.ops import decode_cluster_size
+    # the reference's six points (batch = 4 GiB / sequence), then few long sequences: the case a cluster per (sequence, kv
+    # head) is for
+    points = [(L, total_tokens // L) for L in (4096, 8192, 16384, 32768, 65536, 131072)] + [(32768, 1), (131072, 1), (131072, 4)]
+    for L, B in points:
+        perm = torch.randperm(tok_pages, generator=torch.Generator().manual_seed(L))[:B * (L // page)].to(torch.int32)
         bt = perm.view(B, L // page).to(dev)
         y = (L - 32) // 16 + 1
         per = -(-y // page)
@@ -1124,7 +1127,8 @@ def decode_sweep_4gib(dev):
         ms = e0.elapsed_time(e1) / 30
         alg = B * (3 * y * row + 2 * (16 * 64 + 513) * row)
         out.append({"seqlen": L, "batch": B, "ms_cuda_graph": ms, "tokens_per_s": B / (ms * 1e-3), "hbm_frac": alg / (ms * 1e-3) / 1e9 / peak_gbs,
-                    "reference_h800_ms_cuda_graph": published[L]})
+                    "ctas_per_seq_and_kv_head": decode_cluster_size(B, kh, page, bt.stride(0)),
+                    "reference_h800_ms_cuda_graph": published[L] if B == total_tokens // L else None})
     return out
 
 

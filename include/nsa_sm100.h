@@ -320,10 +320,16 @@ typedef struct NsaDecodeParams {
 } NsaDecodeParams;
 /* replaces the whole body of nsa_decode, flash_nsa/inference/__init__.py:160-257 (8 launches there): pooling of the new
  * compressed row, compressed attention, block scores + top-n, selected and sliding-window attention, gated combine,
- * one CTA per (sequence, kv head): a producer warp streams the K/V tiles of the step through a shared-memory ring with
+ * one CTA (or one cluster, see below) per (sequence, kv head): a producer warp streams the K/V tiles of the step through a shared-memory ring with
  * bulk tensor loads, six consumer warps work on them.  Needs kernel 32 / stride 16 / block 64 and at most 16 query heads
  * per kv head.                                                                                                      */
 int nsa_decode_fused(const NsaDecodeParams* p, void* stream);
+/* How many CTAs nsa_decode_fused would give each (sequence, kv head) of this step: 1, or 2 / 4 / 8 (a thread-block cluster
+ * that splits the tiles of the step and exchanges scores and partial outputs through distributed shared memory) when the
+ * step has few sequences and kv_table_stride * page_size, the bound on the context lengths the host knows, is 16K tokens
+ * or more.  The reference splits long contexts over CTAs with its num_splits arguments
+ * (flash_nsa/inference/__init__.py:160-257); here the library decides.  Reads B, KH, page_size, kv_table_stride only.  */
+int nsa_decode_cluster_size(const NsaDecodeParams* p);
 
 /* ---- context-parallel chunk reorder ------------------------------------------------------------------ */
 typedef struct NsaReorderParams {

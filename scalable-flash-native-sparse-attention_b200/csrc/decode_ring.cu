@@ -13,16 +13,28 @@
 //   1. compressed attention: tiles of compressed K/V round-robin over the six consumers            -> cmp_o, lse
 //   2. block scores: the same K tiles again (from L2), P[j] = sum_heads exp2(s - lse)               -> pcm[]
 //   3. top-n (pool 4 -> 1 + the row before; ties: lowest block index): up to 256 blocks by rank counting on the 128
-//      threads of consumers 0-3 (rank = number of candidates that beat mine), longer contexts by rounds of warp-wide
-//      arg-max on consumer 0
-//   4. consumers 1-3 work through the forced blocks meanwhile; then the free blocks round-robin over consumers 0-3 (the
-//      producer waits for the selection before it fetches them)
+//      threads of consumers 0-3 (rank = number of candidates that beat mine), longer contexts by rounds of arg-max over
+//      the same 128 threads (a thread keeps the best of its run of blocks; one warp reduction and one barrier per round)
+//   4. the forced blocks (their tiles arrive while the selection runs), then the free blocks, round-robin over consumers
+//      0-3 (the producer waits for the selection before it fetches the free ones)
 //   W. consumers 4-5 do the sliding-window tiles once their share of 1 is stored: these depend on nothing, and their
 //      jobs are spread through the list from phase 2 on (one after every two compressed tiles), so that their loads fill
 //      the time in which the others synchronise, merge and select and would leave the memory system idle
 //   5. o = sigmoid(w0) cmp_o + sigmoid(w1) slc_o + sigmoid(w2) swa_o
 // Partial softmax states are merged through shared memory after 1 and after 4; that region holds the score arrays in
 // between.  Bytes read per (sequence, kv head): compressed K twice and V once, 16 selected blocks and <= 9 window tiles.
+//
+// Few sequences with long contexts (fewer CTAs than half the SMs) run as thread-block CLUSTERS of 2, 4 or 8 CTAs per
+// (sequence, kv head), XC = true: CTA r of the cluster takes every CS-th compressed tile, window tile and selected slot.
+// Three exchanges through distributed shared memory: (1) the log-sum-exp of each CTA's share of the compressed rows, read
+// by every CTA to form the global one; (2) every head-summed probability is stored into the score array of EVERY CTA, and
+// each CTA then makes the same selection for itself; (3) every CTA reads the others' normalised partial outputs of the three
+// branches with their log-sum-exps, merges them and writes its slice of the output row.  The exchanges are mbarriers that each CTA's elected
+// thread arrives on remotely (bounded waits like every other one here); one hardware cluster barrier after the barrier
+// initialisation and one before exit (a CTA's shared memory must outlive every remote access to it).
+#include <cstdio>
+#include <cstdlib>
+
 #include "tma.cuh"
 #include "warp_tile_smem.cuh"
 
@@ -36,7 +48,54 @@ constexpr int JOB_CMP_KV = 0, JOB_CMP_K = 1, JOB_WIN = 2, JOB_SLC = 3;
 
 __host__ __device__ constexpr int job_pack(int type, int cons, int idx) { return type | (cons << 2) | (idx << 5); }
 
-template <int D, int RING_NC, int RING_NS>
+// ---- cluster helpers (distributed shared memory)
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank) {   // shared::cta address -> the same place in CTA `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_peer(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ld_peer(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t peer_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(peer_bar) : "memory");
+}
+// bounded wait with cluster-scope acquire: what the peers stored before their arrival is visible afterwards
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* budget) {
+  for (int i = 0; i < *budget; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  *budget = 8;
+  return false;
+}
+__device__ __forceinline__ void cluster_barrier() {   // every thread of every CTA of the cluster
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;\n" ::: "memory");
+}
+constexpr int RING_MAX_CLUSTER = 8;
+
+template <int D, int RING_NC, int RING_NS, bool XC>
 __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     decode_ring_kernel(NsaDecodeParams p, int n_slots, int job_cap, const __grid_constant__ CUtensorMap tmk,
                        const __grid_constant__ CUtensorMap tmv) {
@@ -60,18 +119,22 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   int* rows_win = rows + ((p.y_cap + 63) >> 6);
   int* rows_slc = rows_win + RING_WIN_ROWS;
   float* fac = reinterpret_cast<float*>(rows_slc + 32);          // [RING_NC][16] merge weights, then [3][16] gates
-  int* marks = reinterpret_cast<int*>(fac + (RING_NC + 3) * 16);  // [2] end of the phase-1 / phase-2 part of the job list
-  const uint32_t bars = (smem_u32(marks + 2) + 7u) & ~7u;         // full[n_slots], empty[n_slots], sel_ready
+  float* lse_x = fac + (RING_NC + 3) * 16;                        // [3][16] this CTA's log-sum-exp of its share: cmp, slc, window
+  float* xw = lse_x + 48;                                         // [RING_MAX_CLUSTER][3][16] merge weights of the CTAs' partials
+  int* marks = reinterpret_cast<int*>(xw + RING_MAX_CLUSTER * 48);  // [3] end of the phase-1 / phase-2 part of the job list, its length
+  const uint32_t bars = (smem_u32(marks + 3) + 7u) & ~7u;         // full[n_slots], empty[n_slots], sel_ready, issued, xbar[3]
   auto full = [&](int s) { return bars + 8 * s; };
   auto empty = [&](int s) { return bars + 8 * (n_slots + s); };
   const uint32_t sel_ready = bars + 16 * n_slots;
   const uint32_t issued = sel_ready + 8;   // number of jobs whose loads have been issued (written by the producer)
+  const uint32_t xbar = issued + 8;        // three cluster exchanges, each used once
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g_ = lane >> 2, c_ = lane & 3;
   // the kv heads of a sequence are neighbours in launch order: they read the same token rows (window, forced blocks,
   // compressed rows) at about the same time, 256 bytes each out of the same 2 KB of DRAM
-  const int kh = blockIdx.x, b = blockIdx.y;
+  const int CS = XC ? (int)cluster_size() : 1, cr = XC ? (int)cluster_rank() : 0;   // cluster = CS neighbours in x
+  const int kh = XC ? blockIdx.x / CS : blockIdx.x, b = blockIdx.y;
   const int G = p.QH / p.KH;
   const int ctx = p.context_lens[b];
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.o) + (int64_t)b * p.o_stride_t + (int64_t)kh * G * D;
@@ -79,9 +142,11 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     if (tid == 0 && p.status) atomicOr(p.status, 8);
     return;
   }
-  if (ctx <= 0) {
-    for (int i = tid; i < G * CH; i += blockDim.x) reinterpret_cast<uint4*>(out)[i] = make_uint4(0, 0, 0, 0);
-    if (p.topk_out && tid < p.hp.top_n) p.topk_out[((int64_t)kh * p.B + b) * p.hp.top_n + tid] = -1;
+  if (ctx <= 0) {   // the whole cluster leaves here, before any exchange
+    if (cr == 0) {
+      for (int i = tid; i < G * CH; i += blockDim.x) reinterpret_cast<uint4*>(out)[i] = make_uint4(0, 0, 0, 0);
+      if (p.topk_out && tid < p.hp.top_n) p.topk_out[((int64_t)kh * p.B + b) * p.hp.top_n + tid] = -1;
+    }
     return;
   }
   const int t = ctx - 1, nk = t >> 6;
@@ -101,14 +166,16 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   __nv_bfloat16* vc = reinterpret_cast<__nv_bfloat16*>(p.v_cache) + kh * D;
   const int64_t cs = p.cache_stride_t;
 
-  const int n_ct = (Y + 63) >> 6;
+  const int n_ct_all = (Y + 63) >> 6;
+  const int n_ct = XC ? (n_ct_all - cr + CS - 1) / CS : n_ct_all;   // this CTA's compressed tiles: cr, cr + CS, ...
+  auto ct_row0 = [&](int li) { return (XC ? li * CS + cr : li) << 6; };   // first compressed row of local tile li
   const int lo = max(0, t - W);
   const int w_k0 = (lo >> 6) << 6;                       // first window tile
   const int n_wt = ((t - w_k0) >> 6) + 1;                // window tiles
   const int n_valid = min(top_n, nk + 1);
   const int nf = min(ni + nl, n_valid);                  // forced slots
   const int n_free = n_valid - nf;
-  const int n_jobs = n_ct + ((n_ct + 1) >> 1) + nf + n_wt + n_free;   // the second pass fetches the compressed K tiles in pairs
+  // window tile wi and selected slot s belong to CTA wi % CS and s % CS
 
   // ---- set-up: barriers, the job list, the new compressed row
   if (tid == RING_NC * 32) {
@@ -121,13 +188,15 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       mbar_init(empty(s), 1);
     }
     mbar_init(sel_ready, 1);
+    if (XC)
+      for (int i = 0; i < 3; ++i) mbar_init(xbar + 8 * i, CS);
     asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(issued), "r"(0) : "memory");
     fence_mbar_init();
   }
   // The first cache row of every tile whose place is known now: the page-table look-ups of all tiles are in flight at
   // once (the rows of the free blocks are filled in by the selection).
   for (int i = tid; i < n_ct + n_wt + nf; i += blockDim.x) {
-    if (i < n_ct) rows[i] = (int)cmprow(i << 6);
+    if (i < n_ct) rows[i] = (int)cmprow(ct_row0(i));
     else if (i < n_ct + n_wt) rows_win[i - n_ct] = (int)tokrow(w_k0 + ((i - n_ct) << 6));
     else {
       const int sidx = i - n_ct - n_wt;
@@ -137,12 +206,15 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   // Job list: (type, consumer, index) in the order the producer fetches them.
   if (tid == 32) {
     int n = 0, wi = 0;
+    int wl = 0, sl = 0;   // local counters spread this CTA's jobs over its consumers
     auto win = [&]() {
+      while (XC && wi < n_wt && wi % CS != cr) ++wi;
       if (wi < n_wt) {
-        jobs[n++] = job_pack(JOB_WIN, RING_NS + wi % (RING_NC - RING_NS), wi);
+        jobs[n++] = job_pack(JOB_WIN, RING_NS + wl++ % (RING_NC - RING_NS), wi);
         ++wi;
       }
     };
+    auto mine = [&](int slot_idx) { return !XC || slot_idx % CS == cr; };
     for (int i = 0; i < n_ct; ++i) jobs[n++] = job_pack(JOB_CMP_KV, i % RING_NC, i);
     marks[0] = n;
     for (int i = 0; i < n_ct; i += 2) {   // tiles i and i + 1 in the two halves of one slot
@@ -150,9 +222,17 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       win();
     }
     marks[1] = n;
-    for (int sidx = 0; sidx < nf; ++sidx) jobs[n++] = job_pack(JOB_SLC, RING_NS > 1 ? 1 + sidx % (RING_NS - 1) : 0, sidx);
-    while (wi < n_wt) win();
-    for (int fi = 0; fi < n_free; ++fi) jobs[n++] = job_pack(JOB_SLC, fi % RING_NS, nf + fi);
+    for (int sidx = 0; sidx < nf; ++sidx)
+      if (mine(sidx)) jobs[n++] = job_pack(JOB_SLC, RING_NS > 1 ? 1 + sl++ % (RING_NS - 1) : 0, sidx);
+    for (;;) {
+      const int before = n;
+      win();
+      if (n == before) break;
+    }
+    sl = 0;
+    for (int fi = 0; fi < n_free; ++fi)
+      if (mine(nf + fi)) jobs[n++] = job_pack(JOB_SLC, sl++ % RING_NS, nf + fi);
+    marks[2] = n;
   }
   {
     const int slot = p.slot_mapping ? p.slot_mapping[b] : -1;
@@ -175,18 +255,24 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     }
   }
   __syncthreads();
+  if (XC) cluster_barrier();   // every CTA's barriers exist before a peer arrives on them
+  const int n_jobs = marks[2];
   int budget = kWaitBudget;
   bool timed_out = false;
 
   if (warp == RING_NC) {
     // ================================================= producer (one lane)
     if (lane == 0) {
+      bool have_sel = false;
       for (int j = 0; j < n_jobs; ++j) {
         const int job = jobs[j], type = job & 3, idx = job >> 5;
         const int s = j % n_slots;
         if (j >= n_slots && !mbar_wait(empty(s), ((j / n_slots) - 1) & 1, &budget)) timed_out = true;
         // the first free block: the selection warp has written the list and the rows of all free blocks
-        if (type == JOB_SLC && idx == nf && !mbar_wait(sel_ready, 0, &budget)) timed_out = true;
+        if (type == JOB_SLC && idx >= nf && !have_sel) {
+          if (!mbar_wait(sel_ready, 0, &budget)) timed_out = true;
+          have_sel = true;
+        }
         const int row = type <= JOB_CMP_K ? rows[idx] : (type == JOB_WIN ? rows_win[idx] : rows_slc[idx]);
         const uint32_t dst = ring + (uint32_t)s * 2 * TILE_BYTES;
         const bool k_pair = type == JOB_CMP_K && idx + 1 < n_ct;
@@ -239,7 +325,16 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
         for (int w = 0; w < nw; ++w) L += state[(w0 + w) * STATE + 16 + r] * fast_exp2(state[(w0 + w) * STATE + r] - M);
       const float inv = L > 0.f ? 1.f / L : 0.f;
       for (int w = 0; w < nw; ++w) fac[(w0 + w) * 16 + r] = L > 0.f ? fast_exp2(state[(w0 + w) * STATE + r] - M) * inv : 0.f;
-      return L > 0.f ? M + log2f(L) : 0.f;
+      return L > 0.f ? M + log2f(L) : -INFINITY;
+    };
+    // cluster exchange k: what this CTA's consumers wrote before it (here or into the peers) is visible to every CTA of the
+    // cluster after it
+    auto xchg = [&](int k) {
+      fence_cluster();
+      named_barrier(1, NCT);
+      if (ctid == 0)
+        for (int c = 0; c < CS; ++c) mbar_arrive_peer(peer_addr(xbar + 8 * k, c));
+      if (!mbar_wait_cluster(xbar + 8 * k, 0, &budget)) timed_out = true;
     };
 
     constexpr int NST = RING_NS * 32;   // threads of consumers 0-3 (named barrier 2)
@@ -251,7 +346,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       ca.init();
       for (; j < end_a; ++j) {
         if (((jobs[j] >> 2) & 7) != cw) continue;
-        const int j0 = (jobs[j] >> 5) << 6;
+        const int j0 = ct_row0(jobs[j] >> 5);
         wait_job(j);
         const uint32_t bk = ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES;
         wts::attend64_smem<D>(ca, qf, bk, bk + TILE_BYTES, [&](int i) { return j0 + i < Y; }, min(64, Y - j0), c2, lane);
@@ -260,14 +355,31 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       wts::store_state<D>(ca, state + cw * STATE, lane);
     }
     named_barrier(1, NCT);
-    if (ctid < 16) lse_s[ctid] = merge_weights(0, RING_NC, ctid);
+    if (ctid < 16) {
+      const float l = merge_weights(0, RING_NC, ctid);
+      if (XC) lse_x[ctid] = l;
+      else lse_s[ctid] = l == -INFINITY ? 0.f : l;
+    }
     named_barrier(1, NCT);
     for (int idx = ctid; idx < 16 * D; idx += NCT) {
       const int r = idx / D;
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < RING_NC; ++w) o += state[w * STATE + 32 + idx] * fac[w * 16 + r];
-      cmp_o_s[idx] = o;
+      cmp_o_s[idx] = o;   // normalised by this CTA's own sum
+    }
+    if (XC) {
+      // exchange 1: the log-sum-exp over ALL compressed rows.  Every CTA is past reading its states when it arrives, so the
+      // peers may store probabilities into that region afterwards.
+      xchg(0);
+      if (ctid < 16) {
+        const uint32_t a = smem_u32(lse_x + ctid);
+        float M = -INFINITY, L = 0.f;
+        for (int c = 0; c < CS; ++c) M = fmaxf(M, ld_peer(peer_addr(a, c)));
+        if (M != -INFINITY)
+          for (int c = 0; c < CS; ++c) L += fast_exp2(ld_peer(peer_addr(a, c)) - M);
+        lse_s[ctid] = L > 0.f ? M + log2f(L) : 0.f;
+      }
     }
     named_barrier(1, NCT);   // the states are dead until phase 4 is over: the score arrays live there
 
@@ -296,7 +408,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       for (int half = 0; half < 2; ++half) {
         const int ti = (job >> 5) + half;   // the slot holds K tiles ti (first half) and ti + 1 (second half)
         if (ti >= n_ct) break;
-        const int j0 = ti << 6;
+        const int j0 = ct_row0(ti);
         float s[8][4];
         wts::scores64<D>(s, qf, ring + (uint32_t)(j % n_slots) * 2 * TILE_BYTES + half * TILE_BYTES, lane);
         if (half == 1 || ti + 1 >= n_ct) release(j);
@@ -314,13 +426,23 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
             v1 += __shfl_xor_sync(0xffffffffu, v1, o);
           }
           if (g_ == nt) {
-            pcm[1 + col] = v0;
-            pcm[2 + col] = v1;
+            if (XC) {   // into the score array of every CTA of the cluster
+              const uint32_t a = smem_u32(pcm + 1 + col);
+              for (int c = 0; c < CS; ++c) {
+                const uint32_t pa = peer_addr(a, c);
+                st_peer(pa, v0);
+                st_peer(pa + 4, v1);
+              }
+            } else {
+              pcm[1 + col] = v0;
+              pcm[2 + col] = v1;
+            }
           }
         }
       }
     }
-    named_barrier(1, NCT);   // pcm[] is complete
+    if (XC) xchg(1);               // exchange 2: every CTA's pcm[] is complete
+    else named_barrier(1, NCT);   // pcm[] is complete
 
     if (cw >= RING_NS) {
       // ================================ W. the rest of the sliding window
@@ -357,15 +479,17 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
         if (ctid < ni) sel[ctid] = (ctid <= nk) ? ctid : -1;
         else if (ctid < ni + nl) sel[ctid] = (ctid <= nk) ? nk - (ctid - ni) : -1;
         named_barrier(2, NST);
-      } else if (cw == 0) {
-        for (int blk = lane; blk < n_blk; blk += 32) psl[blk] = pooled(blk);
-        sel[lane] = -1;
-        __syncwarp();
-        // Rounds of warp-wide arg-max.  A lane owns `per` CONSECUTIVE blocks and keeps the best of them (ascending scan: the
-        // lowest index among equals); a round is one warp reduction (largest score) and a ballot: the lowest lane that holds
-        // that score holds the lowest such block.  Only the winner rescans its blocks.  Scores are >= 0, so their bit
+      } else {
+        // Rounds of arg-max over the 128 threads.  A thread owns `per` CONSECUTIVE blocks and keeps the best of them (ascending
+        // scan: the lowest index among equals); a round is one warp reduction (largest score) and a ballot -- the lowest lane
+        // that holds that score holds the warp's lowest such block -- then the four warps' candidates through shared memory and
+        // one barrier (two sets of places, used in turn).  Only the winner rescans its blocks.  Scores are >= 0, so their bit
         // patterns order like unsigned integers; 0 = no candidate.
-        const int per = (n_blk + 31) >> 5, b0 = lane * per;
+        for (int blk = ctid; blk < n_blk; blk += NST) psl[blk] = pooled(blk);
+        if (ctid < 32) sel[ctid] = -1;
+        named_barrier(2, NST);
+        unsigned* wbest = reinterpret_cast<unsigned*>(xw);   // [2][RING_NS][2]: key, block
+        const int per = (n_blk + NST - 1) / NST, b0 = ctid * per;
         unsigned key;
         int bi;
         auto local_best = [&]() {
@@ -382,37 +506,46 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
         };
         local_best();
         for (int r = 0; r < n_free; ++r) {
-          const unsigned best = __reduce_max_sync(0xffffffffu, key);
-          if (best == 0u) break;   // fewer candidates than slots
-          const int wl = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1;
-          if (lane == wl) {
+          const unsigned wkey = __reduce_max_sync(0xffffffffu, key);
+          const int wl = __ffs(__ballot_sync(0xffffffffu, key == wkey)) - 1;
+          const int wbi = __shfl_sync(0xffffffffu, bi, wl);
+          unsigned* slot = wbest + (r & 1) * 2 * RING_NS;
+          if (lane == 0) {
+            slot[2 * cw] = wkey;
+            slot[2 * cw + 1] = (unsigned)wbi;
+          }
+          named_barrier(2, NST);
+          unsigned best = 0u;
+          int best_blk = -1;
+#pragma unroll
+          for (int w = 0; w < RING_NS; ++w)   // ascending warps own ascending blocks: the first of equal scores is the lowest block
+            if (slot[2 * w] > best) {
+              best = slot[2 * w];
+              best_blk = (int)slot[2 * w + 1];
+            }
+          if (best == 0u) break;   // fewer candidates than slots (the same answer in every thread)
+          if (best_blk == bi && key == best) {
             sel[ni + nl + r] = bi;
             psl[bi] = -1.f;
             local_best();
           }
         }
-        __syncwarp();
-        if (lane < ni) sel[lane] = (lane <= nk) ? lane : -1;
-        else if (lane < ni + nl) sel[lane] = (lane <= nk) ? nk - (lane - ni) : -1;
-        __syncwarp();
+        if (ctid < ni) sel[ctid] = (ctid <= nk) ? ctid : -1;
+        else if (ctid < ni + nl) sel[ctid] = (ctid <= nk) ? nk - (ctid - ni) : -1;
+        named_barrier(2, NST);
       }
       if (cw == 0) {
-        if (p.topk_out && lane < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + lane] = sel[lane];
+        if (cr == 0 && p.topk_out && lane < top_n) p.topk_out[((int64_t)kh * p.B + b) * top_n + lane] = sel[lane];
         // the cache rows of the free blocks, for the producer (an unused slot fetches block 0 and takes no part)
         if (lane >= nf && lane < n_valid) rows_slc[lane] = (int)tokrow(max(0, min(sel[lane], nk)) << 6);
         __syncwarp();
         if (lane == 0) mbar_arrive(sel_ready);
       }
       // ---- 4. the selected blocks
-      bool have_sel = cw == 0 || by_rank;
       for (; j < n_jobs; ++j) {
         const int job = jobs[j];
         if (((job >> 2) & 7) != cw) continue;
         const int idx = job >> 5;
-        if (idx >= nf && !have_sel) {
-          if (!mbar_wait(sel_ready, 0, &budget)) timed_out = true;
-          have_sel = true;
-        }
         const int blk = idx >= nf ? sel[idx] : (idx < ni ? idx : nk - (idx - ni));
         int k0 = max(0, min(blk, nk)) << 6;
         if (blk < 0 || blk > nk) k0 = -1;   // an unused slot: its tile was fetched (block 0) but takes no part
@@ -428,34 +561,80 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     named_barrier(1, NCT);
     // ---- 5. merge + gated combine
     const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t)b * p.w_stride_t + (int64_t)kh * G * 3;
-    if (ctid < 16) merge_weights(0, RING_NS, ctid);
-    else if (ctid < 32) merge_weights(RING_NS, RING_NC - RING_NS, ctid - 16);
-    else if (ctid < 32 + 3 * 16) {
+    if (ctid < 16) {
+      const float l = merge_weights(0, RING_NS, ctid);
+      if (XC) lse_x[16 + ctid] = l;
+    } else if (ctid < 32) {
+      const float l = merge_weights(RING_NS, RING_NC - RING_NS, ctid - 16);
+      if (XC) lse_x[32 + ctid - 16] = l;
+    } else if (ctid < 32 + 3 * 16) {
       const int i = ctid - 32, r = i / 3;   // gates: sigmoid of the three logits of head r
       fac[RING_NC * 16 + i] = r < G ? 1.f / (1.f + __expf(-__bfloat162float(wp[i]))) : 0.f;
     }
     named_barrier(1, NCT);
     const float* gate = fac + RING_NC * 16;
-    for (int idx = ctid; idx < G * D; idx += NCT) {
-      const int r = idx / D;
-      float slc = 0.f, swa = 0.f;
+    if (!XC) {
+      for (int idx = ctid; idx < G * D; idx += NCT) {
+        const int r = idx / D;
+        float slc = 0.f, swa = 0.f;
 #pragma unroll
-      for (int w = 0; w < RING_NS; ++w) slc += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+        for (int w = 0; w < RING_NS; ++w) slc += state[w * STATE + 32 + idx] * fac[w * 16 + r];
 #pragma unroll
-      for (int w = RING_NS; w < RING_NC; ++w) swa += state[w * STATE + 32 + idx] * fac[w * 16 + r];
-      out[idx] = __float2bfloat16(gate[r * 3] * cmp_o_s[idx] + gate[r * 3 + 1] * slc + gate[r * 3 + 2] * swa);
+        for (int w = RING_NS; w < RING_NC; ++w) swa += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+        out[idx] = __float2bfloat16(gate[r * 3] * cmp_o_s[idx] + gate[r * 3 + 1] * slc + gate[r * 3 + 2] * swa);
+      }
+    } else {
+      // this CTA's normalised partial outputs, in place: the selected branch over the state of consumer 0, the window over the
+      // state of the first window consumer (a thread reads and writes only its own element of every state)
+      for (int idx = ctid; idx < G * D; idx += NCT) {
+        const int r = idx / D;
+        float slc = 0.f, swa = 0.f;
+#pragma unroll
+        for (int w = 0; w < RING_NS; ++w) slc += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+#pragma unroll
+        for (int w = RING_NS; w < RING_NC; ++w) swa += state[w * STATE + 32 + idx] * fac[w * 16 + r];
+        state[32 + idx] = slc;
+        state[RING_NS * STATE + 32 + idx] = swa;
+      }
+      xchg(2);   // exchange 3: every CTA's partials and their log-sum-exps are in place
+      {          // CTA c merges and writes the c-th slice of the output row
+        if (ctid < 48) {   // weight of CTA c's partial of branch ctid / 16, head ctid % 16: exp2(lse_c) / sum over the CTAs
+          const uint32_t a = smem_u32(lse_x + ctid);
+          float M = -INFINITY, L = 0.f;
+          for (int c = 0; c < CS; ++c) M = fmaxf(M, ld_peer(peer_addr(a, c)));
+          if (M != -INFINITY)
+            for (int c = 0; c < CS; ++c) L += fast_exp2(ld_peer(peer_addr(a, c)) - M);
+          const float inv = L > 0.f ? 1.f / L : 0.f;
+          for (int c = 0; c < CS; ++c) xw[c * 48 + ctid] = L > 0.f ? fast_exp2(ld_peer(peer_addr(a, c)) - M) * inv : 0.f;
+        }
+        named_barrier(1, NCT);
+        const uint32_t a_cmp = smem_u32(cmp_o_s), a_slc = smem_u32(state + 32), a_swa = smem_u32(state + RING_NS * STATE + 32);
+        const int chunk = (G * D + CS - 1) / CS;
+        for (int idx = cr * chunk + ctid; idx < min(G * D, (cr + 1) * chunk); idx += NCT) {
+          const int r = idx / D;
+          float cmp = 0.f, slc = 0.f, swa = 0.f;
+          for (int c = 0; c < CS; ++c) {
+            cmp += xw[c * 48 + r] * ld_peer(peer_addr(a_cmp + 4 * idx, c));
+            slc += xw[c * 48 + 16 + r] * ld_peer(peer_addr(a_slc + 4 * idx, c));
+            swa += xw[c * 48 + 32 + r] * ld_peer(peer_addr(a_swa + 4 * idx, c));
+          }
+          out[idx] = __float2bfloat16(gate[r * 3] * cmp + gate[r * 3 + 1] * slc + gate[r * 3 + 2] * swa);
+        }
+      }
     }
   }
   if (timed_out && p.status) atomicOr(p.status, 2048);
+  if (XC) cluster_barrier();   // a CTA's shared memory outlives every remote access to it
 }
 
-template <int D, int NC, int NS>
-static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_t smem_cap) {
+template <int D, int NC, int NS, bool XC>
+static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_t smem_cap, int cs) {
   const size_t tile = (size_t)64 * D * 2;
   const int job_cap = 2 * ((p.y_cap + 63) / 64) + 2 * p.hp.top_n + p.hp.window / 64 + 8;
   const int rows_cap = (p.y_cap + 63) / 64 + RING_WIN_ROWS + 32;
   const size_t region = (size_t)max(NC * (32 + 16 * D), p.y_cap + 8 + p.y_cap / 4 + 8) * 4;
-  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap + rows_cap + (NC + 3) * 16 + 2) * 4 + 8 + 16 * 8 + 16 + 1024;
+  const size_t fixed = region + ((size_t)16 * D + 16 + 32 + job_cap + rows_cap + (NC + 3) * 16 + 48 + RING_MAX_CLUSTER * 48 + 3) * 4 + 8 +
+                       16 * 8 + 16 + 1024;
   if (fixed + 2 * 2 * tile > smem_cap) return 1;
   int n_slots = (int)((smem_cap - fixed) / (2 * tile));
   if (n_slots > max_slots) n_slots = max_slots;
@@ -465,14 +644,70 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
   if (!tma::make_map(&tmk, p.k_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1) ||
       !tma::make_map(&tmv, p.v_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1))
     return 1;
-  cudaError_t e = cudaFuncSetAttribute(decode_ring_kernel<D, NC, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kernel = decode_ring_kernel<D, NC, NS, XC>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("decode_fused: cudaFuncSetAttribute(%zu B) failed: %s", smem, cudaGetErrorString(e));
     return NSA_ERR_CUDA;
   }
-  dim3 grid(p.KH, p.B);
-  decode_ring_kernel<D, NC, NS><<<grid, 32 * (NC + 1), smem, st>>>(p, n_slots, job_cap, tmk, tmv);
+  if (!XC) {
+    dim3 grid(p.KH, p.B);
+    kernel<<<grid, 32 * (NC + 1), smem, st>>>(p, n_slots, job_cap, tmk, tmv);
+    return check_launch("decode_fused");
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.KH * cs, p.B);
+  cfg.blockDim = dim3(32 * (NC + 1));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = cs;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  // clusters of this size and shared-memory footprint the GPU holds at once: all of the step's clusters must fit, a second
+  // wave would cost more than the split saves
+  int fit = 0;
+  if (cudaOccupancyMaxActiveClusters(&fit, kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    fit = 0;
+  }
+  static const bool debug = getenv("NSA_DECODE_CLUSTER_DEBUG") != nullptr;
+  if (debug) fprintf(stderr, "[nsa] decode: %d x %d CTAs as clusters of %d: %d clusters fit\n", p.B, p.KH, cs, fit);
+  if (fit < 1 || (int64_t)p.B * p.KH > fit) return 2;
+  e = cudaLaunchKernelEx(&cfg, kernel, p, n_slots, job_cap, tmk, tmv);
+  if (e != cudaSuccess) {
+    set_error("decode_fused: cluster launch failed: %s", cudaGetErrorString(e));
+    return NSA_ERR_CUDA;
+  }
   return check_launch("decode_fused");
+}
+
+// CTAs per (sequence, kv head).  1 when the batch fills the GPU by itself or the contexts are short: the exchanges cost a few
+// microseconds, which a split only wins back from about 16K tokens on (measured: 4K -5..-15 %, 32K +25..35 %, 128K x2.3 at
+// batch 1).  The host does not know the context lengths (they are device data); the width of the page table bounds them.
+// Else the largest power of two (<= 8) that keeps the grid within the SMs and leaves a CTA at least eight compressed tiles
+// at that bound.  NSA_DECODE_CLUSTER=1|2|4|8 overrides it.
+int decode_cluster_size_for(const NsaDecodeParams* p) {
+  static const int forced = [] {
+    const char* e = getenv("NSA_DECODE_CLUSTER");
+    const int v = e ? atoi(e) : 0;
+    return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
+  }();
+  if (forced) return forced;
+  static const int sms = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    return n;
+  }();
+  const int64_t ctas = (int64_t)p->B * p->KH;
+  const int64_t cap_tokens = (int64_t)p->kv_table_stride * p->page_size;
+  if (cap_tokens < 16384) return 1;
+  int cs = 1;
+  while (cs < RING_MAX_CLUSTER && ctas * cs * 2 <= sms && cap_tokens >= (int64_t)8192 * cs) cs *= 2;
+  return cs;
 }
 
 // returns 1 when the configuration is not covered (decode_fused_kernel then runs), 0 on launch, < 0 on error
@@ -480,7 +715,12 @@ int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) {
   const int D = p->D;
   if (p->cache_rows <= 0 || (p->cache_stride_t * 2) % 16 || (((uintptr_t)p->k_cache | (uintptr_t)p->v_cache) & 15)) return 1;
   if (p->hp.window / 64 + 2 > RING_WIN_ROWS || p->hp.top_n > 32) return 1;
-  return D == 128 ? launch_shape<128, 6, 4>(*p, st, 5, 227 * 1024) : launch_shape<64, 6, 4>(*p, st, 5, 227 * 1024);
+  const size_t cap = 227 * 1024;
+  for (int cs = decode_cluster_size_for(p); cs > 1; cs >>= 1) {   // 2 = no room for clusters of this size: try the next smaller one
+    const int rc = D == 128 ? launch_shape<128, 6, 4, true>(*p, st, 5, cap, cs) : launch_shape<64, 6, 4, true>(*p, st, 5, cap, cs);
+    if (rc != 2) return rc;
+  }
+  return D == 128 ? launch_shape<128, 6, 4, false>(*p, st, 5, cap, 1) : launch_shape<64, 6, 4, false>(*p, st, 5, cap, 1);
 }
 
 }  // namespace nsa

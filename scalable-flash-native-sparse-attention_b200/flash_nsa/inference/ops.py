@@ -321,6 +321,18 @@ def decode_fused_supported(q, k, kernel_size, stride, block_size, top_n, num_ini
             and top_n <= 32 and num_init_blocks + num_local_blocks <= top_n and page >= 64 and page & (page - 1) == 0)
 
 
+def decode_cluster_size(B, KH, page_size, table_width):
+    """CTAs the one-launch decode step gives each (sequence, kv head) for a batch of B sequences whose page table has
+    `table_width` columns: 1, or 2 / 4 / 8 (a thread-block cluster) for few sequences with room for long contexts."""
+    from .._lib import lib
+    import ctypes
+    p = S["NsaDecodeParams"]()
+    p.B, p.KH, p.page_size, p.kv_table_stride = B, KH, page_size, table_width
+    n = lib().nsa_decode_cluster_size(ctypes.byref(p))
+    assert n > 0, lib().nsa_last_error().decode()
+    return n
+
+
 def nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, cmp_block_tables, fixed_y_maxlen=8192,
                      kernel_size=32, stride=16, block_size=64, top_n=16, num_init_blocks=1, num_local_blocks=2, window_size=512,
                      sm_scale=None, return_topk=False):

@@ -244,6 +244,46 @@ def test_decode_long_contexts_use_the_round_based_selection():
             assert len(set(row)) == 16 and min(row) >= 0 and max(row) <= nkb
 
 
+@pytest.mark.parametrize("B,KH,want", [(1, 2, 8), (5, 4, 4), (16, 4, 2)])
+def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
+    """With few sequences and a page table wide enough for long contexts the one-launch decode step runs as clusters of
+    `want` CTAs per (sequence, kv head), each taking every want-th tile.  Same selection and output as the op-by-op path,
+    for contexts that leave some CTAs of a cluster without a compressed tile, with a tile each, and with many."""
+    from flash_nsa.inference import nsa_decode_unfused, nsa_decode_fused, mean_pooling_prefill
+    QH, D = KH * 4, 128
+    g = torch.Generator().manual_seed(500 + B)
+    lens = ([9000, 40, 700, 2500, 4100, 64, 1, 5000] * 2)[:B]
+    cache = Cache(lens, KH, D, seed=B)
+    flat_k = cache.k.view(-1, KH, D)
+    flat_v = cache.v.view(-1, KH, D)
+    for b, L in enumerate(lens):
+        pos = torch.arange(L)
+        rows = cache.block_tables[b].long()[pos // PAGE] * PAGE + pos % PAGE
+        flat_k[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
+        flat_v[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
+    cache.cuda()
+    y_len = [max((L - 32) // 16 + 1, 0) for L in lens]
+    y_cu = torch.tensor([0] + torch.tensor(y_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    for c in (cache.k, cache.v):
+        mean_pooling_prefill(c, y_cu, max(y_len), slot_mapping=slots, block_table=cache.block_tables)
+    # a table as wide as a 64K-token context needs (what an engine with that model length replays its graphs on)
+    wide = torch.zeros(B, 65536 // PAGE, dtype=torch.int32, device="cuda")
+    wide[:, :cache.block_tables.size(1)] = cache.block_tables
+    q = torch.randn(B, QH, D, generator=g).bfloat16().cuda()
+    w = torch.randn(B, QH, 3, generator=g).bfloat16().cuda()
+    args = (q, cache.k, cache.v, w, torch.tensor(lens, dtype=torch.int32, device="cuda"), wide,
+            torch.full((B,), -1, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
+    from flash_nsa.inference.ops import decode_cluster_size
+    assert decode_cluster_size(B, KH, PAGE, wide.stride(0)) == want and decode_cluster_size(B, KH, PAGE, cache.block_tables.stride(0)) == 1
+    o_ref, tk_ref = nsa_decode_fused(*args[:5], cache.block_tables, *args[6:], return_topk=True)   # narrow table: one CTA each
+    o, tk = nsa_decode_fused(*args, return_topk=True)
+    o_un = nsa_decode_unfused(*args)
+    assert torch.equal(tk.sort(-1).values, tk_ref.sort(-1).values)
+    assert (o.float() - o_ref.float()).abs().max().item() <= 4e-3      # bf16 rounding of a different merge order
+    assert (o.float() - o_un.float()).abs().max().item() <= TOL
+
+
 def test_rows_past_a_sequence_end_may_hold_anything():
     """Never-written cache memory (here: NaN everywhere a row was not stored) must not reach a result: the tile kernels read
     whole tiles of a page, and a zero probability times NaN is NaN."""
