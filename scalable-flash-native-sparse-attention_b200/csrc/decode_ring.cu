@@ -669,10 +669,19 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
   cfg.numAttrs = 1;
   // clusters of this size and shared-memory footprint the GPU holds at once: all of the step's clusters must fit, a second
   // wave would cost more than the split saves
-  int fit = 0;
-  if (cudaOccupancyMaxActiveClusters(&fit, kernel, &cfg) != cudaSuccess) {
-    (void)cudaGetLastError();
-    fit = 0;
+  static struct { size_t smem; int dev, fit; } cache[4] = {{0, -1, 0}, {0, -1, 0}, {0, -1, 0}, {0, -1, 0}};   // per cluster size (this D)
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  auto& slot = cache[cs == 2 ? 1 : cs == 4 ? 2 : cs == 8 ? 3 : 0];
+  int fit = slot.fit;
+  if (slot.smem != smem || slot.dev != dev) {   // the query costs more host time than the launch itself: ask once
+    if (cudaOccupancyMaxActiveClusters(&fit, kernel, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      fit = 0;
+    }
+    slot.smem = smem;
+    slot.dev = dev;
+    slot.fit = fit;
   }
   static const bool debug = getenv("NSA_DECODE_CLUSTER_DEBUG") != nullptr;
   if (debug) fprintf(stderr, "[nsa] decode: %d x %d CTAs as clusters of %d: %d clusters fit\n", p.B, p.KH, cs, fit);
