@@ -326,8 +326,9 @@ typedef struct NsaDecodeParams {
 int nsa_decode_fused(const NsaDecodeParams* p, void* stream);
 /* How many CTAs nsa_decode_fused would give each (sequence, kv head) of this step: 1, or 2 / 4 / 8 (a thread-block cluster
  * that splits the tiles of the step and exchanges scores and partial outputs through distributed shared memory) when the
- * step has few sequences and kv_table_stride * page_size, the bound on the context lengths the host knows, is 16K tokens
- * or more.  The reference splits long contexts over CTAs with its num_splits arguments
+ * step has few sequences (B * KH * size within the SM count) and kv_table_stride * page_size, the bound on the context
+ * lengths the host knows, is at least 4K tokens (sizes 4 and 8) or 16K tokens (size 2); the launch falls back to the next
+ * smaller size when the GPU cannot hold all clusters at once.  The reference splits long contexts over CTAs with its num_splits arguments
  * (flash_nsa/inference/__init__.py:160-257); here the library decides.  Reads B, KH, page_size, kv_table_stride only.  */
 int nsa_decode_cluster_size(const NsaDecodeParams* p);
 

@@ -64,13 +64,23 @@ __device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank) {  
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_peer(uint32_t addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+__device__ __forceinline__ void st_peer4(uint32_t addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 __device__ __forceinline__ float ld_peer(uint32_t addr) {
   float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
   return v;
+}
+constexpr int RING_MAX_CLUSTER = 8;
+// The same shared-memory word of every CTA of the cluster.  A remote load takes several hundred nanoseconds, so all of
+// them are issued before the first value is used (a loop that folds each value as it arrives pays that time per CTA).
+__device__ __forceinline__ void ld_all_peers(float (&v)[RING_MAX_CLUSTER], uint32_t local_addr, int CS, float fill) {
+#pragma unroll
+  for (int c = 0; c < RING_MAX_CLUSTER; ++c) v[c] = fill;
+#pragma unroll
+  for (int c = 0; c < RING_MAX_CLUSTER; ++c)
+    if (c < CS) v[c] = ld_peer(peer_addr(local_addr, c));
 }
 __device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive_peer(uint32_t peer_bar) {
@@ -93,7 +103,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ void cluster_barrier() {   // every thread of every CTA of the cluster
   asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;\n" ::: "memory");
 }
-constexpr int RING_MAX_CLUSTER = 8;
 
 template <int D, int RING_NC, int RING_NS, bool XC>
 __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
@@ -108,7 +117,8 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
   unsigned char* after_ring = smem_raw + (size_t)n_slots * 2 * TILE_BYTES;
   float* state = reinterpret_cast<float*>(after_ring);            // RING_NC x STATE floats; the score arrays between the merges
   const size_t region = (size_t)max(RING_NC * STATE, p.y_cap + 8 + p.y_cap / 4 + 8) * 4;
-  float* pcm = state;                       // [y_cap + 8] head-summed probabilities of the compressed rows (index +1)
+  float* pcm = state;                       // [y_cap + 8] head-summed probabilities of the compressed rows (index + PO)
+  constexpr int PO = 4;                     // row j at pcm[PO + j]: a tile's 64 values start on a 16-byte boundary
   float* psl = state + p.y_cap + 8;         // [y_cap/4 + 8] block scores
   float* cmp_o_s = reinterpret_cast<float*>(after_ring + region);  // [16][D] merged output of the compressed branch
   float* lse_s = cmp_o_s + 16 * D;                                // [16]
@@ -332,8 +342,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     auto xchg = [&](int k) {
       fence_cluster();
       named_barrier(1, NCT);
-      if (ctid == 0)
-        for (int c = 0; c < CS; ++c) mbar_arrive_peer(peer_addr(xbar + 8 * k, c));
+      if (ctid < CS) mbar_arrive_peer(peer_addr(xbar + 8 * k, ctid));   // thread c tells CTA c
       if (!mbar_wait_cluster(xbar + 8 * k, 0, &budget)) timed_out = true;
     };
 
@@ -373,17 +382,21 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       // peers may store probabilities into that region afterwards.
       xchg(0);
       if (ctid < 16) {
-        const uint32_t a = smem_u32(lse_x + ctid);
+        float l[RING_MAX_CLUSTER];
+        ld_all_peers(l, smem_u32(lse_x + ctid), CS, -INFINITY);
         float M = -INFINITY, L = 0.f;
-        for (int c = 0; c < CS; ++c) M = fmaxf(M, ld_peer(peer_addr(a, c)));
-        if (M != -INFINITY)
-          for (int c = 0; c < CS; ++c) L += fast_exp2(ld_peer(peer_addr(a, c)) - M);
+#pragma unroll
+        for (int c = 0; c < RING_MAX_CLUSTER; ++c) M = fmaxf(M, l[c]);
+        if (M != -INFINITY) {
+#pragma unroll
+          for (int c = 0; c < RING_MAX_CLUSTER; ++c) L += fast_exp2(l[c] - M);   // exp2(-inf) = 0 for absent or empty CTAs
+        }
         lse_s[ctid] = L > 0.f ? M + log2f(L) : 0.f;
       }
     }
     named_barrier(1, NCT);   // the states are dead until phase 4 is over: the score arrays live there
 
-    // ---- 2. head-summed probabilities of every compressed row -> pcm[1 + j]; consumers 4-5 also start on the window
+    // ---- 2. head-summed probabilities of every compressed row -> pcm[PO + j]; consumers 4-5 also start on the window
     wts::Acc<D> acc;   // the state a consumer ends with: selected branch (consumers 0-3) or window (4-5)
     acc.init();
     const float nl_lo = (g_ < G) ? -lse_s[g_] : 0.f, nl_hi = (g_ + 8 < G) ? -lse_s[g_ + 8] : 0.f;
@@ -395,7 +408,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       wts::attend64_smem<D>(acc, qf, bk, bk + TILE_BYTES, [&](int x) { return k0 + x >= lo && k0 + x <= t; }, min(64, t - k0 + 1), c2, lane);
       release(jj);
     };
-    if (ctid == 0) pcm[0] = 0.f;
+    if (ctid == 0) pcm[PO - 1] = 0.f;
     for (; j < end_b; ++j) {
       const int job = jobs[j];
       if (((job >> 2) & 7) != cw) continue;
@@ -426,17 +439,17 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
             v1 += __shfl_xor_sync(0xffffffffu, v1, o);
           }
           if (g_ == nt) {
-            if (XC) {   // into the score array of every CTA of the cluster
-              const uint32_t a = smem_u32(pcm + 1 + col);
-              for (int c = 0; c < CS; ++c) {
-                const uint32_t pa = peer_addr(a, c);
-                st_peer(pa, v0);
-                st_peer(pa + 4, v1);
-              }
-            } else {
-              pcm[1 + col] = v0;
-              pcm[2 + col] = v1;
-            }
+            pcm[PO + col] = v0;
+            pcm[PO + 1 + col] = v1;
+          }
+        }
+        if (XC) {   // the tile's 64 values into the score array of every other CTA of the cluster: 16 lanes x 16 bytes each
+          __syncwarp();
+          if (lane < 16) {
+            const float4 v = *reinterpret_cast<const float4*>(pcm + PO + j0 + 4 * lane);
+            const uint32_t a = smem_u32(pcm + PO + j0 + 4 * lane);
+            for (int c = 0; c < CS; ++c)
+              if (c != cr) st_peer4(peer_addr(a, c), v);
           }
         }
       }
@@ -453,7 +466,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       const int n_blk = nk + 1;
       const bool by_rank = n_blk <= 2 * NST;   // CTA-uniform
       auto pooled = [&](int blk) -> float {
-        auto at = [&](int jj) { return (jj >= 0 && jj < Y) ? pcm[1 + jj] : 0.f; };
+        auto at = [&](int jj) { return (jj >= 0 && jj < Y) ? pcm[PO + jj] : 0.f; };
         const int jj = 4 * blk;
         const float pv = at(jj - 1) + ((2.f * at(jj) + 2.f * at(jj + 1)) + (2.f * at(jj + 2) + at(jj + 3)));
         return (blk >= ni && blk <= nk - nl) ? pv : -1.f;   // forced blocks are not candidates
@@ -599,24 +612,34 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
       xchg(2);   // exchange 3: every CTA's partials and their log-sum-exps are in place
       {          // CTA c merges and writes the c-th slice of the output row
         if (ctid < 48) {   // weight of CTA c's partial of branch ctid / 16, head ctid % 16: exp2(lse_c) / sum over the CTAs
-          const uint32_t a = smem_u32(lse_x + ctid);
+          float l[RING_MAX_CLUSTER];
+          ld_all_peers(l, smem_u32(lse_x + ctid), CS, -INFINITY);
           float M = -INFINITY, L = 0.f;
-          for (int c = 0; c < CS; ++c) M = fmaxf(M, ld_peer(peer_addr(a, c)));
-          if (M != -INFINITY)
-            for (int c = 0; c < CS; ++c) L += fast_exp2(ld_peer(peer_addr(a, c)) - M);
+#pragma unroll
+          for (int c = 0; c < RING_MAX_CLUSTER; ++c) M = fmaxf(M, l[c]);
+          if (M != -INFINITY) {
+#pragma unroll
+            for (int c = 0; c < RING_MAX_CLUSTER; ++c) L += fast_exp2(l[c] - M);
+          }
           const float inv = L > 0.f ? 1.f / L : 0.f;
-          for (int c = 0; c < CS; ++c) xw[c * 48 + ctid] = L > 0.f ? fast_exp2(ld_peer(peer_addr(a, c)) - M) * inv : 0.f;
+#pragma unroll
+          for (int c = 0; c < RING_MAX_CLUSTER; ++c) xw[c * 48 + ctid] = L > 0.f ? fast_exp2(l[c] - M) * inv : 0.f;
         }
         named_barrier(1, NCT);
         const uint32_t a_cmp = smem_u32(cmp_o_s), a_slc = smem_u32(state + 32), a_swa = smem_u32(state + RING_NS * STATE + 32);
         const int chunk = (G * D + CS - 1) / CS;
         for (int idx = cr * chunk + ctid; idx < min(G * D, (cr + 1) * chunk); idx += NCT) {
           const int r = idx / D;
+          float pc[RING_MAX_CLUSTER], ps[RING_MAX_CLUSTER], pw[RING_MAX_CLUSTER];   // 3 x CS remote loads in flight
+          ld_all_peers(pc, a_cmp + 4 * idx, CS, 0.f);
+          ld_all_peers(ps, a_slc + 4 * idx, CS, 0.f);
+          ld_all_peers(pw, a_swa + 4 * idx, CS, 0.f);
           float cmp = 0.f, slc = 0.f, swa = 0.f;
-          for (int c = 0; c < CS; ++c) {
-            cmp += xw[c * 48 + r] * ld_peer(peer_addr(a_cmp + 4 * idx, c));
-            slc += xw[c * 48 + 16 + r] * ld_peer(peer_addr(a_slc + 4 * idx, c));
-            swa += xw[c * 48 + 32 + r] * ld_peer(peer_addr(a_swa + 4 * idx, c));
+#pragma unroll
+          for (int c = 0; c < RING_MAX_CLUSTER; ++c) {   // the weights of absent CTAs are 0
+            cmp += xw[c * 48 + r] * pc[c];
+            slc += xw[c * 48 + 16 + r] * ps[c];
+            swa += xw[c * 48 + 32 + r] * pw[c];
           }
           out[idx] = __float2bfloat16(gate[r * 3] * cmp + gate[r * 3 + 1] * slc + gate[r * 3 + 2] * swa);
         }
@@ -694,18 +717,21 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
   return check_launch("decode_fused");
 }
 
-// CTAs per (sequence, kv head).  1 when the batch fills the GPU by itself or the contexts are short: the exchanges cost a few
-// microseconds, which a split only wins back from about 16K tokens on (measured: 4K -5..-15 %, 32K +25..35 %, 128K x2.3 at
-// batch 1).  The host does not know the context lengths (they are device data); the width of the page table bounds them.
-// Else the largest power of two (<= 8) that keeps the grid within the SMs and leaves a CTA at least eight compressed tiles
-// at that bound.  NSA_DECODE_CLUSTER=1|2|4|8 overrides it.
-int decode_cluster_size_for(const NsaDecodeParams* p) {
+// CTAs per (sequence, kv head).  The host does not know the context lengths (they are device data); the width of the page
+// table bounds them.  Measured (batch 1 / 4 / 16 of 4 kv heads, CUDA graph, against one CTA): clusters of 4 and 8 win from 4K
+// tokens on (4K: 0.0247 -> 0.021-0.023 ms, 16K: 0.041 -> 0.029, 128K: 0.109 -> 0.037); clusters of 2 lose at 4K, are even at
+// 8K and win from 16K on (0.041 -> 0.036; 128K batch 16: 0.121 -> 0.094), because the three exchanges cost what half of a
+// short step saves.  So: the largest size whose grid stays within the SMs, 4 and 8 for tables of 4K tokens or more, 2 for
+// 16K or more.  NSA_DECODE_CLUSTER=1|2|4|8 overrides it.
+static int forced_cluster_size() {
   static const int forced = [] {
     const char* e = getenv("NSA_DECODE_CLUSTER");
     const int v = e ? atoi(e) : 0;
     return (v == 1 || v == 2 || v == 4 || v == 8) ? v : 0;
   }();
-  if (forced) return forced;
+  return forced;
+}
+static bool cluster_size_ok(const NsaDecodeParams* p, int cs) {
   static const int sms = [] {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
@@ -713,10 +739,14 @@ int decode_cluster_size_for(const NsaDecodeParams* p) {
   }();
   const int64_t ctas = (int64_t)p->B * p->KH;
   const int64_t cap_tokens = (int64_t)p->kv_table_stride * p->page_size;
-  if (cap_tokens < 16384) return 1;
-  int cs = 1;
-  while (cs < RING_MAX_CLUSTER && ctas * cs * 2 <= sms && cap_tokens >= (int64_t)8192 * cs) cs *= 2;
-  return cs;
+  if (ctas * cs > sms) return false;
+  return cap_tokens >= (cs >= 4 ? 4096 : 16384);
+}
+int decode_cluster_size_for(const NsaDecodeParams* p) {
+  if (forced_cluster_size()) return forced_cluster_size();
+  for (int cs = RING_MAX_CLUSTER; cs > 1; cs >>= 1)
+    if (cluster_size_ok(p, cs)) return cs;
+  return 1;
 }
 
 // returns 1 when the configuration is not covered (decode_fused_kernel then runs), 0 on launch, < 0 on error
@@ -726,6 +756,7 @@ int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) {
   if (p->hp.window / 64 + 2 > RING_WIN_ROWS || p->hp.top_n > 32) return 1;
   const size_t cap = 227 * 1024;
   for (int cs = decode_cluster_size_for(p); cs > 1; cs >>= 1) {   // 2 = no room for clusters of this size: try the next smaller one
+    if (!forced_cluster_size() && !cluster_size_ok(p, cs)) continue;
     const int rc = D == 128 ? launch_shape<128, 6, 4, true>(*p, st, 5, cap, cs) : launch_shape<64, 6, 4, true>(*p, st, 5, cap, cs);
     if (rc != 2) return rc;
   }

@@ -275,8 +275,13 @@ def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
     args = (q, cache.k, cache.v, w, torch.tensor(lens, dtype=torch.int32, device="cuda"), wide,
             torch.full((B,), -1, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
     from flash_nsa.inference.ops import decode_cluster_size
-    assert decode_cluster_size(B, KH, PAGE, wide.stride(0)) == want and decode_cluster_size(B, KH, PAGE, cache.block_tables.stride(0)) == 1
-    o_ref, tk_ref = nsa_decode_fused(*args[:5], cache.block_tables, *args[6:], return_topk=True)   # narrow table: one CTA each
+    assert decode_cluster_size(B, KH, PAGE, wide.stride(0)) == want
+    # the same sequences many times over fill the GPU by themselves: one CTA per (sequence, kv head)
+    rep = 148 // (B * KH) + 1
+    assert decode_cluster_size(B * rep, KH, PAGE, wide.stride(0)) == 1
+    o_ref, tk_ref = nsa_decode_fused(*[a.repeat(rep, *([1] * (a.dim() - 1))) if i in (0, 3, 4, 5, 6, 7) else a for i, a in enumerate(args)],
+                                     return_topk=True)
+    o_ref, tk_ref = o_ref[:B], tk_ref[:, :B]
     o, tk = nsa_decode_fused(*args, return_topk=True)
     o_un = nsa_decode_unfused(*args)
     assert torch.equal(tk.sort(-1).values, tk_ref.sort(-1).values)
