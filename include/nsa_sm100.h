@@ -329,7 +329,8 @@ int nsa_decode_fused(const NsaDecodeParams* p, void* stream);
  * step has few sequences (B * KH * size within the SM count) and kv_table_stride * page_size, the bound on the context
  * lengths the host knows, is at least 4K tokens (sizes 4 and 8) or 16K tokens (size 2); the launch falls back to the next
  * smaller size when the GPU cannot hold all clusters at once.  The reference splits long contexts over CTAs with its num_splits arguments
- * (flash_nsa/inference/__init__.py:160-257); here the library decides.  Reads B, KH, page_size, kv_table_stride only.  */
+ * (flash_nsa/inference/__init__.py:160-257); here the library decides.  Reads the sizes (B, KH, D, page_size,
+ * kv_table_stride, y_cap, hp), no pointer; asks the device how many clusters it holds, so it needs a current device.  */
 int nsa_decode_cluster_size(const NsaDecodeParams* p);
 
 /* ---- context-parallel chunk reorder ------------------------------------------------------------------ */

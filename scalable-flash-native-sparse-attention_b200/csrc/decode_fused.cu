@@ -255,13 +255,14 @@ using namespace nsa;
 
 namespace nsa {
 int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st);   // decode_ring.cu
-int decode_cluster_size_for(const NsaDecodeParams* p);                // decode_ring.cu
+int decode_cluster_size_query(const NsaDecodeParams* p);               // decode_ring.cu
 }
 
 extern "C" int nsa_decode_cluster_size(const NsaDecodeParams* p) {
-  NSA_REQUIRE(p && p->B >= 0 && p->KH > 0 && p->page_size > 0, NSA_ERR_BAD_ARG, "decode_cluster_size: bad sizes");
+  NSA_REQUIRE(p && p->B >= 0 && p->KH > 0 && p->page_size > 0 && p->y_cap > 0, NSA_ERR_BAD_ARG, "decode_cluster_size: bad sizes");
+  NSA_REQUIRE(p->D == 64 || p->D == 128, NSA_ERR_UNSUPPORTED_SHAPE, "decode_cluster_size: head dim %d not supported (64 or 128)", p->D);
   static const bool per_warp = [] { const char* e = getenv("NSA_DECODE_PER_WARP_LOADS"); return e && e[0] == '1'; }();
-  return per_warp ? 1 : decode_cluster_size_for(p);
+  return per_warp ? 1 : decode_cluster_size_query(p);
 }
 
 extern "C" int nsa_decode_fused(const NsaDecodeParams* p, void* stream) {

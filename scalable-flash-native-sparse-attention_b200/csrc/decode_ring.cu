@@ -651,7 +651,7 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
 }
 
 template <int D, int NC, int NS, bool XC>
-static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_t smem_cap, int cs) {
+static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_t smem_cap, int cs, bool dry) {
   const size_t tile = (size_t)64 * D * 2;
   const int job_cap = 2 * ((p.y_cap + 63) / 64) + 2 * p.hp.top_n + p.hp.window / 64 + 8;
   const int rows_cap = (p.y_cap + 63) / 64 + RING_WIN_ROWS + 32;
@@ -664,8 +664,8 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
   if (n_slots < 2) return 1;
   const size_t smem = (size_t)n_slots * 2 * tile + fixed;
   CUtensorMap tmk, tmv;
-  if (!tma::make_map(&tmk, p.k_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1) ||
-      !tma::make_map(&tmv, p.v_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1))
+  if (!dry && (!tma::make_map(&tmk, p.k_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1) ||
+               !tma::make_map(&tmv, p.v_cache, p.cache_rows, p.KH, D, p.cache_stride_t, 64, 1)))
     return 1;
   auto kernel = decode_ring_kernel<D, NC, NS, XC>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -674,6 +674,7 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
     return NSA_ERR_CUDA;
   }
   if (!XC) {
+    if (dry) return 0;
     dim3 grid(p.KH, p.B);
     kernel<<<grid, 32 * (NC + 1), smem, st>>>(p, n_slots, job_cap, tmk, tmv);
     return check_launch("decode_fused");
@@ -709,6 +710,7 @@ static int launch_shape(NsaDecodeParams p, cudaStream_t st, int max_slots, size_
   static const bool debug = getenv("NSA_DECODE_CLUSTER_DEBUG") != nullptr;
   if (debug) fprintf(stderr, "[nsa] decode: %d x %d CTAs as clusters of %d: %d clusters fit\n", p.B, p.KH, cs, fit);
   if (fit < 1 || (int64_t)p.B * p.KH > fit) return 2;
+  if (dry) return 0;
   e = cudaLaunchKernelEx(&cfg, kernel, p, n_slots, job_cap, tmk, tmv);
   if (e != cudaSuccess) {
     set_error("decode_fused: cluster launch failed: %s", cudaGetErrorString(e));
@@ -742,25 +744,35 @@ static bool cluster_size_ok(const NsaDecodeParams* p, int cs) {
   if (ctas * cs > sms) return false;
   return cap_tokens >= (cs >= 4 ? 4096 : 16384);
 }
-int decode_cluster_size_for(const NsaDecodeParams* p) {
+static int decode_cluster_size_for(const NsaDecodeParams* p) {
   if (forced_cluster_size()) return forced_cluster_size();
   for (int cs = RING_MAX_CLUSTER; cs > 1; cs >>= 1)
     if (cluster_size_ok(p, cs)) return cs;
   return 1;
 }
 
-// returns 1 when the configuration is not covered (decode_fused_kernel then runs), 0 on launch, < 0 on error
-int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) {
+// dry: everything but the launch; returns the cluster size that a launch would use (0 when the kernel does not cover the
+// configuration) instead of a status
+static int launch_or_ask(const NsaDecodeParams* p, cudaStream_t st, bool dry) {
   const int D = p->D;
-  if (p->cache_rows <= 0 || (p->cache_stride_t * 2) % 16 || (((uintptr_t)p->k_cache | (uintptr_t)p->v_cache) & 15)) return 1;
-  if (p->hp.window / 64 + 2 > RING_WIN_ROWS || p->hp.top_n > 32) return 1;
+  if (!dry && (p->cache_rows <= 0 || (p->cache_stride_t * 2) % 16 || (((uintptr_t)p->k_cache | (uintptr_t)p->v_cache) & 15))) return 1;
+  if (p->hp.window / 64 + 2 > RING_WIN_ROWS || p->hp.top_n > 32) return dry ? 0 : 1;
   const size_t cap = 227 * 1024;
   for (int cs = decode_cluster_size_for(p); cs > 1; cs >>= 1) {   // 2 = no room for clusters of this size: try the next smaller one
     if (!forced_cluster_size() && !cluster_size_ok(p, cs)) continue;
-    const int rc = D == 128 ? launch_shape<128, 6, 4, true>(*p, st, 5, cap, cs) : launch_shape<64, 6, 4, true>(*p, st, 5, cap, cs);
-    if (rc != 2) return rc;
+    const int rc = D == 128 ? launch_shape<128, 6, 4, true>(*p, st, 5, cap, cs, dry) : launch_shape<64, 6, 4, true>(*p, st, 5, cap, cs, dry);
+    if (rc != 2) return dry ? (rc == 0 ? cs : (rc == 1 ? 0 : rc)) : rc;
   }
-  return D == 128 ? launch_shape<128, 6, 4, false>(*p, st, 5, cap, 1) : launch_shape<64, 6, 4, false>(*p, st, 5, cap, 1);
+  const int rc = D == 128 ? launch_shape<128, 6, 4, false>(*p, st, 5, cap, 1, dry) : launch_shape<64, 6, 4, false>(*p, st, 5, cap, 1, dry);
+  return dry ? (rc == 0 ? 1 : (rc == 1 ? 0 : rc)) : rc;
+}
+
+// returns 1 when the configuration is not covered (decode_fused_kernel then runs), 0 on launch, < 0 on error
+int launch_decode_ring(const NsaDecodeParams* p, cudaStream_t st) { return launch_or_ask(p, st, false); }
+// CTAs per (sequence, kv head) a launch with these parameters would use; 1 also when the fallback kernel would run
+int decode_cluster_size_query(const NsaDecodeParams* p) {
+  const int n = launch_or_ask(p, nullptr, true);
+  return n == 0 ? 1 : n;
 }
 
 }  // namespace nsa

@@ -321,13 +321,15 @@ def decode_fused_supported(q, k, kernel_size, stride, block_size, top_n, num_ini
             and top_n <= 32 and num_init_blocks + num_local_blocks <= top_n and page >= 64 and page & (page - 1) == 0)
 
 
-def decode_cluster_size(B, KH, page_size, table_width):
+def decode_cluster_size(B, KH, page_size, table_width, D=128, fixed_y_maxlen=8192):
     """CTAs the one-launch decode step gives each (sequence, kv head) for a batch of B sequences whose page table has
     `table_width` columns: 1, or 2 / 4 / 8 (a thread-block cluster) for few sequences with room for long contexts."""
     from .._lib import lib
     import ctypes
     p = S["NsaDecodeParams"]()
-    p.B, p.KH, p.page_size, p.kv_table_stride = B, KH, page_size, table_width
+    p.B, p.KH, p.QH, p.D, p.page_size, p.kv_table_stride = B, KH, KH, D, page_size, table_width
+    p.hp = _hyper()
+    p.y_cap = min((int(fixed_y_maxlen) + 3) // 4 * 4, ((8 * (32 + 16 * D) - 16) * 4 // 5) // 4 * 4)
     n = lib().nsa_decode_cluster_size(ctypes.byref(p))
     assert n > 0, lib().nsa_last_error().decode()
     return n
