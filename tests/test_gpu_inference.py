@@ -247,12 +247,14 @@ def test_decode_long_contexts_use_the_round_based_selection():
 @pytest.mark.parametrize("B,KH,want", [(1, 2, 8), (5, 4, 4), (16, 4, 2)])
 def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
     """With few sequences and a page table wide enough for long contexts the one-launch decode step runs as clusters of
-    `want` CTAs per (sequence, kv head), each taking every want-th tile.  Same selection and output as the op-by-op path,
-    for contexts that leave some CTAs of a cluster without a compressed tile, with a tile each, and with many."""
+    `want` CTAs per (sequence, kv head), each taking every want-th tile.  Same selection, output and new compressed row as
+    with one CTA each and as the op-by-op path, for contexts that leave some CTAs of a cluster without a compressed tile,
+    with a tile each, and with many."""
     from flash_nsa.inference import nsa_decode_unfused, nsa_decode_fused, mean_pooling_prefill
+    from flash_nsa.inference.ops import decode_cluster_size
     QH, D = KH * 4, 128
     g = torch.Generator().manual_seed(500 + B)
-    lens = ([9000, 40, 700, 2500, 4100, 64, 1, 5000] * 2)[:B]
+    lens = ([9008, 48, 700, 2500, 4100, 64, 1, 5008] * 2)[:B]          # multiples of 16 complete a compressed row
     cache = Cache(lens, KH, D, seed=B)
     flat_k = cache.k.view(-1, KH, D)
     flat_v = cache.v.view(-1, KH, D)
@@ -262,19 +264,19 @@ def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
         flat_k[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
         flat_v[rows] = torch.randn(L, KH, D, generator=g).bfloat16()
     cache.cuda()
-    y_len = [max((L - 32) // 16 + 1, 0) for L in lens]
-    y_cu = torch.tensor([0] + torch.tensor(y_len).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
-    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_len[b])], dtype=torch.int32, device="cuda")
+    y_old = [max((L - 1 - 32) // 16 + 1, 0) for L in lens]             # the rows earlier steps have written
+    y_cu = torch.tensor([0] + torch.tensor(y_old).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_old[b])], dtype=torch.int32, device="cuda")
     for c in (cache.k, cache.v):
-        mean_pooling_prefill(c, y_cu, max(y_len), slot_mapping=slots, block_table=cache.block_tables)
+        mean_pooling_prefill(c, y_cu, max(y_old), slot_mapping=slots, block_table=cache.block_tables)
+    new_slot = [cache.cmp_slot(b, (L - 32) // 16) if (L % 16 == 0 and L >= 32) else -1 for b, L in enumerate(lens)]
     # a table as wide as a 64K-token context needs (what an engine with that model length replays its graphs on)
     wide = torch.zeros(B, 65536 // PAGE, dtype=torch.int32, device="cuda")
     wide[:, :cache.block_tables.size(1)] = cache.block_tables
     q = torch.randn(B, QH, D, generator=g).bfloat16().cuda()
     w = torch.randn(B, QH, 3, generator=g).bfloat16().cuda()
     args = (q, cache.k, cache.v, w, torch.tensor(lens, dtype=torch.int32, device="cuda"), wide,
-            torch.full((B,), -1, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
-    from flash_nsa.inference.ops import decode_cluster_size
+            torch.tensor(new_slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
     assert decode_cluster_size(B, KH, PAGE, wide.stride(0)) == want
     # the same sequences many times over fill the GPU by themselves: one CTA per (sequence, kv head)
     rep = 148 // (B * KH) + 1
@@ -282,7 +284,13 @@ def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
     o_ref, tk_ref = nsa_decode_fused(*[a.repeat(rep, *([1] * (a.dim() - 1))) if i in (0, 3, 4, 5, 6, 7) else a for i, a in enumerate(args)],
                                      return_topk=True)
     o_ref, tk_ref = o_ref[:B], tk_ref[:, :B]
+    written = [s_ for s_ in new_slot if s_ >= 0]
+    fk, fv = cache.k.view(-1, KH, D), cache.v.view(-1, KH, D)
+    rows_ref = (fk[written].clone(), fv[written].clone())
+    fk[written] = 0
+    fv[written] = 0
     o, tk = nsa_decode_fused(*args, return_topk=True)
+    assert torch.equal(fk[written], rows_ref[0]) and torch.equal(fv[written], rows_ref[1]) and bool((rows_ref[0] != 0).any())
     o_un = nsa_decode_unfused(*args)
     assert torch.equal(tk.sort(-1).values, tk_ref.sort(-1).values)
     assert (o.float() - o_ref.float()).abs().max().item() <= 4e-3      # bf16 rounding of a different merge order
