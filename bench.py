@@ -279,7 +279,8 @@ def reference_gpu_arm(args):
 
 def reference_gpu_decode(dev):
     """The reference's own nsa_decode on the shapes of config 4 (batch 64, contexts U[4096, 8192] with seed 1004, 32 q / 8 kv
-    heads, d = 128, page 256, shuffled page tables) and of its 4 GiB sweep at 8K and 64K tokens; caches filled with seeded
+    heads, d = 128, page 256, shuffled page tables), of its 4 GiB sweep at 8K, 64K and 128K tokens and of one sequence of 32K /
+    128K tokens; caches filled with seeded
     N(0,1) values (the timing does not depend on them), eager and replayed from a CUDA graph."""
     from flash_nsa.inference import nsa_decode
 
@@ -329,8 +330,10 @@ def reference_gpu_decode(dev):
 
     rng = random.Random(1004)
     res = {"config4": case([rng.randint(4096, 8192) for _ in range(64)], 32, 8, 128, 256, 1004)}
-    for L in (8192, 65536):
+    for L in (8192, 65536, 131072):
         res[f"sweep_4gib_{L}"] = case([L] * (1024 * 2048 // L), 64, 4, 128, 256, L)
+    for L in (32768, 131072):   # one long sequence: what the reference's split-count arguments are for
+        res[f"one_sequence_{L}"] = case([L], 64, 4, 128, 256, L + 1)
     return res
 
 
