@@ -328,12 +328,43 @@ def reference_gpu_decode(dev):
             out["cuda_graph"] = f"not captured: {type(e).__name__}"
         return out
 
+    def prefill_case(prefix, chunk, qh, kh, d, page):
+        """The chunked-prefill step of config 4: `chunk` new tokens of one sequence on a `prefix`-token context, K/V of all
+        of them already in the (seeded N(0,1)) cache, the compressed rows of the chunk written by the step."""
+        from flash_nsa.inference import nsa_prefill
+        L1 = prefix + chunk
+        ylen = (L1 - 32) // 16 + 1
+        n_tok, n_cmp = -(-L1 // page), -(-ylen // page)
+        g = torch.Generator(device=dev).manual_seed(prefix)
+        kc = torch.randn(n_tok + n_cmp, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        vc = torch.randn(n_tok + n_cmp, page, kh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        perm = torch.randperm(n_tok + n_cmp, generator=torch.Generator().manual_seed(prefix)).to(torch.int32)
+        bt, cbt = perm[:n_tok].view(1, -1).to(dev), perm[n_tok:].view(1, -1).to(dev)
+        slots = [int(perm[n_tok + j // page]) * page + j % page if 16 * j + 31 >= prefix else -1 for j in range(ylen)]
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        q = torch.randn(chunk, qh, d, device=dev, dtype=torch.bfloat16, generator=g)
+        w = torch.randn(chunk, qh, 3, device=dev, dtype=torch.bfloat16, generator=g)
+        args = (q, kc, vc, w, i32([0, chunk]), i32([0, ylen]), chunk, ylen, i32([L1]), bt, i32(slots), cbt)
+        out = {"ms_eager": timed(lambda: nsa_prefill(*args), 20)}
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                nsa_prefill(*args)
+            out["ms_cuda_graph"] = timed(graph.replay, 50)
+        except Exception as e:  # noqa: BLE001
+            out["cuda_graph"] = f"not captured: {type(e).__name__}"
+        return out
+
     rng = random.Random(1004)
     res = {"config4": case([rng.randint(4096, 8192) for _ in range(64)], 32, 8, 128, 256, 1004)}
     for L in (8192, 65536, 131072):
         res[f"sweep_4gib_{L}"] = case([L] * (1024 * 2048 // L), 64, 4, 128, 256, L)
     for L in (32768, 131072):   # one long sequence: what the reference's split-count arguments are for
         res[f"one_sequence_{L}"] = case([L], 64, 4, 128, 256, L + 1)
+    try:
+        res["config4_prefill_chunk"] = prefill_case(6144, 2048, 32, 8, 128, 256)
+    except Exception as e:  # noqa: BLE001
+        res["config4_prefill_chunk"] = {"unavailable": f"{type(e).__name__}: {(str(e).strip().splitlines() or [''])[0]}"[:300]}
     return res
 
 
