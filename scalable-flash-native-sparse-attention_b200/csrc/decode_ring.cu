@@ -245,23 +245,46 @@ __global__ void __launch_bounds__(32 * (RING_NC + 1), RING_NC <= 3 ? 2 : 1)
     marks[2] = n;
   }
   {
+    // The new compressed row: the mean of the last ks token rows, summed in row order like the stand-alone pooling kernel.
+    // All threads first bring the ks x (K, V) row slices into shared memory with every load in flight at once (a thread
+    // that loads and adds row after row pays a page-table look-up and a cache-row read ks times in a row: 5 us per CTA).
     const int slot = p.slot_mapping ? p.slot_mapping[b] : -1;
-    if (slot >= 0 && ctx >= ks && tid < 2 * CH) {   // K by threads 0..CH-1, V by the next CH threads
-      __nv_bfloat16* cache = tid < CH ? kc : vc;
-      const int c = tid % CH;
+    if (slot >= 0 && ctx >= ks) {   // the same for every thread of the CTA (and every CTA of a cluster: each writes the row)
       const int start = ((ctx - ks) / st) * st;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int i = 0; i < ks; ++i) {
-        uint4 u = *reinterpret_cast<const uint4*>(cache + tokrow(start + i) * cs + c * 8);
-        acc[0] += bf16_lo(u.x); acc[1] += bf16_hi(u.x); acc[2] += bf16_lo(u.y); acc[3] += bf16_hi(u.y);
-        acc[4] += bf16_lo(u.z); acc[5] += bf16_hi(u.z); acc[6] += bf16_lo(u.w); acc[7] += bf16_hi(u.w);
+      uint4* stage = reinterpret_cast<uint4*>(state);   // [ks][K chunks, V chunks]: the states are not in use yet
+      const int total = min(ks * 2 * CH, 5 * (int)blockDim.x);
+      uint4 piece[5];
+#pragma unroll
+      for (int u = 0; u < 5; ++u) {
+        const int idx = tid + u * blockDim.x;
+        if (idx < total) {
+          const int i = idx / (2 * CH), rem = idx - i * 2 * CH;
+          const __nv_bfloat16* cache = rem < CH ? kc : vc;
+          piece[u] = *reinterpret_cast<const uint4*>(cache + tokrow(start + i) * cs + (rem % CH) * 8);
+        }
       }
-      const float inv = 1.f / (float)ks;
-      uint4 w4;
-      w4.x = pack_bf16(acc[0] * inv, acc[1] * inv); w4.y = pack_bf16(acc[2] * inv, acc[3] * inv);
-      w4.z = pack_bf16(acc[4] * inv, acc[5] * inv); w4.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-      *reinterpret_cast<uint4*>(cache + (int64_t)slot * cs + c * 8) = w4;
-      fence_proxy_async_global();   // the row is read below by bulk tensor loads of this CTA
+#pragma unroll
+      for (int u = 0; u < 5; ++u) {
+        const int idx = tid + u * blockDim.x;
+        if (idx < total) stage[idx] = piece[u];
+      }
+      __syncthreads();
+      if (tid < 2 * CH) {   // K by threads 0..CH-1, V by the next CH threads
+        __nv_bfloat16* cache = tid < CH ? kc : vc;
+        const int c = tid % CH;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int i = 0; i < ks; ++i) {
+          const uint4 u = stage[i * 2 * CH + tid];
+          acc[0] += bf16_lo(u.x); acc[1] += bf16_hi(u.x); acc[2] += bf16_lo(u.y); acc[3] += bf16_hi(u.y);
+          acc[4] += bf16_lo(u.z); acc[5] += bf16_hi(u.z); acc[6] += bf16_lo(u.w); acc[7] += bf16_hi(u.w);
+        }
+        const float inv = 1.f / (float)ks;
+        uint4 w4;
+        w4.x = pack_bf16(acc[0] * inv, acc[1] * inv); w4.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+        w4.z = pack_bf16(acc[4] * inv, acc[5] * inv); w4.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+        *reinterpret_cast<uint4*>(cache + (int64_t)slot * cs + c * 8) = w4;
+        fence_proxy_async_global();   // the row is read below by bulk tensor loads of this CTA
+      }
     }
   }
   __syncthreads();
