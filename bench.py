@@ -1106,7 +1106,7 @@ def inference_bench(dev, check_seqs=16, sweep=True):
                                  "tensor_frac": pre_flop / (ms_pre * 1e-3) / 1e12 / peak_tf, "algorithmic_gb": pre_bytes / 1e9,
                                  "hbm_frac": pre_bytes / (ms_pre * 1e-3) / 1e9 / peak_gbs,
                                  "bound": "latency / occupancy: 2048 query rows are a few hundred CTAs of short loops, far below both roofs",
-                                 "launches": 7},
+                                 "launches": 9},
             "decode_sweep_4gib_64q_4kv": sweep}
 
 

@@ -366,12 +366,24 @@ __global__ void paged_pool_kernel(NsaPagedPoolParams p) {
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
   const int start = j * p.stride;
-  for (int i = 0; i < p.kernel_size; ++i) {
-    int r = start + i;
-    int64_t row = (int64_t)tab[r / p.page_size] * p.page_size + r % p.page_size;
-    F8 f = unpack8(*reinterpret_cast<const uint4*>(cache + row * p.row_stride + h * p.D + c * 8));
+  // rows are added in order; eight of them are fetched together (page-table entry, then the row: two dependent memory
+  // round trips that a one-row-at-a-time loop pays kernel_size times)
+  for (int i0 = 0; i0 < p.kernel_size; i0 += 8) {
+    uint4 piece[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+    for (int u = 0; u < 8; ++u) {
+      const int r = start + min(i0 + u, p.kernel_size - 1);
+      const int64_t row = (int64_t)tab[r / p.page_size] * p.page_size + r % p.page_size;
+      piece[u] = *reinterpret_cast<const uint4*>(cache + row * p.row_stride + h * p.D + c * 8);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (i0 + u < p.kernel_size) {
+        const F8 f = unpack8(piece[u]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc.v[e] += f.v[e];
+      }
+    }
   }
   float inv = 1.f / (float)p.kernel_size;
 #pragma unroll

@@ -9,7 +9,7 @@ forward kernels running on a piece table with the paged-row lookup switched on: 
 any of these calls, shapes depend only on the arguments, so a decode step can be captured in a CUDA graph.
 """
 from ..ops._common import poll_status, post_status
-from .ops import (mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
+from .ops import (mean_pooling_prefill, kv_mean_pooling_prefill, mean_pooling_decode, kv_mean_pooling_decode, cmp_attn_prefill, cmp_attn_decode,
                   topk_prefill, topk_decode, slc_attn_prefill, slc_attn_decode, fused_slc_swa_attn_decode, swa_prefill,
                   combine_prefill, combine_decode, nsa_decode_fused, decode_fused_supported, zero_cache_tails, one_step)
 
@@ -42,8 +42,7 @@ def nsa_prefill(q, k, v, w, x_cu_seqlens, y_cu_seqlens, x_maxlen, y_maxlen, cont
     poll_status(q.device)      # a pipeline time-out of an earlier call raises here, without synchronising
     hp = dict(kernel_size=kernel_size, stride=stride)
     with one_step():   # the four attention ops share the length tables derived from context_lens / x_cu_seqlens
-        mean_pooling_prefill(k, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
-        mean_pooling_prefill(v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
+        kv_mean_pooling_prefill(k, v, y_cu_seqlens, y_maxlen, block_table=block_tables, slot_mapping=cmp_slot_mapping, **hp)
         cmp_o, lse = cmp_attn_prefill(q, k, v, x_cu_seqlens, x_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,
                                       sm_scale=sm_scale, **hp)
         topk = topk_prefill(q, k, lse, x_cu_seqlens, x_maxlen, y_maxlen, block_tables=cmp_block_tables, context_lens=context_lens,

@@ -157,6 +157,12 @@ def mean_pooling_prefill(x, y_cu_seqlens, y_maxlen, slot_mapping, block_table, k
     return x
 
 
+def kv_mean_pooling_prefill(k, v, y_cu_seqlens, y_maxlen, slot_mapping, block_table, kernel_size=32, stride=16):
+    """K and V caches in one launch (the reference pools them one after the other, inference/__init__.py:76-77)."""
+    assert k.shape == v.shape
+    _pool(k, v, slot_mapping, block_table, y_cu_seqlens, y_maxlen, None, kernel_size, stride, False)
+
+
 def mean_pooling_decode(x, slot_mapping, block_table, context_lens=None, kernel_size=32, stride=16):
     _pool(x, None, slot_mapping, block_table, None, None, context_lens, kernel_size, stride, True)
     return x
