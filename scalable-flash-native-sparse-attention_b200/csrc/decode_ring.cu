@@ -24,13 +24,14 @@
 // Partial softmax states are merged through shared memory after 1 and after 4; that region holds the score arrays in
 // between.  Bytes read per (sequence, kv head): compressed K twice and V once, 16 selected blocks and <= 9 window tiles.
 //
-// Few sequences with long contexts (fewer CTAs than half the SMs) run as thread-block CLUSTERS of 2, 4 or 8 CTAs per
-// (sequence, kv head), XC = true: CTA r of the cluster takes every CS-th compressed tile, window tile and selected slot.
-// Three exchanges through distributed shared memory: (1) the log-sum-exp of each CTA's share of the compressed rows, read
-// by every CTA to form the global one; (2) every head-summed probability is stored into the score array of EVERY CTA, and
-// each CTA then makes the same selection for itself; (3) every CTA reads the others' normalised partial outputs of the three
-// branches with their log-sum-exps, merges them and writes its slice of the output row.  The exchanges are mbarriers that each CTA's elected
-// thread arrives on remotely (bounded waits like every other one here); one hardware cluster barrier after the barrier
+// Few sequences (the grid would leave most SMs idle) run as thread-block CLUSTERS of 2, 4 or 8 CTAs per (sequence, kv
+// head), XC = true: CTA r of the cluster takes every CS-th compressed tile, window tile and selected slot.  Three exchanges
+// through distributed shared memory: (1) the log-sum-exp of each CTA's share of the compressed rows, read by every CTA to
+// form the global one; (2) every tile's 64 head-summed probabilities are stored into the score array of EVERY CTA (16-byte
+// remote stores), and each CTA then makes the same selection for itself; (3) every CTA reads the others' normalised partial
+// outputs of the three branches with their log-sum-exps (all of a thread's remote loads in flight together), merges them
+// and writes its slice of the output row.  An exchange is an mbarrier per CTA on which thread c of every CTA arrives
+// remotely for CTA c (bounded waits like every other one here); one hardware cluster barrier after the barrier
 // initialisation and one before exit (a CTA's shared memory must outlive every remote access to it).
 #include <cstdio>
 #include <cstdlib>
