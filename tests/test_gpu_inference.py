@@ -244,18 +244,14 @@ def test_decode_long_contexts_use_the_round_based_selection():
             assert len(set(row)) == 16 and min(row) >= 0 and max(row) <= nkb
 
 
-@pytest.mark.parametrize("B,KH,want", [(1, 2, 8), (5, 4, 4), (16, 4, 2)])
-def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
-    """With few sequences and a page table wide enough for long contexts the one-launch decode step runs as clusters of
-    `want` CTAs per (sequence, kv head), each taking every want-th tile.  Same selection, output and new compressed row as
-    with one CTA each and as the op-by-op path, for contexts that leave some CTAs of a cluster without a compressed tile,
-    with a tile each, and with many."""
+def _cluster_case(lens, KH, G, D, seed, want=None):
+    """One fused decode step on a page table as wide as a 64K-token context needs (few sequences then run as clusters)
+    against the same sequences many times over (enough CTAs for one each) and against the op-by-op path."""
     from flash_nsa.inference import nsa_decode_unfused, nsa_decode_fused, mean_pooling_prefill
     from flash_nsa.inference.ops import decode_cluster_size
-    QH, D = KH * 4, 128
-    g = torch.Generator().manual_seed(500 + B)
-    lens = ([9008, 48, 700, 2500, 4100, 64, 1, 5008] * 2)[:B]          # multiples of 16 complete a compressed row
-    cache = Cache(lens, KH, D, seed=B)
+    B, QH = len(lens), KH * G
+    g = torch.Generator().manual_seed(seed)
+    cache = Cache(lens, KH, D, seed=seed)
     flat_k = cache.k.view(-1, KH, D)
     flat_v = cache.v.view(-1, KH, D)
     for b, L in enumerate(lens):
@@ -267,20 +263,21 @@ def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
     y_old = [max((L - 1 - 32) // 16 + 1, 0) for L in lens]             # the rows earlier steps have written
     y_cu = torch.tensor([0] + torch.tensor(y_old).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
     slots = torch.tensor([cache.cmp_slot(b, j) for b in range(B) for j in range(y_old[b])], dtype=torch.int32, device="cuda")
-    for c in (cache.k, cache.v):
-        mean_pooling_prefill(c, y_cu, max(y_old), slot_mapping=slots, block_table=cache.block_tables)
+    if slots.numel():
+        for c in (cache.k, cache.v):
+            mean_pooling_prefill(c, y_cu, max(y_old), slot_mapping=slots, block_table=cache.block_tables)
     new_slot = [cache.cmp_slot(b, (L - 32) // 16) if (L % 16 == 0 and L >= 32) else -1 for b, L in enumerate(lens)]
-    # a table as wide as a 64K-token context needs (what an engine with that model length replays its graphs on)
     wide = torch.zeros(B, 65536 // PAGE, dtype=torch.int32, device="cuda")
     wide[:, :cache.block_tables.size(1)] = cache.block_tables
     q = torch.randn(B, QH, D, generator=g).bfloat16().cuda()
     w = torch.randn(B, QH, 3, generator=g).bfloat16().cuda()
     args = (q, cache.k, cache.v, w, torch.tensor(lens, dtype=torch.int32, device="cuda"), wide,
             torch.tensor(new_slot, dtype=torch.int32, device="cuda"), cache.cmp_block_tables)
-    assert decode_cluster_size(B, KH, PAGE, wide.stride(0)) == want
+    cs = decode_cluster_size(B, KH, PAGE, wide.stride(0), D=D)
+    assert cs == want if want is not None else cs > 1
     # the same sequences many times over fill the GPU by themselves: one CTA per (sequence, kv head)
     rep = 148 // (B * KH) + 1
-    assert decode_cluster_size(B * rep, KH, PAGE, wide.stride(0)) == 1
+    assert decode_cluster_size(B * rep, KH, PAGE, wide.stride(0), D=D) == 1
     o_ref, tk_ref = nsa_decode_fused(*[a.repeat(rep, *([1] * (a.dim() - 1))) if i in (0, 3, 4, 5, 6, 7) else a for i, a in enumerate(args)],
                                      return_topk=True)
     o_ref, tk_ref = o_ref[:B], tk_ref[:, :B]
@@ -290,11 +287,36 @@ def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
     fk[written] = 0
     fv[written] = 0
     o, tk = nsa_decode_fused(*args, return_topk=True)
-    assert torch.equal(fk[written], rows_ref[0]) and torch.equal(fv[written], rows_ref[1]) and bool((rows_ref[0] != 0).any())
+    assert torch.equal(fk[written], rows_ref[0]) and torch.equal(fv[written], rows_ref[1])
+    assert not written or bool((rows_ref[0] != 0).any())
     o_un = nsa_decode_unfused(*args)
     assert torch.equal(tk.sort(-1).values, tk_ref.sort(-1).values)
     assert (o.float() - o_ref.float()).abs().max().item() <= 4e-3      # bf16 rounding of a different merge order
     assert (o.float() - o_un.float()).abs().max().item() <= TOL
+
+
+@pytest.mark.parametrize("B,KH,want", [(1, 2, 8), (5, 4, 4), (16, 4, 2)])
+def test_decode_of_few_sequences_splits_each_over_a_cluster(B, KH, want):
+    """With few sequences and a page table wide enough for long contexts the one-launch decode step runs as clusters of
+    `want` CTAs per (sequence, kv head), each taking every want-th tile.  Same selection, output and new compressed row as
+    with one CTA each and as the op-by-op path, for contexts that leave some CTAs of a cluster without a compressed tile,
+    with a tile each, and with many."""
+    lens = ([9008, 48, 700, 2500, 4100, 64, 1, 5008] * 2)[:B]          # multiples of 16 complete a compressed row
+    _cluster_case(lens, KH, 4, 128, seed=500 + B, want=want)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_cluster_decode_on_random_shapes(seed):
+    """Random batch sizes, head counts, head dims and context lengths (1 to 6000 tokens, some completing a compressed row)
+    through the cluster form of the decode step."""
+    import random
+    rng = random.Random(9000 + seed)
+    KH = rng.choice([1, 2, 4])
+    G = rng.choice([1, 2, 4, 8, 16])
+    D = rng.choice([64, 128])
+    B = rng.randint(1, max(1, 16 // KH))
+    lens = [rng.choice([rng.randint(1, 6000), 16 * rng.randint(2, 370)]) for _ in range(B)]
+    _cluster_case(lens, KH, G, D, seed=9000 + seed)
 
 
 def test_rows_past_a_sequence_end_may_hold_anything():
