@@ -394,6 +394,11 @@ int nsa_wgrad_accum(const NsaWgradParams* p, void* stream);
 int nsa_selftest_wait_timeout(int32_t* status, int32_t polls, int32_t* waits_failed, void* stream);
 const char* nsa_last_error(void);
 int nsa_version(void);
+/* The 16-bit element type this build of the library computes in: 0 = bf16 (libnsa_sm100.so), 1 = IEEE half
+ * (libnsa_sm100_f16.so, the same sources compiled with -DNSA_F16; where this header says bf16, that build reads and writes
+ * half).  The reference's ops take either type (its tests switch DTYPE, test.py:14); a host loads the library that matches
+ * its tensors.                                                                                                        */
+int nsa_element_type(void);
 /* sizeof() of a parameter struct by name ("NsaAttnParams", ...), 0 if unknown: lets a binding verify its mirror */
 int nsa_struct_size(const char* name);
 

@@ -62,7 +62,12 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, 
   cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)row_stride_elems * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   cuuint32_t estr[3] = {1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+#ifdef NSA_F16
+  const CUtensorMapDataType elem = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;   // matters for the bulk tensor REDUCTIONS (adds in this type)
+#else
+  const CUtensorMapDataType elem = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+#endif
+  return fn(m, elem, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -72,6 +77,13 @@ bool make_map(CUtensorMap* m, const void* base, int64_t rows, int heads, int D, 
 
 extern "C" const char* nsa_last_error(void) { return nsa::g_err; }
 extern "C" int nsa_version(void) { return 100; }
+extern "C" int nsa_element_type(void) {
+#ifdef NSA_F16
+  return 1;
+#else
+  return 0;
+#endif
+}
 
 extern "C" int nsa_struct_size(const char* name) {
   if (!name) return 0;

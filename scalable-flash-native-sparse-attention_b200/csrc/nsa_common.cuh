@@ -7,6 +7,18 @@
 #include <stdint.h>
 #include "../../include/nsa_sm100.h"
 
+// NSA_F16: the second build of the library (libnsa_sm100_f16.so), the same kernels with IEEE half as the 16-bit element
+// type.  Every kernel touches its 16-bit data through the helpers below, the two scalar conversions and the element type
+// named here; the MMA operand formats and the tensor-map element type follow the same switch (tc_common.cuh, abi.cu).
+#ifdef NSA_F16
+#define __nv_bfloat16 __half
+#define __float2bfloat16 __float2half_rn
+#define __bfloat162float __half2float
+#define NSA_MMA_ELEM "f16"
+#else
+#define NSA_MMA_ELEM "bf16"
+#endif
+
 namespace nsa {
 
 // ------------------------------------------------------------------ host-side error plumbing
@@ -76,12 +88,22 @@ __device__ __forceinline__ Piece load_piece(const NsaSeqMeta& m, int b) {
 }
 
 // ------------------------------------------------------------------ small math / packing
+// two floats -> one word of two 16-bit elements (low half first), and back ("bf16" in the names: the element type of the build)
+#ifdef NSA_F16
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __low2float(*reinterpret_cast<const __half2*>(&v)); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __high2float(*reinterpret_cast<const __half2*>(&v)); }
+#else
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -150,14 +172,14 @@ __device__ __forceinline__ void load_b_frag_kn(uint32_t (&b)[4], uint32_t tile, 
 // D(16x8, fp32) += A(16x16, bf16) * B(16x8, bf16)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      "mma.sync.aligned.m16n8k16.row.col.f32." NSA_MMA_ELEM "." NSA_MMA_ELEM ".f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      "mma.sync.aligned.m16n8k16.row.col.f32." NSA_MMA_ELEM "." NSA_MMA_ELEM ".f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }

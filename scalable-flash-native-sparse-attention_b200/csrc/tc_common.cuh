@@ -40,9 +40,15 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t slab_b
   d |= (uint64_t)2 << 61;
   return d;
 }
-// bf16 x bf16 -> fp32, M x N tile; each operand K-major (contraction index contiguous) or MN-major
+// 16-bit x 16-bit -> fp32, M x N tile; each operand K-major (contraction index contiguous) or MN-major.  Operand format
+// fields (bits 7-9 for A, 10-12 for B): 1 = bf16, 0 = IEEE half (the NSA_F16 build).
+#ifdef NSA_F16
+constexpr uint32_t kOperandFormat = 0u;
+#else
+constexpr uint32_t kOperandFormat = 1u;
+#endif
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, bool b_mn_major, bool a_mn_major = false) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+  return (1u << 4) | (kOperandFormat << 7) | (kOperandFormat << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 

@@ -51,18 +51,20 @@ def _parse_header(text):
 with open(_HEADER) as _f:
     _parse_header(_f.read())
 
-_lib = None
+_LIB_PATH_F16 = os.path.join(_PKG_ROOT, "csrc", "libnsa_sm100_f16.so")
+_libs = {}
 
 
-def lib():
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not os.path.exists(_LIB_PATH):
+def lib(f16=False):
+    """The kernel library: the bf16 build, or (f16=True) the build of the same sources for IEEE-half tensors."""
+    if f16 in _libs:
+        return _libs[f16]
+    path = _LIB_PATH_F16 if f16 else _LIB_PATH
+    if not os.path.exists(path):
         raise ImportError(
-            f"{_LIB_PATH} is missing: build it with `python {os.path.join(_PKG_ROOT, 'build.py')}` "
+            f"{path} is missing: build it with `python {os.path.join(_PKG_ROOT, 'build.py')}` "
             "(nvcc, sm_100a).  flash_nsa has no CPU or PyTorch fallback.")
-    L = ctypes.CDLL(_LIB_PATH)
+    L = ctypes.CDLL(path)
     L.nsa_last_error.restype = ctypes.c_char_p
     L.nsa_struct_size.argtypes = [ctypes.c_char_p]
     for name, st in structs.items():
@@ -71,8 +73,10 @@ def lib():
             raise ImportError(f"ABI mismatch for {name}: header mirror {ctypes.sizeof(st)} bytes, library {n} bytes")
     for fn in functions:
         if not hasattr(L, fn):
-            raise ImportError(f"{_LIB_PATH} does not export {fn}")
-    _lib = L
+            raise ImportError(f"{path} does not export {fn}")
+    if L.nsa_element_type() != (1 if f16 else 0):
+        raise ImportError(f"{path} computes in the other 16-bit element type")
+    _libs[f16] = L
     return L
 
 
@@ -87,10 +91,10 @@ KERNELS_PER_CALL = {
 launch_count = 0
 
 
-def call(fn_name, params, stream):
+def call(fn_name, params, stream, f16=False):
     """Invoke an entry point `int fn(const Params*, void* stream)`; raise on a non-zero status."""
     global launch_count
-    L = lib()
+    L = lib(f16)
     n = KERNELS_PER_CALL.get(fn_name, 1)
     ph = getattr(params, "phases", 0) if fn_name.endswith("_bwd") else 0
     if ph:   # a backward entry point asked for a subset of {delta, dK/dV, dQ}

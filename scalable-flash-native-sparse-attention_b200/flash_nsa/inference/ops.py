@@ -86,13 +86,14 @@ class _PagedMeta:
 
 def _flat(cache):
     """[pages, page, h, d] -> ([pages*page, h, d] view, page_size)"""
-    assert cache.dim() == 4 and cache.is_contiguous() and cache.dtype == torch.bfloat16
+    assert cache.dim() == 4 and cache.is_contiguous() and cache.dtype in (torch.bfloat16, torch.float16)
     return cache.view(-1, cache.size(2), cache.size(3)), cache.size(1)
 
 
 def _attn_params(q, kf, vf, meta, hp, sm_scale, o, lse, lse_head_major, topk=None):
     T, QH, D = q.shape
-    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1 and q.stride(1) == D
+    assert q.dtype in (torch.bfloat16, torch.float16) and kf.dtype == q.dtype and vf.dtype == q.dtype
+    assert q.stride(-1) == 1 and q.stride(1) == D
     KH = kf.size(1)
     p = S["NsaAttnParams"]()
     p.meta, p.hp = meta.struct, hp
@@ -350,7 +351,8 @@ def nsa_decode_fused(q, k, v, w, context_lens, block_tables, cmp_slot_mapping, c
     kf, page = _flat(k)
     vf, _ = _flat(v)
     KH = kf.size(1)
-    assert q.dtype == torch.bfloat16 and q.stride(-1) == 1 and q.stride(1) == D and w.stride(-1) == 1 and w.stride(1) == 3
+    assert q.dtype in (torch.bfloat16, torch.float16) and kf.dtype == q.dtype and vf.dtype == q.dtype and w.dtype == q.dtype
+    assert q.stride(-1) == 1 and q.stride(1) == D and w.stride(-1) == 1 and w.stride(1) == 3
     o = torch.empty(B, QH, D, device=q.device, dtype=q.dtype)
     topk = torch.empty(KH, B, top_n, dtype=torch.int32, device=q.device) if return_topk else None
     p = S["NsaDecodeParams"]()

@@ -25,7 +25,7 @@ def wgrad_accum(input, grad_output, main_grad):
     from ..ops._common import S, call, ptr, status_word
     rows, n_in = input.shape
     n_out = grad_output.size(1)
-    ok = (input.is_cuda and input.dtype == torch.bfloat16 and grad_output.dtype == torch.bfloat16 and main_grad.dtype == torch.float32
+    ok = (input.is_cuda and input.dtype in (torch.bfloat16, torch.float16) and grad_output.dtype == input.dtype and main_grad.dtype == torch.float32
           and tuple(main_grad.shape) == (n_out, n_in) and n_out % 128 == 0 and n_in % 128 == 0
           and input.stride(1) == 1 and grad_output.stride(1) == 1 and main_grad.stride(1) == 1
           and input.stride(0) % 8 == 0 and grad_output.stride(0) % 8 == 0 and main_grad.stride(0) % 4 == 0

@@ -64,9 +64,12 @@ def local_rows(helper, cp=None) -> int:
     return helper.cp_len if cp else helper.total_len
 
 
+HALF_TYPES = (torch.bfloat16, torch.float16)   # one build of the kernel library each
+
+
 def check_bf16_3d(name, t, last_contig=True):
     assert t.is_cuda, f"{name} must be a CUDA tensor"
-    assert t.dtype == torch.bfloat16, f"{name} must be bfloat16 (got {t.dtype}); this build computes in bf16 only"
+    assert t.dtype in HALF_TYPES, f"{name} must be bfloat16 or float16 (got {t.dtype})"
     assert t.dim() == 3, f"{name} must be [t, h, d]"
     assert t.stride(-1) == 1 and t.stride(1) == t.size(-1), f"{name}: heads and head_dim must be contiguous"
 
@@ -146,7 +149,9 @@ def post_status(device):
 
 
 def call(fn, params, ref_tensor):
-    _lib.call(fn, params, stream_ptr(ref_tensor))
+    """`ref_tensor`: one of the call's 16-bit tensors (its device gives the stream, its dtype the build of the library);
+    entry points without 16-bit data pass any tensor of the call."""
+    _lib.call(fn, params, stream_ptr(ref_tensor), f16=ref_tensor.dtype == torch.float16)
 
 
 def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_major=False, dout=None, delta=None,
@@ -157,6 +162,7 @@ def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_majo
     check_bf16_3d("v", v)
     T, QH, D = q.shape
     KH = k.size(1)
+    assert k.dtype == q.dtype and v.dtype == q.dtype, "q, k and v must share one 16-bit dtype"
     assert k.size(-1) == D and v.size(-1) == D, "this build needs qk_head_dim == v_head_dim"
     assert v.size(1) == KH and v.size(0) == k.size(0) and QH % KH == 0
     p = S["NsaAttnParams"]()
@@ -166,7 +172,7 @@ def attn_params(q, k, v, helper, sm_scale, *, o=None, lse=None, lse_is_head_majo
     p.q_stride_t, p.k_stride_t, p.v_stride_t = q.stride(0), k.stride(0), v.stride(0)
     for name, t in (("o", o), ("dout", dout), ("dq", dq)):
         if t is not None:
-            assert t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: bf16, contiguous heads"
+            assert t.dtype == q.dtype and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: the dtype of q, contiguous heads"
     for name, t in (("dk", dk), ("dv", dv)):
         if t is not None:
             assert t.dtype == torch.float32 and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: fp32, contiguous heads"

@@ -15,7 +15,7 @@ def _params(x, y, dy, dx, kind):
 
 
 def _fwd(x, kind):
-    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.size(-1) % 16 == 0
+    assert x.dtype in (torch.bfloat16, torch.float16) and x.is_contiguous() and x.size(-1) % 16 == 0
     y = torch.empty(*x.shape[:-1], x.size(-1) // 2, device=x.device, dtype=x.dtype)
     call("nsa_act_fwd", _params(x, y, None, None, kind), x)
     return y

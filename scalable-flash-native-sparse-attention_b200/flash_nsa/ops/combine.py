@@ -22,8 +22,8 @@ def _check(a, b, c, w):
     assert list(w.shape) == [T, H, 3], f"w.shape: {w.shape}, expected: [{T}, {H}, 3]"
     assert math.log2(D).is_integer()
     for name, t in (("a", a), ("b", b), ("c", c)):
-        assert t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: bf16 with contiguous heads"
-    assert w.dtype == torch.bfloat16 and w.stride(-1) == 1 and w.stride(1) == 3
+        assert t.dtype == a.dtype and t.stride(-1) == 1 and t.stride(1) == D, f"{name}: one 16-bit dtype, contiguous heads"
+    assert a.dtype in (torch.bfloat16, torch.float16) and w.dtype == a.dtype and w.stride(-1) == 1 and w.stride(1) == 3
 
 
 def combine_fwd(a, b, c, w, out=None):

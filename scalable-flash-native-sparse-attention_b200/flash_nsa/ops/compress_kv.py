@@ -62,7 +62,7 @@ def construct_block_fwd(x, helper=NSAHelper):
 
 def construct_block_bwd(x, dy, dx: Optional[torch.Tensor] = None, helper=NSAHelper):
     dy = dy.contiguous()
-    assert dy.dtype == torch.bfloat16 and dy.dim() == 4
+    assert dy.dtype in (torch.bfloat16, torch.float16) and dy.dim() == 4
     if dx is not None:
         assert dx.dtype == torch.float32
         call("nsa_construct_block_bwd", _block_params(None, dy, dx, helper, True), dy)

@@ -26,7 +26,7 @@ def _launch(q, k, qe, ke, cos, sin, backward):
 def _check(q, k, cos, sin):
     assert q.dim() == 4 and k.dim() == 4 and q.shape[:2] == k.shape[:2] and q.size(-1) == k.size(-1)
     assert q.size(1) == cos.size(1)
-    assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and cos.dtype == torch.bfloat16 and sin.dtype == torch.bfloat16
+    assert q.dtype in (torch.bfloat16, torch.float16) and k.dtype == q.dtype and cos.dtype == q.dtype and sin.dtype == q.dtype
     assert cos.shape == sin.shape and cos.stride() == sin.stride() and cos.size(-1) == q.size(-1)
     for t in (q, k, cos, sin):
         assert t.stride(-1) == 1

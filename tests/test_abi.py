@@ -39,6 +39,15 @@ def test_every_declared_entry_point_is_exported():
     assert not missing, missing
 
 
+def test_the_half_build_exports_the_same_entry_points():
+    """libnsa_sm100_f16.so: the same sources with IEEE half as the 16-bit element type; same symbols, same structs."""
+    m = _lib_module()
+    L, H = m.lib(), m.lib(f16=True)          # raises on a missing symbol, a struct size mismatch or the wrong element type
+    assert L.nsa_element_type() == 0 and H.nsa_element_type() == 1
+    fns, _ = _declared()
+    assert not [f for f in fns if not hasattr(H, f)]
+
+
 def test_struct_mirrors_match_the_library():
     m = _lib_module()
     L = m.lib()                      # raises on any size mismatch or missing symbol
